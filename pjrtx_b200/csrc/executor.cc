@@ -1,0 +1,1186 @@
+#include "executor.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <set>
+
+namespace pjrtx {
+
+// ---------------------------------------------------------------------------
+// Custom-call registry.
+
+namespace {
+
+struct CustomCallEntry {
+  std::string op_name;  // "identity" or a plan kind name
+  int arity;
+};
+std::mutex g_registry_mu;
+std::map<std::string, CustomCallEntry> g_registry;
+uint64_t g_registry_version = 0;
+
+const char* kSdpaTargets[] = {"pjrtx.mlx_metal.scaled_dot_product_attention", "pjrtx.b200.scaled_dot_product_attention"};
+const char* kBinaryAddTargets[] = {"pjrtx.mlx_metal.custom_binary_add_f32", "pjrtx.b200.custom_binary_add_f32"};
+
+bool is_sdpa_target(const std::string& t) {
+  for (const char* n : kSdpaTargets)
+    if (t == n) return true;
+  return false;
+}
+
+}  // namespace
+
+bool register_custom_call(const std::string& target, const std::string& op_name, int arity) {
+  if (target.empty()) return false;
+  if (op_name != "identity") {
+    Kind k = kind_from_name(op_name);
+    NodeKind nk = program_node_kind(k);
+    if (k == Kind::unsupported || nk != NodeKind::elementwise) return false;
+  }
+  std::lock_guard<std::mutex> lock(g_registry_mu);
+  g_registry[target] = CustomCallEntry{op_name, arity};
+  g_registry_version++;
+  return true;
+}
+
+void unregister_custom_call(const std::string& target) {
+  std::lock_guard<std::mutex> lock(g_registry_mu);
+  if (g_registry.erase(target)) g_registry_version++;
+}
+
+uint64_t custom_call_registry_version() {
+  std::lock_guard<std::mutex> lock(g_registry_mu);
+  return g_registry_version;
+}
+
+// ---------------------------------------------------------------------------
+// Plan rewriting and legalization.
+
+namespace {
+
+// Resolves registered custom calls into ordinary kinds so they fuse.
+Plan rewrite_plan(const Plan& plan) {
+  Plan p = plan;
+  std::lock_guard<std::mutex> lock(g_registry_mu);
+  for (Instruction& ins : p.instructions) {
+    if (ins.kind != Kind::custom_call) continue;
+    const std::string& t = ins.custom_call_target;
+    if (t == "annotate_device_placement" && ins.inputs.size() == 1 && ins.outputs.size() == 1) {
+      ins.kind = Kind::copy_arg0;
+      continue;
+    }
+    for (const char* n : kBinaryAddTargets)
+      if (t == n && ins.inputs.size() == 2) ins.kind = Kind::add;
+    auto it = g_registry.find(t);
+    if (it == g_registry.end() || ins.kind != Kind::custom_call) continue;
+    if (it->second.op_name == "identity") {
+      if (ins.inputs.size() == 1 && ins.outputs.size() == 1) ins.kind = Kind::copy_arg0;
+    } else if ((int)ins.inputs.size() == it->second.arity) {
+      ins.kind = kind_from_name(it->second.op_name);
+    }
+  }
+  return p;
+}
+
+bool mergeable(const std::vector<int64_t>& sizes, const std::vector<int64_t>& strides, int64_t* size, int64_t* stride) {
+  int64_t total = 1, last_stride = 0;
+  bool any = false;
+  for (size_t i = 0; i < sizes.size(); i++) {
+    if (sizes[i] == 1) continue;
+    if (any && last_stride != strides[i] * sizes[i]) return false;
+    any = true;
+    last_stride = strides[i];
+    total *= sizes[i];
+  }
+  *size = total;
+  *stride = any ? last_stride : 0;
+  return true;
+}
+
+std::vector<int64_t> dense_strides(const std::vector<int64_t>& dims) {
+  std::vector<int64_t> s(dims.size());
+  int64_t st = 1;
+  for (size_t d = dims.size(); d-- > 0;) {
+    s[d] = st;
+    st *= dims[d];
+  }
+  return s;
+}
+
+// Canonical contraction of a dot_general, or a reason why it has none.
+bool analyze_dot(const Plan& plan, const Instruction& ins, DotShape* out, std::string* why) {
+  const Value& lhs = plan.values[ins.inputs[0]];
+  const Value& rhs = plan.values[ins.inputs[1]];
+  const Value& res = plan.values[ins.outputs[0]];
+  if (lhs.dtype != rhs.dtype || lhs.dtype != res.dtype || !dtype_is_float(lhs.dtype)) {
+    *why = "dot_general operands and result must share one of f32, f16, bf16";
+    return false;
+  }
+  const auto& lb = ins.list("lhs_batch_dimensions");
+  const auto& rb = ins.list("rhs_batch_dimensions");
+  const auto& lc = ins.list("lhs_contracting_dimensions");
+  const auto& rc = ins.list("rhs_contracting_dimensions");
+  if (lb.size() != rb.size() || lc.size() != 1 || rc.size() != 1) {
+    *why = "dot_general needs equal batch ranks and exactly one contracting dimension";
+    return false;
+  }
+  auto valid = [](const std::vector<int64_t>& l, size_t rank) {
+    for (int64_t d : l)
+      if (d < 0 || d >= (int64_t)rank) return false;
+    return true;
+  };
+  if (!valid(lb, lhs.dims.size()) || !valid(lc, lhs.dims.size()) || !valid(rb, rhs.dims.size()) || !valid(rc, rhs.dims.size())) {
+    *why = "dot_general dimension number is out of range";
+    return false;
+  }
+  if (lhs.dims[lc[0]] != rhs.dims[rc[0]]) {
+    *why = "dot_general contracting sizes differ";
+    return false;
+  }
+  std::vector<int64_t> ls = dense_strides(lhs.dims), rs = dense_strides(rhs.dims);
+  auto is_in = [](const std::vector<int64_t>& l, int64_t d) { return std::find(l.begin(), l.end(), d) != l.end(); };
+  std::vector<int64_t> bsz, lbs, rbs, msz, mst, nsz, nst;
+  for (size_t i = 0; i < lb.size(); i++) {
+    if (lhs.dims[lb[i]] != rhs.dims[rb[i]]) {
+      *why = "dot_general batch sizes differ";
+      return false;
+    }
+    bsz.push_back(lhs.dims[lb[i]]);
+    lbs.push_back(ls[lb[i]]);
+    rbs.push_back(rs[rb[i]]);
+  }
+  for (size_t d = 0; d < lhs.dims.size(); d++)
+    if (!is_in(lb, (int64_t)d) && (int64_t)d != lc[0]) {
+      msz.push_back(lhs.dims[d]);
+      mst.push_back(ls[d]);
+    }
+  for (size_t d = 0; d < rhs.dims.size(); d++)
+    if (!is_in(rb, (int64_t)d) && (int64_t)d != rc[0]) {
+      nsz.push_back(rhs.dims[d]);
+      nst.push_back(rs[d]);
+    }
+  DotShape s;
+  s.dtype = lhs.dtype;
+  s.k = lhs.dims[lc[0]];
+  s.lhs_k = ls[lc[0]];
+  s.rhs_k = rs[rc[0]];
+  if (!mergeable(msz, mst, &s.m, &s.lhs_m) || !mergeable(nsz, nst, &s.n, &s.rhs_n)) {
+    *why = "dot_general free dimensions are not contiguous in their operand";
+    return false;
+  }
+  // Batch axes: drop size-1 axes, then merge into at most two strided axes.
+  std::vector<int64_t> b, bl, br;
+  for (size_t i = 0; i < bsz.size(); i++)
+    if (bsz[i] != 1) {
+      b.push_back(bsz[i]);
+      bl.push_back(lbs[i]);
+      br.push_back(rbs[i]);
+    }
+  for (size_t i = 0; i + 1 < b.size();) {
+    if (bl[i] == bl[i + 1] * b[i + 1] && br[i] == br[i + 1] * b[i + 1]) {
+      b[i] *= b[i + 1];
+      bl[i] = bl[i + 1];
+      br[i] = br[i + 1];
+      b.erase(b.begin() + i + 1);
+      bl.erase(bl.begin() + i + 1);
+      br.erase(br.begin() + i + 1);
+    } else {
+      i++;
+    }
+  }
+  if (b.size() > 2) {
+    *why = "dot_general has more than two independent batch strides";
+    return false;
+  }
+  if (b.size() == 2) {
+    s.b0 = b[0]; s.lhs_b0 = bl[0]; s.rhs_b0 = br[0];
+    s.b1 = b[1]; s.lhs_b1 = bl[1]; s.rhs_b1 = br[1];
+  } else if (b.size() == 1) {
+    s.b1 = b[0]; s.lhs_b1 = bl[0]; s.rhs_b1 = br[0];
+  }
+  s.out_m = s.n;
+  s.out_b1 = s.m * s.n;
+  s.out_b0 = s.b1 * s.m * s.n;
+  if (res.count() != s.b0 * s.b1 * s.m * s.n) {
+    *why = "dot_general result shape does not match its operands";
+    return false;
+  }
+  *out = s;
+  return true;
+}
+
+bool analyze_sdpa(const Plan& plan, const Instruction& ins, SdpaShape* out, std::string* why) {
+  if (ins.inputs.size() != 4 || ins.outputs.size() != 1) {
+    *why = "scaled_dot_product_attention takes q, k, v, token_index";
+    return false;
+  }
+  const Value& q = plan.values[ins.inputs[0]];
+  const Value& k = plan.values[ins.inputs[1]];
+  const Value& v = plan.values[ins.inputs[2]];
+  const Value& t = plan.values[ins.inputs[3]];
+  const Value& o = plan.values[ins.outputs[0]];
+  if (q.dtype != k.dtype || q.dtype != v.dtype || !dtype_is_float(q.dtype) || o.dtype != q.dtype || o.dims != q.dims ||
+      (q.dims.size() != 3 && q.dims.size() != 4) || k.dims.size() != q.dims.size() || k.dims != v.dims ||
+      t.count() != 1 || !dtype_is_int(t.dtype)) {
+    *why = "scaled_dot_product_attention operand types or ranks are not supported";
+    return false;
+  }
+  const bool hb = q.dims.size() == 4;
+  SdpaShape s;
+  s.dtype = q.dtype;
+  s.batch = hb ? q.dims[0] : 1;
+  s.q_len = q.dims[hb ? 1 : 0];
+  s.heads = q.dims[hb ? 2 : 1];
+  s.head_dim = q.dims[hb ? 3 : 2];
+  s.kv_len = k.dims[hb ? 1 : 0];
+  s.kv_heads = k.dims[hb ? 2 : 1];
+  s.token_dtype = t.dtype;
+  if (s.batch <= 0 || s.q_len <= 0 || s.heads <= 0 || s.kv_len <= 0 || s.kv_heads <= 0 || s.head_dim <= 0 ||
+      k.dims[hb ? 3 : 2] != s.head_dim || s.heads % s.kv_heads != 0 || (hb && k.dims[0] != s.batch)) {
+    *why = "scaled_dot_product_attention shapes are inconsistent";
+    return false;
+  }
+  *out = s;
+  return true;
+}
+
+struct Issue {
+  long instruction = -1;
+  long value = -1;
+  std::string detail;
+  std::string feature = "b200-backend-executable";
+};
+
+std::string format_issue(const Plan& plan, const Issue& is) {
+  std::string s = "invalid executable plan: pass=b200-backend-legalization";
+  if (is.instruction >= 0) {
+    s += strfmt(" instruction=%ld", is.instruction);
+    const char* n = kind_name(plan.instructions[is.instruction].kind);
+    std::string op = n;
+    while (!op.empty() && op.back() == '_') op.pop_back();
+    s += " op=" + op;
+  }
+  if (is.value >= 0 && is.value < (long)plan.values.size()) {
+    const Value& v = plan.values[is.value];
+    s += strfmt(" value=%ld dtype=%s rank=%zu shape=[", is.value, dtype_name(v.dtype), v.dims.size());
+    for (size_t d = 0; d < v.dims.size(); d++) s += strfmt(d ? ",%lld" : "%lld", (long long)v.dims[d]);
+    s += "] sharding=";
+    const char* sharding = "internal";
+    std::vector<uint32_t> params = plan.parameter_ids();
+    for (size_t p = 0; p < params.size() && p < plan.parameter_shardings.size(); p++)
+      if (params[p] == v.id) {
+        static const char* names[] = {"replicated", "partitioned", "manual"};
+        sharding = names[(int)plan.parameter_shardings[p].kind];
+      }
+    s += sharding;
+  }
+  s += " detail=\"" + is.detail + "\" feature=" + is.feature;
+  return s;
+}
+
+bool dtype_supported(int dt) {
+  switch (dt) {
+    case kPred: case kS8: case kU8: case kS16: case kU16: case kS32: case kU32: case kS64: case kU64:
+    case kF16: case kBF16: case kF32:
+      return true;
+    default:
+      return false;
+  }
+}
+
+// First reason the rewritten plan cannot run on this backend.
+bool lowering_issue(const Plan& plan, size_t device_count, Issue* out) {
+  if (device_count == 0) {
+    *out = Issue{-1, -1, "backend executable requires at least one device", "b200-device-assignment"};
+    return true;
+  }
+  for (uint32_t id : plan.output_ids)
+    if (id >= plan.values.size()) {
+      *out = Issue{-1, (long)id, "plan output value is outside the executable value table", "b200-executable-values"};
+      return true;
+    }
+  for (size_t i = 0; i < plan.instructions.size(); i++) {
+    const Instruction& ins = plan.instructions[i];
+    for (uint32_t v : ins.outputs)
+      if (!dtype_supported(plan.values[v].dtype)) {
+        *out = Issue{(long)i, (long)v, "element type is not supported by the B200 backend", "b200-element-type"};
+        return true;
+      }
+    for (uint32_t v : ins.inputs)
+      if (!dtype_supported(plan.values[v].dtype)) {
+        *out = Issue{(long)i, (long)v, "element type is not supported by the B200 backend", "b200-element-type"};
+        return true;
+      }
+    std::string why;
+    switch (ins.kind) {
+      case Kind::constant:
+        break;
+      case Kind::dot_general: {
+        DotShape s;
+        if (ins.inputs.size() != 2 || ins.outputs.size() != 1 || !analyze_dot(plan, ins, &s, &why)) {
+          *out = Issue{(long)i, (long)ins.outputs[0], why.empty() ? "malformed dot_general" : why, "b200-dot-general"};
+          return true;
+        }
+        break;
+      }
+      case Kind::dynamic_update_slice: {
+        if (ins.inputs.size() < 2 || ins.outputs.size() != 1) {
+          *out = Issue{(long)i, -1, "dynamic_update_slice needs operand, update and start indices", "b200-dynamic-update-slice"};
+          return true;
+        }
+        const Value& op = plan.values[ins.inputs[0]];
+        const Value& up = plan.values[ins.inputs[1]];
+        bool ok = op.dims.size() == up.dims.size() && op.dtype == up.dtype && ins.inputs.size() == 2 + op.dims.size() &&
+                  op.dims.size() <= 8 && plan.values[ins.outputs[0]].dims == op.dims;
+        for (size_t d = 0; ok && d < op.dims.size(); d++) {
+          ok = up.dims[d] <= op.dims[d] && plan.values[ins.inputs[2 + d]].count() == 1 &&
+               dtype_is_int(plan.values[ins.inputs[2 + d]].dtype);
+        }
+        if (!ok) {
+          *out = Issue{(long)i, (long)ins.outputs[0], "dynamic_update_slice operands are inconsistent", "b200-dynamic-update-slice"};
+          return true;
+        }
+        break;
+      }
+      case Kind::custom_call: {
+        SdpaShape s;
+        if (is_sdpa_target(ins.custom_call_target)) {
+          if (!analyze_sdpa(plan, ins, &s, &why)) {
+            *out = Issue{(long)i, -1, why, ins.custom_call_target};
+            return true;
+          }
+          break;
+        }
+        *out = Issue{(long)i, ins.outputs.empty() ? -1 : (long)ins.outputs[0], "custom call target is not registered",
+                     ins.custom_call_target.empty() ? "custom-call" : ins.custom_call_target};
+        return true;
+      }
+      case Kind::all_reduce: case Kind::all_gather:
+        if (ins.inputs.size() != 1 || ins.outputs.size() != 1) {
+          *out = Issue{(long)i, -1, "collective takes one operand", "b200-collective"};
+          return true;
+        }
+        break;
+      case Kind::gather:
+        if (!codegen_fusible(plan, ins)) {
+          *out = Issue{(long)i, (long)ins.outputs[0], "only row-lookup gathers (embedding form) are supported", "gather-form"};
+          return true;
+        }
+        break;
+      default:
+        if (!codegen_fusible(plan, ins)) {
+          *out = Issue{(long)i, ins.outputs.empty() ? -1 : (long)ins.outputs[0],
+                       "operation is not supported by the B200 backend executable", "b200-op"};
+          return true;
+        }
+    }
+  }
+  return false;
+}
+
+// ---------------------------------------------------------------------------
+// Kernel planning.
+
+struct KernelPlan {
+  Plan plan;  // rewritten
+  Program program;
+  std::vector<uint32_t> root;      // storage class representative per value
+  std::vector<Step> steps;
+  std::vector<Storage> storage;    // per value (meaningful for roots)
+  std::vector<uint32_t> params;    // parameter value ids in order
+  std::vector<size_t> constants;   // constant instruction indices in slot order
+  std::vector<uint64_t> param_slot;  // arena offset of the staging slot of a small parameter, or UINT64_MAX
+  std::vector<char> param_donated;
+  uint64_t arena_bytes = 0, scratch_bytes = 0;
+};
+
+constexpr uint64_t kAlign = 256;
+uint64_t align_up(uint64_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+bool is_alias_kind(const Instruction& ins) {
+  return (ins.kind == Kind::reshape || ins.kind == Kind::copy_arg0 ||
+          (ins.kind == Kind::optimization_barrier && ins.inputs.size() == 1)) &&
+         ins.inputs.size() == 1 && ins.outputs.size() == 1;
+}
+
+bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::string* error) {
+  kp->plan = rewrite_plan(original);
+  const Plan& plan = kp->plan;
+  std::string verr = verify_plan(plan);
+  if (!verr.empty()) {
+    *error = verr;
+    return false;
+  }
+  Issue issue;
+  if (lowering_issue(plan, 1, &issue)) {
+    *error = format_issue(plan, issue);
+    return false;
+  }
+  if (!build_program(plan, &kp->program, error)) return false;
+
+  const size_t nv = plan.values.size(), ni = plan.instructions.size();
+  kp->params = plan.parameter_ids();
+  kp->param_donated.assign(kp->params.size(), 0);
+  for (uint32_t p : plan.donated_parameter_indices)
+    if (p < kp->params.size()) kp->param_donated[p] = 1;
+  std::map<uint32_t, uint32_t> param_index;
+  for (size_t p = 0; p < kp->params.size(); p++) param_index[kp->params[p]] = (uint32_t)p;
+
+  std::vector<long> producer(nv, -1), last_read(nv, -1);
+  std::vector<std::vector<size_t>> users(nv);
+  std::vector<char> is_output(nv, 0);
+  for (uint32_t id : plan.output_ids) is_output[id] = 1;
+  for (size_t i = 0; i < ni; i++) {
+    for (uint32_t v : plan.instructions[i].inputs) {
+      users[v].push_back(i);
+      last_read[v] = (long)i;
+    }
+    for (uint32_t v : plan.instructions[i].outputs) producer[v] = (long)i;
+  }
+
+  // Storage classes: pure aliases and in-place slice updates share their operand's storage.
+  kp->root.resize(nv);
+  std::vector<long> class_last(nv, -1);
+  std::vector<char> class_output(nv, 0);
+  for (size_t v = 0; v < nv; v++) {
+    kp->root[v] = (uint32_t)v;
+    if (producer[v] < 0) {  // parameters
+      class_last[v] = last_read[v];
+      class_output[v] = is_output[v];
+    }
+  }
+  std::vector<char> dus_in_place(ni, 0);
+  for (size_t i = 0; i < ni; i++) {
+    const Instruction& ins = plan.instructions[i];
+    auto join = [&](uint32_t out, uint32_t r) {
+      kp->root[out] = r;
+      class_last[r] = std::max(class_last[r], last_read[out]);
+      class_output[r] |= is_output[out];
+    };
+    if (is_alias_kind(ins)) {
+      join(ins.outputs[0], kp->root[ins.inputs[0]]);
+      continue;
+    }
+    if (ins.kind == Kind::dynamic_update_slice) {
+      uint32_t r = kp->root[ins.inputs[0]];
+      bool storage_ok = producer[r] >= 0 ? plan.instructions[producer[r]].kind != Kind::constant
+                                         : (param_index.count(r) && kp->param_donated[param_index[r]]);
+      // The update and the start indices must not live in the operand's storage.
+      bool disjoint = true;
+      for (size_t k = 1; k < ins.inputs.size(); k++) disjoint &= kp->root[ins.inputs[k]] != r;
+      if (storage_ok && disjoint && class_last[r] <= (long)i && !class_output[r]) {
+        dus_in_place[i] = 1;
+        join(ins.outputs[0], r);
+        continue;
+      }
+    }
+    for (uint32_t o : ins.outputs) {
+      class_last[o] = last_read[o];
+      class_output[o] = is_output[o];
+    }
+  }
+
+  // Steps. Runs of fusible nodes become generated kernels (longest prefix that
+  // one kernel can express), everything else is one step per node.
+  std::vector<char> in_set(ni, 0);
+  auto stored_roots = [&](size_t a, size_t b) {  // instruction range [a, b)
+    std::vector<uint32_t> stored;
+    for (size_t i = a; i < b; i++) {
+      if (plan.instructions[i].kind == Kind::constant) continue;
+      for (uint32_t v : plan.instructions[i].outputs) {
+        bool needed = is_output[v];
+        for (size_t u : users[v]) needed |= (u < a || u >= b);
+        if (!needed) continue;
+        uint32_t r = kp->root[v];
+        if (producer[r] < (long)a || producer[r] >= (long)b) continue;  // storage owned elsewhere
+        if (std::find(stored.begin(), stored.end(), r) == stored.end()) stored.push_back(r);
+      }
+    }
+    return stored;
+  };
+  auto fusible_at = [&](size_t i) {
+    const Instruction& ins = plan.instructions[i];
+    return ins.kind == Kind::constant || codegen_fusible(plan, ins);
+  };
+
+  size_t i = 0;
+  while (i < ni) {
+    const Instruction& ins = plan.instructions[i];
+    if (ins.kind == Kind::constant) {
+      i++;
+      continue;
+    }
+    if (fusible_at(i)) {
+      size_t end = i;
+      while (end < ni && fusible_at(end)) end++;
+      size_t a = i;
+      while (a < end) {
+        size_t b = end;
+        bool placed = false;
+        std::string why;
+        for (; b > a; b--) {
+          if (plan.instructions[b - 1].kind == Kind::constant && b - 1 > a) continue;  // never end a kernel on a constant
+          std::vector<uint32_t> stored = stored_roots(a, b);
+          if (stored.empty()) {
+            placed = true;  // pure aliases: nothing to launch
+            break;
+          }
+          std::vector<size_t> nodes;
+          for (size_t n = a; n < b; n++)
+            if (plan.instructions[n].kind != Kind::constant) nodes.push_back(n);
+          Step st;
+          st.type = Step::kFused;
+          if (generate_fused_kernel(plan, nodes, stored, sm_count, &st.fused, &why)) {
+            st.nodes = nodes;
+            for (uint32_t v : st.fused.inputs) {
+              uint32_t r = kp->root[v];
+              if (std::find(st.inputs.begin(), st.inputs.end(), r) == st.inputs.end()) st.inputs.push_back(r);
+            }
+            st.outputs = stored;
+            kp->steps.push_back(std::move(st));
+            placed = true;
+            break;
+          }
+        }
+        if (!placed) {
+          Issue is{(long)a, plan.instructions[a].outputs.empty() ? -1 : (long)plan.instructions[a].outputs[0],
+                   "no kernel can be generated: " + why, "b200-fusion"};
+          *error = format_issue(plan, is);
+          return false;
+        }
+        a = b;
+      }
+      i = end;
+      continue;
+    }
+    Step st;
+    st.nodes = {i};
+    std::string why;
+    switch (ins.kind) {
+      case Kind::dot_general:
+        st.type = Step::kDot;
+        analyze_dot(plan, ins, &st.dot, &why);
+        st.dot_scratch = dot_plan(st.dot, sm_count);
+        st.inputs = {kp->root[ins.inputs[0]], kp->root[ins.inputs[1]]};
+        st.outputs = {ins.outputs[0]};
+        break;
+      case Kind::dynamic_update_slice: {
+        st.type = Step::kSliceUpdate;
+        const Value& op = plan.values[ins.inputs[0]];
+        const Value& up = plan.values[ins.inputs[1]];
+        st.dus.rank = (int)op.dims.size();
+        st.dus.elem_size = (int)dtype_size(op.dtype);
+        for (size_t d = 0; d < op.dims.size(); d++) {
+          st.dus.dst_dims[d] = op.dims[d];
+          st.dus.upd_dims[d] = up.dims[d];
+          st.dus.start_dtype[d] = plan.values[ins.inputs[2 + d]].dtype;
+        }
+        st.in_place = dus_in_place[i];
+        st.bytes = op.bytes();
+        for (uint32_t v : ins.inputs) st.inputs.push_back(kp->root[v]);
+        st.outputs = {kp->root[ins.outputs[0]]};
+        break;
+      }
+      case Kind::custom_call:
+        st.type = Step::kSdpa;
+        analyze_sdpa(plan, ins, &st.sdpa, &why);
+        for (uint32_t v : ins.inputs) st.inputs.push_back(kp->root[v]);
+        st.outputs = {ins.outputs[0]};
+        break;
+      case Kind::all_reduce: case Kind::all_gather:
+        st.type = ins.kind == Kind::all_reduce ? Step::kAllReduce : Step::kAllGather;
+        st.inputs = {kp->root[ins.inputs[0]]};
+        st.outputs = {ins.outputs[0]};
+        st.count = (uint64_t)plan.values[ins.inputs[0]].count();
+        st.dtype = plan.values[ins.inputs[0]].dtype;
+        break;
+      default:
+        *error = format_issue(plan, Issue{(long)i, -1, "operation has no kernel", "b200-op"});
+        return false;
+    }
+    kp->steps.push_back(std::move(st));
+    i++;
+  }
+
+  // Storage: parameters, constants, arena intervals for everything produced by a step.
+  kp->storage.assign(nv, Storage{});
+  for (size_t p = 0; p < kp->params.size(); p++) kp->storage[kp->params[p]] = Storage{Storage::kParameter, 0, (uint32_t)p};
+  for (size_t n = 0; n < ni; n++)
+    if (plan.instructions[n].kind == Kind::constant) {
+      kp->storage[plan.instructions[n].outputs[0]] = Storage{Storage::kConstant, 0, (uint32_t)kp->constants.size()};
+      kp->constants.push_back(n);
+    }
+  const size_t ns = kp->steps.size();
+  std::vector<long> first_write(nv, -1), last_touch(nv, -1);
+  for (size_t s = 0; s < ns; s++) {
+    for (uint32_t r : kp->steps[s].outputs) {
+      if (first_write[r] < 0) first_write[r] = (long)s;
+      last_touch[r] = (long)s;
+    }
+    for (uint32_t r : kp->steps[s].inputs) last_touch[r] = std::max(last_touch[r], (long)s);
+  }
+  for (size_t v = 0; v < nv; v++)
+    if (is_output[v]) last_touch[kp->root[v]] = (long)ns;  // lives to the end
+  // Small non-donated parameters get a staging slot so a captured graph reads a fixed address.
+  uint64_t top = 0;
+  kp->param_slot.assign(kp->params.size(), UINT64_MAX);
+  for (size_t p = 0; p < kp->params.size(); p++) {
+    const Value& v = plan.values[kp->params[p]];
+    if (!kp->param_donated[p] && v.bytes() <= 4096) {
+      kp->param_slot[p] = top;
+      top += align_up(std::max<uint64_t>(v.bytes(), 1));
+    }
+  }
+  const uint64_t slots_end = top;
+  struct Block { uint64_t offset, size; long free_after; };
+  std::vector<Block> live;
+  uint64_t high = slots_end;
+  for (size_t s = 0; s < ns; s++) {
+    for (uint32_t r : kp->steps[s].outputs) {
+      if (kp->storage[r].kind != Storage::kNone) continue;  // parameter storage (in-place update) or already placed
+      uint64_t size = align_up(std::max<uint64_t>(plan.values[r].bytes(), 1));
+      // Drop blocks whose last reader ran before this step, then first-fit.
+      live.erase(std::remove_if(live.begin(), live.end(), [&](const Block& b) { return b.free_after < (long)s; }), live.end());
+      std::sort(live.begin(), live.end(), [](const Block& a, const Block& b) { return a.offset < b.offset; });
+      uint64_t at = slots_end;
+      for (const Block& b : live) {
+        if (at + size <= b.offset) break;
+        at = std::max(at, b.offset + b.size);
+      }
+      live.push_back(Block{at, size, last_touch[r]});
+      high = std::max(high, at + size);
+      kp->storage[r] = Storage{Storage::kArena, at, 0};
+    }
+  }
+  kp->arena_bytes = high;
+  // Scratch for split-K partials and their counters (counters first: they must start at zero).
+  uint64_t scratch = 0;
+  for (Step& st : kp->steps)
+    if (st.type == Step::kDot && st.dot_scratch.ksplit > 1) {
+      st.counter_offset = scratch;
+      scratch += align_up(st.dot_scratch.counter_bytes);
+    }
+  uint64_t counters_end = scratch;
+  uint64_t partial_max = 0;
+  for (Step& st : kp->steps)
+    if (st.type == Step::kDot && st.dot_scratch.ksplit > 1) {
+      st.scratch_offset = counters_end;  // partials are consumed inside the launch that wrote them: one shared region
+      partial_max = std::max(partial_max, align_up(st.dot_scratch.partial_bytes));
+    }
+  kp->scratch_bytes = counters_end + partial_max;
+  return true;
+}
+
+std::string step_type_name(Step::Type t) {
+  static const char* names[] = {"fused", "dot", "slice_update", "sdpa", "all_reduce", "all_gather", "copy"};
+  return names[(int)t];
+}
+
+std::string describe_steps(const KernelPlan& kp, bool with_source) {
+  std::string s = strfmt("{\"arena_bytes\":%llu,\"scratch_bytes\":%llu,\"steps\":[", (unsigned long long)kp.arena_bytes,
+                         (unsigned long long)kp.scratch_bytes);
+  for (size_t i = 0; i < kp.steps.size(); i++) {
+    const Step& st = kp.steps[i];
+    s += strfmt("%s{\"type\":\"%s\",\"nodes\":[", i ? "," : "", step_type_name(st.type).c_str());
+    for (size_t n = 0; n < st.nodes.size(); n++) s += strfmt(n ? ",%zu" : "%zu", st.nodes[n]);
+    s += "]";
+    if (st.type == Step::kFused) {
+      s += strfmt(",\"row\":%s,\"rows\":%lld,\"cols\":%lld,\"n\":%lld,\"vec\":%d,\"block\":%d,\"grid\":%lld,\"stages\":%d,"
+                  "\"reduces\":%d,\"inputs\":%zu,\"outputs\":%zu",
+                  st.fused.row ? "true" : "false", (long long)st.fused.rows, (long long)st.fused.cols, (long long)st.fused.n,
+                  st.fused.vec, st.fused.block, (long long)st.fused.grid, st.fused.stages, st.fused.reduce_count,
+                  st.fused.inputs.size(), st.fused.outputs.size());
+      if (with_source) {
+        std::string esc;
+        for (char c : st.fused.source) {
+          if (c == '"' || c == '\\') { esc += '\\'; esc += c; }
+          else if (c == '\n') esc += "\\n";
+          else if (c == '\t') esc += "\\t";
+          else esc += c;
+        }
+        s += ",\"source\":\"" + esc + "\"";
+      }
+    } else if (st.type == Step::kDot) {
+      s += strfmt(",\"path\":%d,\"ksplit\":%d,\"b0\":%lld,\"b1\":%lld,\"m\":%lld,\"n\":%lld,\"k\":%lld", st.dot_scratch.path,
+                  st.dot_scratch.ksplit, (long long)st.dot.b0, (long long)st.dot.b1, (long long)st.dot.m, (long long)st.dot.n,
+                  (long long)st.dot.k);
+    } else if (st.type == Step::kSliceUpdate) {
+      s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");
+    }
+    s += "}";
+  }
+  return s + "]}";
+}
+
+}  // namespace
+
+std::string lowering_diagnostic(const Plan& plan, size_t device_count) {
+  Plan p = rewrite_plan(plan);
+  Issue issue;
+  if (!lowering_issue(p, device_count, &issue)) return "";
+  return format_issue(p, issue);
+}
+
+std::string describe_kernel_plan(const Plan& plan, std::string* error) {
+  KernelPlan kp;
+  if (!plan_kernels(plan, 148, &kp, error)) return "";
+  return describe_steps(kp, true);
+}
+
+// ---------------------------------------------------------------------------
+// Executable.
+
+struct DeviceState {
+  Device* dev = nullptr;
+  std::vector<void*> constants;
+  void* arena = nullptr;
+  void* scratch = nullptr;
+  cudaGraphExec_t graph = nullptr;
+  std::vector<void*> graph_param_ptrs;  // pointers the graph was captured with
+};
+
+struct Executable {
+  KernelPlan kp;
+  std::vector<int> device_ordinals;
+  std::vector<DeviceState> devices;
+  ExecutableStats stats;
+  bool use_graph = false;
+  std::mutex mu;
+};
+
+namespace {
+
+bool env_flag(const char* name, bool fallback) {
+  const char* v = getenv(name);
+  if (!v || !*v) return fallback;
+  return !(v[0] == '0' || v[0] == 'f' || v[0] == 'F' || v[0] == 'n' || v[0] == 'N');
+}
+
+bool profile_enabled() {
+  static int on = -1;
+  if (on < 0) on = env_flag("PJRTX_PROFILE", false) ? 1 : 0;
+  return on == 1;
+}
+
+struct Pointers {
+  const KernelPlan* kp;
+  const DeviceState* ds;
+  const std::vector<void*>* param_ptrs;
+  std::vector<void*> fresh;  // per value, outputs allocated outside the arena (direct mode)
+  void* of(uint32_t value) const {
+    uint32_t r = kp->root[value];
+    const Storage& st = kp->storage[r];
+    switch (st.kind) {
+      case Storage::kParameter: return (*param_ptrs)[st.index];
+      case Storage::kConstant: return ds->constants[st.index];
+      case Storage::kArena:
+        if (!fresh.empty() && fresh[r]) return fresh[r];
+        return (char*)ds->arena + st.offset;
+      default: return nullptr;
+    }
+  }
+};
+
+bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* launches, std::string* error) {
+  Device* dev = ds.dev;
+  const KernelPlan& kp = exe->kp;
+  for (const Step& st : kp.steps) {
+    switch (st.type) {
+      case Step::kFused: {
+        std::vector<void*> addr;
+        for (uint32_t v : st.fused.inputs) addr.push_back(ptr.of(v));
+        for (uint32_t v : st.fused.outputs) addr.push_back(ptr.of(v));
+        std::vector<void*> args(addr.size());
+        for (size_t k = 0; k < addr.size(); k++) args[k] = &addr[k];
+        cudaError_t e = cudaLaunchKernel((const void*)st.jit->kernel, dim3((unsigned)st.fused.grid), dim3((unsigned)st.fused.block),
+                                         args.data(), 0, dev->stream);
+        if (e != cudaSuccess) {
+          *error = std::string("fused kernel launch failed: ") + cudaGetErrorString(e);
+          return false;
+        }
+        (*launches)++;
+        break;
+      }
+      case Step::kDot: {
+        void* partials = st.dot_scratch.ksplit > 1 ? (char*)ds.scratch + st.scratch_offset : nullptr;
+        void* counters = st.dot_scratch.ksplit > 1 ? (char*)ds.scratch + st.counter_offset : nullptr;
+        int n = dot_launch(st.dot, st.dot_scratch, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.outputs[0]), partials,
+                           counters, dev->stream);
+        if (n == 0) {
+          *error = "dot_general kernel refused the shape";
+          return false;
+        }
+        *launches += n;
+        break;
+      }
+      case Step::kSliceUpdate: {
+        void* dst = ptr.of(st.outputs[0]);
+        if (!st.in_place) {
+          if (cudaMemcpyAsync(dst, ptr.of(st.inputs[0]), st.bytes, cudaMemcpyDeviceToDevice, dev->stream) != cudaSuccess) {
+            *error = "dynamic_update_slice operand copy failed";
+            return false;
+          }
+          (*launches)++;
+        }
+        const void* starts[8] = {nullptr};
+        for (int d = 0; d < st.dus.rank; d++) starts[d] = ptr.of(st.inputs[2 + d]);
+        if (!dus_launch(st.dus, dst, ptr.of(st.inputs[1]), starts, dev->stream)) {
+          *error = "dynamic_update_slice kernel refused the shape";
+          return false;
+        }
+        (*launches)++;
+        break;
+      }
+      case Step::kSdpa:
+        if (!sdpa_launch(st.sdpa, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]), ptr.of(st.inputs[3]),
+                         ptr.of(st.outputs[0]), dev->stream)) {
+          *error = "attention kernel refused the shape";
+          return false;
+        }
+        (*launches)++;
+        break;
+      case Step::kAllReduce:
+        if (!comm_all_reduce_sum(dev, ptr.of(st.inputs[0]), ptr.of(st.outputs[0]), st.count, st.dtype)) {
+          *error = last_error();
+          return false;
+        }
+        (*launches)++;
+        break;
+      case Step::kAllGather:
+        if (!comm_all_gather(dev, ptr.of(st.inputs[0]), ptr.of(st.outputs[0]), st.count, st.dtype)) {
+          *error = last_error();
+          return false;
+        }
+        (*launches)++;
+        break;
+      case Step::kCopy:
+        break;
+    }
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    *error = std::string("kernel launch failed: ") + cudaGetErrorString(e);
+    return false;
+  }
+  return true;
+}
+
+}  // namespace
+
+Executable* compile_executable(const Plan& plan, const std::vector<int>& device_ordinals, std::string* error) {
+  if (device_ordinals.empty()) {
+    *error = "invalid executable plan: pass=b200-backend-legalization detail=\"backend executable requires at least one device\" "
+             "feature=b200-device-assignment";
+    return nullptr;
+  }
+  auto exe = std::make_unique<Executable>();
+  std::vector<Device*> devs;
+  for (int ord : device_ordinals) {
+    Device* d = get_device(ord);
+    if (!d) {
+      *error = last_error();
+      return nullptr;
+    }
+    devs.push_back(d);
+  }
+  if (!plan_kernels(plan, devs[0]->sm_count, &exe->kp, error)) return nullptr;
+  KernelPlan& kp = exe->kp;
+  exe->device_ordinals = device_ordinals;
+  // Generated kernels: compile once per distinct source.
+  uint64_t generated = 0;
+  for (Step& st : kp.steps) {
+    if (st.type != Step::kFused) continue;
+    std::string log;
+    st.jit = jit_get_kernel(st.fused.source, st.fused.name.c_str(), &log);
+    if (!st.jit) {
+      *error = "generated fusion kernel failed to compile: " + log;
+      return nullptr;
+    }
+    generated++;
+  }
+  // Resident constants, arena and scratch per device.
+  uint64_t const_bytes = 0;
+  for (Device* d : devs) {
+    DeviceState ds;
+    ds.dev = d;
+    cudaSetDevice(d->ordinal);
+    const_bytes = 0;
+    for (size_t n : kp.constants) {
+      const Instruction& ins = kp.plan.instructions[n];
+      void* p = device_malloc(d, ins.literal.size());
+      if (!p) {
+        *error = last_error();
+        return nullptr;
+      }
+      if (!ins.literal.empty() &&
+          !check_cuda(cudaMemcpyAsync(p, ins.literal.data(), ins.literal.size(), cudaMemcpyHostToDevice, d->stream), "constant upload")) {
+        *error = last_error();
+        return nullptr;
+      }
+      ds.constants.push_back(p);
+      const_bytes += ins.literal.size();
+    }
+    ds.arena = device_malloc(d, kp.arena_bytes);
+    ds.scratch = device_malloc(d, kp.scratch_bytes);
+    if (!ds.arena || !ds.scratch) {
+      *error = last_error();
+      return nullptr;
+    }
+    cudaMemsetAsync(ds.scratch, 0, std::max<uint64_t>(kp.scratch_bytes, 1), d->stream);
+    if (!check_cuda(cudaStreamSynchronize(d->stream), "compile synchronize")) {
+      *error = last_error();
+      return nullptr;
+    }
+    exe->devices.push_back(std::move(ds));
+  }
+  exe->use_graph = env_flag("PJRTX_B200_GRAPH", true) && kp.steps.size() >= 4;
+  ExecutableStats& s = exe->stats;
+  s.resident_constant_count = kp.constants.size();
+  s.resident_constant_bytes = const_bytes;
+  s.program_value_count = kp.program.values.size();
+  s.program_node_count = kp.program.nodes.size();
+  s.program_edge_count = kp.program.edges.size();
+  s.program_schedule_item_count = kp.program.schedule.size();
+  s.program_fusion_group_count = kp.program.fusion_groups.size();
+  s.program_materialization_boundary_count = kp.program.materialization_boundaries.size();
+  s.program_planned_release_count = kp.program.liveness.planned_release_count;
+  s.program_planned_release_bytes = kp.program.liveness.planned_release_bytes;
+  s.program_peak_live_value_count = kp.program.liveness.peak_live_value_count;
+  s.program_peak_live_bytes = kp.program.liveness.peak_live_bytes;
+  s.program_device_count = device_ordinals.size();
+  s.kernel_step_count = kp.steps.size();
+  s.generated_kernel_count = generated;
+  s.arena_bytes = kp.arena_bytes;
+  s.scratch_bytes = kp.scratch_bytes;
+  return exe.release();
+}
+
+bool execute_executable(Executable* exe, size_t device_index, Buffer* const* args, size_t nargs,
+                        std::vector<Buffer*>* outputs, std::string* error) {
+  auto t0 = std::chrono::steady_clock::now();
+  if (!exe) {
+    *error = "null executable";
+    return false;
+  }
+  const KernelPlan& kp = exe->kp;
+  const Plan& plan = kp.plan;
+  if (device_index >= exe->devices.size()) {
+    *error = strfmt("device index %zu is outside the executable's %zu devices", device_index, exe->devices.size());
+    return false;
+  }
+  if (nargs != kp.params.size()) {
+    *error = strfmt("executable takes %zu arguments, got %zu", kp.params.size(), nargs);
+    return false;
+  }
+  DeviceState& ds = exe->devices[device_index];
+  Device* dev = ds.dev;
+  for (size_t p = 0; p < nargs; p++) {
+    const Value& v = plan.values[kp.params[p]];
+    Buffer* b = args[p];
+    if (!b || b->donated || !b->ptr) {
+      *error = strfmt("argument %zu is null, deleted or donated", p);
+      return false;
+    }
+    if (b->device != dev->ordinal) {
+      *error = strfmt("argument %zu lives on device %d, executable runs on device %d", p, b->device, dev->ordinal);
+      return false;
+    }
+    if (b->dtype != v.dtype || b->dims != v.dims) {
+      *error = strfmt("argument %zu does not match the parameter descriptor (%s)", p, dtype_name(v.dtype));
+      return false;
+    }
+    for (size_t q = 0; q < p; q++)
+      if (args[q] == b && (kp.param_donated[p] || kp.param_donated[q])) {
+        *error = strfmt("donated argument %zu is passed twice", p);
+        return false;
+      }
+  }
+  std::lock_guard<std::mutex> lock(exe->mu);
+  cudaSetDevice(dev->ordinal);
+  std::vector<void*> param_ptrs(nargs);
+  for (size_t p = 0; p < nargs; p++) param_ptrs[p] = args[p]->ptr;
+
+  uint64_t launches = 0;
+  Pointers ptr{&kp, &ds, &param_ptrs, {}};
+  std::vector<Buffer*> outs(plan.output_ids.size(), nullptr);
+  auto cleanup = [&]() {
+    for (Buffer* b : outs)
+      if (b) buffer_free(b);
+  };
+
+  if (exe->use_graph) {
+    // Small parameters are staged into fixed slots; the graph reads the slots.
+    std::vector<void*> graph_ptrs = param_ptrs;
+    uint64_t dynamic_inputs = 0;
+    for (size_t p = 0; p < nargs; p++)
+      if (kp.param_slot[p] != UINT64_MAX) {
+        void* slot = (char*)ds.arena + kp.param_slot[p];
+        if (args[p]->bytes &&
+            !check_cuda(cudaMemcpyAsync(slot, args[p]->ptr, args[p]->bytes, cudaMemcpyDeviceToDevice, dev->stream), "stage argument")) {
+          *error = last_error();
+          return false;
+        }
+        graph_ptrs[p] = slot;
+        dynamic_inputs++;
+      }
+    if (!ds.graph || ds.graph_param_ptrs != graph_ptrs) {
+      if (ds.graph) {
+        cudaGraphExecDestroy(ds.graph);
+        ds.graph = nullptr;
+      }
+      Pointers gp{&kp, &ds, &graph_ptrs, {}};
+      cudaGraph_t graph = nullptr;
+      if (!check_cuda(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) {
+        *error = last_error();
+        return false;
+      }
+      uint64_t captured = 0;
+      std::string run_error;
+      bool ok = run_steps(exe, ds, gp, &captured, &run_error);
+      cudaError_t ce = cudaStreamEndCapture(dev->stream, &graph);
+      if (!ok || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        *error = ok ? std::string("graph capture failed: ") + cudaGetErrorString(ce) : run_error;
+        cudaGetLastError();
+        return false;
+      }
+      ce = cudaGraphInstantiate(&ds.graph, graph, 0);
+      cudaGraphDestroy(graph);
+      if (ce != cudaSuccess) {
+        *error = std::string("graph instantiate failed: ") + cudaGetErrorString(ce);
+        ds.graph = nullptr;
+        return false;
+      }
+      ds.graph_param_ptrs = graph_ptrs;
+      exe->stats.graph_capture_count++;
+    }
+    if (!check_cuda(cudaGraphLaunch(ds.graph, dev->stream), "graph launch")) {
+      *error = last_error();
+      return false;
+    }
+    launches = kp.steps.size();
+    exe->stats.graph_launch_count++;
+    exe->stats.captured_program_execute_count++;
+    exe->stats.captured_program_dynamic_input_count = dynamic_inputs;
+    exe->stats.captured_program_captured_input_count = nargs - dynamic_inputs;
+    ptr.param_ptrs = &param_ptrs;
+  } else {
+    // Direct mode: program outputs are written straight into fresh buffers.
+    ptr.fresh.assign(plan.values.size(), nullptr);
+    for (size_t o = 0; o < plan.output_ids.size(); o++) {
+      uint32_t r = kp.root[plan.output_ids[o]];
+      if (kp.storage[r].kind != Storage::kArena || ptr.fresh[r]) continue;
+      const Value& rv = plan.values[r];
+      Buffer* b = buffer_alloc(dev, rv.dtype, rv.dims, false);
+      if (!b) {
+        *error = last_error();
+        cleanup();
+        return false;
+      }
+      ptr.fresh[r] = b->ptr;
+      outs[o] = b;
+    }
+    if (!run_steps(exe, ds, ptr, &launches, error)) {
+      cleanup();
+      return false;
+    }
+  }
+
+  // Wrap outputs.
+  std::vector<char> param_taken(nargs, 0);
+  for (size_t o = 0; o < plan.output_ids.size(); o++) {
+    const Value& ov = plan.values[plan.output_ids[o]];
+    uint32_t r = kp.root[ov.id];
+    const Storage& st = kp.storage[r];
+    if (outs[o]) {  // direct mode fresh buffer; give it the output's own dims
+      outs[o]->dims = ov.dims;
+      outs[o]->dtype = ov.dtype;
+      continue;
+    }
+    if (st.kind == Storage::kParameter && kp.param_donated[st.index] && !param_taken[st.index]) {
+      // Donation: the output takes over the argument's storage (src/backend/mlx_metal/api.cc:5474-5478).
+      Buffer* in = args[st.index];
+      Buffer* b = new Buffer();
+      b->device = in->device;
+      b->dtype = ov.dtype;
+      b->dims = ov.dims;
+      b->ptr = in->ptr;
+      b->bytes = in->bytes;
+      b->owns = in->owns;
+      in->donated = true;
+      in->ptr = nullptr;
+      param_taken[st.index] = 1;
+      outs[o] = b;
+      exe->stats.donation_alias_output_count++;
+      exe->stats.donation_alias_output_bytes += b->bytes;
+      continue;
+    }
+    Buffer* b = buffer_alloc(dev, ov.dtype, ov.dims, false);
+    if (!b) {
+      *error = last_error();
+      cleanup();
+      return false;
+    }
+    const void* src = st.kind == Storage::kParameter && param_taken[st.index] ? nullptr : ptr.of(ov.id);
+    if (st.kind == Storage::kParameter && param_taken[st.index]) {
+      // A second output aliasing an already transferred argument: copy from the first one.
+      for (size_t q = 0; q < o; q++)
+        if (kp.root[plan.output_ids[q]] == r) src = outs[q]->ptr;
+    }
+    if (b->bytes && src &&
+        !check_cuda(cudaMemcpyAsync(b->ptr, src, b->bytes, cudaMemcpyDeviceToDevice, dev->stream), "output copy")) {
+      *error = last_error();
+      buffer_free(b);
+      cleanup();
+      return false;
+    }
+    outs[o] = b;
+  }
+  *outputs = outs;
+
+  ExecutableStats& s = exe->stats;
+  s.execute_count++;
+  s.last_execute_device_index = device_index;
+  s.last_execute_local_hardware_id = dev->ordinal;
+  s.compiled_program_execute_count++;
+  s.compiled_program_output_count += outs.size();
+  s.kernel_launch_total += launches;
+  for (const Step& st : kp.steps)
+    if (st.type == Step::kFused) s.fusion_group_execute_count++;
+  uint64_t us = (uint64_t)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+  s.execute_wall_us_total += us;
+  s.execute_wall_us_peak = std::max(s.execute_wall_us_peak, us);
+  if (profile_enabled())
+    fprintf(stderr,
+            "pjrtx_profile event=backend_execute device_index=%zu local_hardware_id=%d inputs=%zu outputs=%zu kernel_steps=%zu "
+            "graph=%d host_enqueue_us=%llu\n",
+            device_index, dev->ordinal, nargs, outs.size(), kp.steps.size(), exe->use_graph ? 1 : 0, (unsigned long long)us);
+  return true;
+}
+
+ExecutableStats executable_stats(Executable* exe) {
+  std::lock_guard<std::mutex> lock(exe->mu);
+  return exe->stats;
+}
+
+std::string executable_describe(Executable* exe) {
+  return "{\"program\":" + describe_program(exe->kp.program) + ",\"kernel_plan\":" + describe_steps(exe->kp, false) + "}";
+}
+
+void destroy_executable(Executable* exe) {
+  if (!exe) return;
+  for (DeviceState& ds : exe->devices) {
+    cudaSetDevice(ds.dev->ordinal);
+    if (ds.graph) cudaGraphExecDestroy(ds.graph);
+    for (size_t k = 0; k < ds.constants.size(); k++)
+      device_free(ds.dev, ds.constants[k], exe->kp.plan.instructions[exe->kp.constants[k]].literal.size());
+    device_free(ds.dev, ds.arena, exe->kp.arena_bytes);
+    device_free(ds.dev, ds.scratch, exe->kp.scratch_bytes);
+  }
+  delete exe;
+}
+
+}  // namespace pjrtx

@@ -1,0 +1,99 @@
+// Compiled executable: legalization, kernel planning and per-step execution.
+//
+// Mirrors the reference's compile → execute pair
+//   src/backend/mlx_metal/executable_compile.zig:17-108   (legalize, build program, upload constants)
+//   src/backend/mlx_metal/execution_call.zig:66-145        (argument checks, run schedule, wrap outputs)
+//   src/backend/mlx_metal/executable_stats.zig:6-56        (counters)
+// with a different execution strategy: the schedule is lowered once, at compile
+// time, into a list of kernel steps (generated fusion kernels, streaming /
+// tiled contractions, in-place slice updates, attention, collectives) whose
+// intermediates live in one liveness-planned arena, and the whole step list is
+// replayed as a CUDA graph.
+#pragma once
+
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "codegen.h"
+#include "device.h"
+#include "kernels/kernels.h"
+#include "plan.h"
+#include "program.h"
+
+namespace pjrtx {
+
+struct ExecutableStats {
+  uint64_t resident_constant_count = 0, resident_constant_bytes = 0;
+  uint64_t program_value_count = 0, program_node_count = 0, program_edge_count = 0;
+  uint64_t program_schedule_item_count = 0, program_subprogram_count = 0, program_control_flow_count = 0;
+  uint64_t program_fusion_group_count = 0, program_materialization_boundary_count = 0;
+  uint64_t program_planned_release_count = 0, program_planned_release_bytes = 0;
+  uint64_t program_peak_live_value_count = 0, program_peak_live_bytes = 0;
+  uint64_t program_device_count = 0;
+  uint64_t last_execute_device_index = UINT64_MAX;
+  int32_t last_execute_local_hardware_id = -1;
+  uint64_t execute_count = 0;
+  uint64_t compiled_program_execute_count = 0, compiled_program_output_count = 0;
+  uint64_t captured_program_execute_count = 0, captured_program_dynamic_input_count = 0;
+  uint64_t captured_program_captured_input_count = 0;
+  uint64_t donation_alias_output_count = 0, donation_alias_output_bytes = 0;
+  uint64_t fusion_group_execute_count = 0;
+  uint64_t execute_wall_us_total = 0, execute_wall_us_peak = 0;
+  // Additions describing the kernel plan.
+  uint64_t kernel_step_count = 0;        // launches per execute
+  uint64_t generated_kernel_count = 0;   // fusion kernels compiled
+  uint64_t arena_bytes = 0, scratch_bytes = 0;
+  uint64_t graph_capture_count = 0, graph_launch_count = 0;
+  uint64_t kernel_launch_total = 0;      // kernels enqueued since compile
+};
+
+struct Step {
+  enum Type { kFused, kDot, kSliceUpdate, kSdpa, kAllReduce, kAllGather, kCopy } type = kFused;
+  std::vector<size_t> nodes;        // plan instructions this step covers
+  std::vector<uint32_t> inputs;     // root values read
+  std::vector<uint32_t> outputs;    // root values written
+  FusedKernel fused;
+  JitKernel* jit = nullptr;
+  DotShape dot;
+  DotScratch dot_scratch;
+  uint64_t scratch_offset = 0, counter_offset = 0;
+  SliceUpdateShape dus;
+  bool in_place = false;
+  SdpaShape sdpa;
+  uint64_t bytes = 0;  // kCopy / collectives
+  uint64_t count = 0;
+  int dtype = 0;
+};
+
+struct Storage {
+  enum Kind { kNone, kParameter, kConstant, kArena, kFresh } kind = kNone;
+  uint64_t offset = 0;      // arena
+  uint32_t index = 0;       // parameter index / constant slot
+};
+
+struct Executable;
+
+// Runs legalization only; "" when the plan can be compiled, otherwise one line
+//   invalid executable plan: pass=b200-backend-legalization [instruction=N] [op=<kind>] ... detail="..." feature=<label>
+// (format of src/backend/mlx_metal/lowering_diagnostic.zig:31-45).
+std::string lowering_diagnostic(const Plan& plan, size_t device_count);
+
+// Kernel plan without touching a device: used by the introspection entry point.
+std::string describe_kernel_plan(const Plan& plan, std::string* error);
+
+Executable* compile_executable(const Plan& plan, const std::vector<int>& device_ordinals, std::string* error);
+bool execute_executable(Executable* exe, size_t device_index, Buffer* const* args, size_t nargs,
+                        std::vector<Buffer*>* outputs, std::string* error);
+ExecutableStats executable_stats(Executable* exe);
+std::string executable_describe(Executable* exe);
+void destroy_executable(Executable* exe);
+
+// Custom-call registry (src/backend/mlx_metal/custom_call.zig): named targets
+// that lower to an elementwise kind or to identity.
+bool register_custom_call(const std::string& target, const std::string& op_name, int arity);
+void unregister_custom_call(const std::string& target);
+uint64_t custom_call_registry_version();
+
+}  // namespace pjrtx

@@ -1,0 +1,395 @@
+// dot_general kernels for sm_100a.
+//
+// Four paths behind one canonical contraction out[b0,b1,m,n] = sum_k lhs*rhs
+// (the reference reaches MLX matmul/tensordot for the same op,
+// src/backend/mlx_metal/api.cc:3349-3498; its generated kernels are the
+// one-thread-per-output and 256-thread tiled dots of
+// src/backend/mlx_metal/metal_graph_dot.zig:46-64 and :199-256):
+//   1  stream_kn : m <= 8, rhs[K,N] with N contiguous. Bandwidth-bound GEMV /
+//                  skinny GEMM: 16-byte loads of rhs rows, f32 accumulators in
+//                  registers, K split over warps and CTAs, deterministic
+//                  last-CTA fold of the f32 partials.
+//   2  stream_nk : m <= 8, rhs[N,K] with K contiguous (attention scores, tied
+//                  heads): lane groups own output columns and shuffle-reduce.
+//   3  tile      : shared-memory tiled FFMA contraction with f32 accumulate,
+//                  any strides (f32 matmul at 1e-5 needs real FFMA, not TF32).
+//   0  generic   : one thread per output element, any strides, any m.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../common.h"
+#include "kernels.h"
+
+namespace pjrtx {
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Sixteen bytes of T held in registers; get(i) unpacks without taking an address
+// so the value never leaves the register file.
+__device__ __forceinline__ unsigned word_of(const uint4& r, int i) { return i == 0 ? r.x : i == 1 ? r.y : i == 2 ? r.z : r.w; }
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  uint4 raw;
+  __device__ __forceinline__ float get(int i) const { return __uint_as_float(word_of(raw, i)); }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ __forceinline__ float get(int i) const {
+    const unsigned u = word_of(raw, i >> 1);
+    return __uint_as_float((i & 1) ? (u & 0xffff0000u) : (u << 16));
+  }
+};
+template <> struct Vec16<__half> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ __forceinline__ float get(int i) const {
+    const unsigned u = word_of(raw, i >> 1);
+    return __half2float(__ushort_as_half((unsigned short)((i & 1) ? (u >> 16) : (u & 0xffffu))));
+  }
+};
+
+// Streaming 16-byte load that does not pollute L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// ---------------------------------------------------------------- generic
+template <typename T>
+__global__ void dot_generic_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out) {
+  const int64_t total = s.b0 * s.b1 * s.m * s.n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t n = i % s.n, m = (i / s.n) % s.m, b1 = (i / (s.n * s.m)) % s.b1, b0 = i / (s.n * s.m * s.b1);
+    const T* a = lhs + b0 * s.lhs_b0 + b1 * s.lhs_b1 + m * s.lhs_m;
+    const T* b = rhs + b0 * s.rhs_b0 + b1 * s.rhs_b1 + n * s.rhs_n;
+    float acc = 0.f;
+    for (int64_t k = 0; k < s.k; k++) acc = fmaf(to_f(a[k * s.lhs_k]), to_f(b[k * s.rhs_k]), acc);
+    out[b0 * s.out_b0 + b1 * s.out_b1 + m * s.out_m + n] = from_f<T>(acc);
+  }
+}
+
+// ---------------------------------------------------------------- stream_kn
+constexpr int kKnWarps = 4;
+constexpr int kKnThreads = kKnWarps * 32;
+constexpr int kKnUnroll = 8;
+
+template <typename T, int M>
+__global__ void __launch_bounds__(kKnThreads)
+stream_kn_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out,
+                 float* __restrict__ partials, unsigned* __restrict__ counters, int ksplit, int kslice) {
+  constexpr int V = Vec16<T>::N;
+  constexpr int TILE = 32 * V;
+  __shared__ float red[kKnWarps - 1][M][TILE];
+  __shared__ T xs[M][1024];
+  __shared__ int is_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t batch = blockIdx.z, b0 = batch / s.b1, b1 = batch % s.b1;
+  const int64_t col = (int64_t)blockIdx.x * TILE + lane * V;
+  const int64_t k_begin = (int64_t)blockIdx.y * kslice;
+  const int64_t k_end = min(k_begin + (int64_t)kslice, s.k);
+  const T* a = lhs + b0 * s.lhs_b0 + b1 * s.lhs_b1;
+  const T* b = rhs + b0 * s.rhs_b0 + b1 * s.rhs_b1;
+  const int rows = (int)min((int64_t)M, s.m);
+
+  float acc[M][V];
+#pragma unroll
+  for (int m = 0; m < M; m++)
+#pragma unroll
+    for (int v = 0; v < V; v++) acc[m][v] = 0.f;
+
+  const bool col_ok = col < s.n;
+  for (int64_t kc = k_begin; kc < k_end; kc += 1024) {
+    const int chunk = (int)min((int64_t)1024, k_end - kc);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * chunk; idx += kKnThreads) {
+      const int m = idx / chunk, kk = idx % chunk;
+      xs[m][kk] = a[m * s.lhs_m + (kc + kk) * s.lhs_k];
+    }
+    __syncthreads();
+    if (col_ok) {
+      const T* bp = b + (kc + warp) * s.rhs_k + col;
+      int kk = warp;
+      for (; kk + (kKnUnroll - 1) * kKnWarps < chunk; kk += kKnUnroll * kKnWarps) {
+        Vec16<T> w[kKnUnroll];
+#pragma unroll
+        for (int u = 0; u < kKnUnroll; u++) w[u].raw = ld_stream(bp + (int64_t)u * kKnWarps * s.rhs_k);
+        bp += (int64_t)kKnUnroll * kKnWarps * s.rhs_k;
+#pragma unroll
+        for (int u = 0; u < kKnUnroll; u++)
+#pragma unroll
+          for (int m = 0; m < M; m++) {
+            const float x = to_f(xs[m][kk + u * kKnWarps]);
+#pragma unroll
+            for (int v = 0; v < V; v++) acc[m][v] = fmaf(x, w[u].get(v), acc[m][v]);
+          }
+      }
+      for (; kk < chunk; kk += kKnWarps) {
+        Vec16<T> w;
+        w.raw = ld_stream(bp);
+        bp += (int64_t)kKnWarps * s.rhs_k;
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+          const float x = to_f(xs[m][kk]);
+#pragma unroll
+          for (int v = 0; v < V; v++) acc[m][v] = fmaf(x, w.get(v), acc[m][v]);
+        }
+      }
+    }
+  }
+  // Fold the warps of this CTA in a fixed order.
+  if (warp > 0) {
+#pragma unroll
+    for (int m = 0; m < M; m++)
+#pragma unroll
+      for (int v = 0; v < V; v++) red[warp - 1][m][lane * V + v] = acc[m][v];
+  }
+  __syncthreads();
+  if (warp == 0 && col_ok) {
+#pragma unroll
+    for (int m = 0; m < M; m++)
+#pragma unroll
+      for (int v = 0; v < V; v++) {
+        float t = acc[m][v];
+#pragma unroll
+        for (int w = 0; w < kKnWarps - 1; w++) t += red[w][m][lane * V + v];
+        acc[m][v] = t;
+      }
+    if (ksplit == 1) {
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        if (m < rows) {
+          T* o = out + b0 * s.out_b0 + b1 * s.out_b1 + m * s.out_m + col;
+#pragma unroll
+          for (int v = 0; v < V; v++) o[v] = from_f<T>(acc[m][v]);
+        }
+      }
+    } else {
+      float* p = partials + ((batch * ksplit + blockIdx.y) * (int64_t)M) * s.n + col;
+#pragma unroll
+      for (int m = 0; m < M; m++)
+        if (m < rows) {
+#pragma unroll
+          for (int v = 0; v < V; v++) p[(int64_t)m * s.n + v] = acc[m][v];
+        }
+    }
+  }
+  if (ksplit == 1) return;
+  // The CTA that arrives last for this column tile folds the partials in slice order.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&counters[batch * gridDim.x + blockIdx.x], 1u);
+    is_last = prev == (unsigned)ksplit - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < rows * TILE; idx += kKnThreads) {
+    const int m = idx / TILE;
+    const int64_t c = (int64_t)blockIdx.x * TILE + idx % TILE;
+    if (c >= s.n) continue;
+    float t = 0.f;
+    for (int ks = 0; ks < ksplit; ks++) t += __ldcg(partials + ((batch * ksplit + ks) * (int64_t)M + m) * s.n + c);
+    out[b0 * s.out_b0 + b1 * s.out_b1 + m * s.out_m + c] = from_f<T>(t);
+  }
+  if (threadIdx.x == 0) counters[batch * gridDim.x + blockIdx.x] = 0;  // ready for the next launch
+}
+
+// ---------------------------------------------------------------- stream_nk
+template <typename T, int M>
+__global__ void __launch_bounds__(256)
+stream_nk_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out, int group) {
+  constexpr int V = Vec16<T>::N;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rows_per_warp = 32 / group;
+  const int64_t batch = blockIdx.y, b0 = batch / s.b1, b1 = batch % s.b1;
+  const int64_t n = ((int64_t)blockIdx.x * 8 + warp) * rows_per_warp + lane / group;
+  const int gl = lane % group;
+  const T* a = lhs + b0 * s.lhs_b0 + b1 * s.lhs_b1;
+  const T* b = rhs + b0 * s.rhs_b0 + b1 * s.rhs_b1 + n * s.rhs_n;
+  const int rows = (int)min((int64_t)M, s.m);
+  float acc[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) acc[m] = 0.f;
+  if (n < s.n) {
+    for (int64_t k = (int64_t)gl * V; k < s.k; k += (int64_t)group * V) {
+      Vec16<T> w;
+      w.raw = ld_stream(b + k);
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        if (m < rows) {
+          Vec16<T> x;
+          x.raw = __ldg(reinterpret_cast<const uint4*>(a + m * s.lhs_m + k));
+#pragma unroll
+          for (int v = 0; v < V; v++) acc[m] = fmaf(x.get(v), w.get(v), acc[m]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < M; m++)
+    for (int o = group >> 1; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+  if (n < s.n && gl == 0) {
+#pragma unroll
+    for (int m = 0; m < M; m++)
+      if (m < rows) out[b0 * s.out_b0 + b1 * s.out_b1 + m * s.out_m + n] = from_f<T>(acc[m]);
+  }
+}
+
+// ---------------------------------------------------------------- tile
+constexpr int kTile = 64, kTileK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+tile_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out) {
+  __shared__ float As[kTileK][kTile + 4];
+  __shared__ float Bs[kTileK][kTile + 4];
+  const int64_t batch = blockIdx.z, b0 = batch / s.b1, b1 = batch % s.b1;
+  const T* a = lhs + b0 * s.lhs_b0 + b1 * s.lhs_b1;
+  const T* b = rhs + b0 * s.rhs_b0 + b1 * s.rhs_b1;
+  const int64_t m0 = (int64_t)blockIdx.y * kTile, n0 = (int64_t)blockIdx.x * kTile;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[4][4] = {};
+  for (int64_t k0 = 0; k0 < s.k; k0 += kTileK) {
+    for (int idx = threadIdx.x; idx < kTile * kTileK; idx += 256) {
+      // Walk the contiguous axis fastest for both operands.
+      int mm, kk;
+      if (s.lhs_k == 1) { kk = idx % kTileK; mm = idx / kTileK; } else { mm = idx % kTile; kk = idx / kTile; }
+      const int64_t gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < s.m && gk < s.k) ? to_f(a[gm * s.lhs_m + gk * s.lhs_k]) : 0.f;
+      int nn;
+      if (s.rhs_n == 1) { nn = idx % kTile; kk = idx / kTile; } else { kk = idx % kTileK; nn = idx / kTileK; }
+      const int64_t gn = n0 + nn, gk2 = k0 + kk;
+      Bs[kk][nn] = (gn < s.n && gk2 < s.k) ? to_f(b[gk2 * s.rhs_k + gn * s.rhs_n]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kTileK; kk++) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int64_t gm = m0 + ty * 4 + i;
+    if (gm >= s.m) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int64_t gn = n0 + tx * 4 + j;
+      if (gn < s.n) out[b0 * s.out_b0 + b1 * s.out_b1 + gm * s.out_m + gn] = from_f<T>(acc[i][j]);
+    }
+  }
+}
+
+template <typename T>
+int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
+                 void* counters, cudaStream_t stream) {
+  const T* a = static_cast<const T*>(lhs);
+  const T* b = static_cast<const T*>(rhs);
+  T* o = static_cast<T*>(out);
+  constexpr int V = 16 / sizeof(T);
+  const int64_t batch = s.b0 * s.b1;
+  if (plan.path == 1) {
+    const int tile = 32 * V;
+    dim3 grid((unsigned)((s.n + tile - 1) / tile), (unsigned)plan.ksplit, (unsigned)batch);
+    const int kslice = (int)((s.k + plan.ksplit - 1) / plan.ksplit);
+    float* p = static_cast<float*>(partials);
+    unsigned* c = static_cast<unsigned*>(counters);
+#define KN(MM) stream_kn_kernel<T, MM><<<grid, kKnThreads, 0, stream>>>(s, a, b, o, p, c, plan.ksplit, kslice)
+    if (s.m <= 1) KN(1); else if (s.m <= 2) KN(2); else if (s.m <= 4) KN(4); else KN(8);
+#undef KN
+    return 1;
+  }
+  if (plan.path == 2) {
+    int group = 32;
+    while (group > 1 && (int64_t)group * V > s.k) group >>= 1;
+    const int rows_per_cta = 8 * (32 / group);
+    dim3 grid((unsigned)((s.n + rows_per_cta - 1) / rows_per_cta), (unsigned)batch);
+#define NK(MM) stream_nk_kernel<T, MM><<<grid, 256, 0, stream>>>(s, a, b, o, group)
+    if (s.m <= 1) NK(1); else if (s.m <= 2) NK(2); else if (s.m <= 4) NK(4); else NK(8);
+#undef NK
+    return 1;
+  }
+  if (plan.path == 3) {
+    dim3 grid((unsigned)((s.n + kTile - 1) / kTile), (unsigned)((s.m + kTile - 1) / kTile), (unsigned)batch);
+    tile_kernel<T><<<grid, 256, 0, stream>>>(s, a, b, o);
+    return 1;
+  }
+  const int64_t total = batch * s.m * s.n;
+  const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
+  dot_generic_kernel<T><<<blocks ? blocks : 1, 256, 0, stream>>>(s, a, b, o);
+  return 1;
+}
+
+}  // namespace
+
+DotScratch dot_plan(const DotShape& s, int sm_count) {
+  DotScratch p;
+  const int esize = (int)dtype_size(s.dtype);
+  if (esize == 0 || !dtype_is_float(s.dtype)) return p;
+  const int V = 16 / esize;
+  const int64_t batch = s.b0 * s.b1;
+  auto aligned = [&](int64_t stride) { return stride % V == 0; };
+  const bool batches_fit = batch <= 65535;
+  if (s.m <= 8 && s.rhs_n == 1 && s.n % V == 0 && aligned(s.rhs_k) && aligned(s.rhs_b0) && aligned(s.rhs_b1) &&
+      batches_fit && s.k >= 1) {
+    p.path = 1;
+    const int64_t tiles = (s.n + 32 * V - 1) / (32 * V);
+    // Enough CTAs to cover every SM several times, slices of at least 64 rows.
+    int64_t want = ((int64_t)sm_count * 6 + tiles * batch - 1) / (tiles * batch);
+    int64_t max_split = std::max<int64_t>(1, s.k / 64);
+    p.ksplit = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, max_split), 64));
+    if (p.ksplit > 1) {
+      const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
+      p.partial_bytes = (uint64_t)batch * p.ksplit * M * s.n * sizeof(float);
+      p.counter_bytes = (uint64_t)batch * tiles * sizeof(unsigned);
+    }
+    return p;
+  }
+  if (s.m <= 8 && s.rhs_k == 1 && s.lhs_k == 1 && s.k % V == 0 && aligned(s.rhs_n) && aligned(s.rhs_b0) &&
+      aligned(s.rhs_b1) && aligned(s.lhs_m) && aligned(s.lhs_b0) && aligned(s.lhs_b1) && batches_fit) {
+    p.path = 2;
+    return p;
+  }
+  if (s.m > 8 && batches_fit && (s.m + kTile - 1) / kTile <= 65535) {
+    p.path = 3;
+    return p;
+  }
+  p.path = 0;
+  return p;
+}
+
+int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
+               void* counters, cudaStream_t stream) {
+  if (s.b0 * s.b1 * s.m * s.n == 0) return 1;
+  switch (s.dtype) {
+    case kF32: return launch_typed<float>(s, plan, lhs, rhs, out, partials, counters, stream);
+    case kF16: return launch_typed<__half>(s, plan, lhs, rhs, out, partials, counters, stream);
+    case kBF16: return launch_typed<__nv_bfloat16>(s, plan, lhs, rhs, out, partials, counters, stream);
+    default: return 0;
+  }
+}
+
+}  // namespace pjrtx

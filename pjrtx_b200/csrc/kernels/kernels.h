@@ -1,0 +1,58 @@
+// Launch wrappers of the precompiled sm_100a kernels. Every wrapper enqueues on
+// the given stream and returns the number of kernels it launched (0 = refused).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace pjrtx {
+
+// Canonical contraction out[b0,b1,m,n] = sum_k lhs[b0,b1,m,k] * rhs[b0,b1,k,n]
+// with arbitrary element strides, as produced by analysing a dot_general
+// (src/backend/mlx_metal/api.cc:3349-3498 canonicalises the same way by
+// transposing; here the strides are passed to the kernel instead).
+struct DotShape {
+  int dtype = 0;
+  int64_t b0 = 1, b1 = 1, m = 1, n = 1, k = 1;
+  int64_t lhs_b0 = 0, lhs_b1 = 0, lhs_m = 0, lhs_k = 1;
+  int64_t rhs_b0 = 0, rhs_b1 = 0, rhs_k = 0, rhs_n = 1;
+  int64_t out_b0 = 0, out_b1 = 0, out_m = 0;  // out n stride is 1
+};
+
+// Scratch a split-K streaming contraction needs: f32 partials + tile counters.
+struct DotScratch {
+  uint64_t partial_bytes = 0;
+  uint64_t counter_bytes = 0;
+  int ksplit = 1;
+  int path = 0;  // 0 generic, 1 streaming rhs[K,N] (N contiguous), 2 streaming rhs[N,K] (K contiguous), 3 f32 tile
+};
+
+// Chooses the kernel for a shape and sizes its scratch.
+DotScratch dot_plan(const DotShape& s, int sm_count);
+int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out,
+               void* partials, void* counters, cudaStream_t stream);
+
+// dynamic_update_slice: writes `update` into `dst` (already holding the operand)
+// at start indices read from device scalars, clamped as StableHLO requires.
+struct SliceUpdateShape {
+  int rank = 0;
+  int elem_size = 1;
+  int64_t dst_dims[8] = {0};
+  int64_t upd_dims[8] = {0};
+  int start_dtype[8] = {0};
+};
+int dus_launch(const SliceUpdateShape& s, void* dst, const void* update, const void* const* start_ptrs,
+               cudaStream_t stream);
+
+// Scaled dot-product attention custom call (src/backend/mlx_metal/custom_call.zig:120-152,
+// src/backend/mlx_metal/api.cc:4929-5043): q [b,]q,h,hd ; k,v [b,]kv,g,hd ; scalar token index.
+struct SdpaShape {
+  int dtype = 0;
+  int64_t batch = 1, q_len = 1, heads = 1, kv_len = 1, kv_heads = 1, head_dim = 1;
+  int token_dtype = 0;
+};
+int sdpa_launch(const SdpaShape& s, const void* q, const void* k, const void* v, const void* token_index, void* out,
+                cudaStream_t stream);
+
+}  // namespace pjrtx

@@ -1,0 +1,275 @@
+#include "plan.h"
+
+#include <cstring>
+
+namespace pjrtx {
+
+static thread_local std::string g_last_error;
+
+void set_last_error(const char* fmt, ...) {
+  char buf[2048];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+}
+
+const char* last_error() { return g_last_error.c_str(); }
+
+std::string strfmt(const char* fmt, ...) {
+  char buf[4096];
+  va_list ap;
+  va_start(ap, fmt);
+  int n = vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (n < 0) return "";
+  if ((size_t)n < sizeof buf) return std::string(buf, n);
+  std::string big(n + 1, '\0');
+  va_start(ap, fmt);
+  vsnprintf(&big[0], big.size(), fmt, ap);
+  va_end(ap);
+  big.resize(n);
+  return big;
+}
+
+static const char* kKindNames[] = {
+#define X(n) #n,
+    PJRTX_KINDS(X)
+#undef X
+};
+
+const char* kind_name(Kind k) {
+  int i = (int)k;
+  if (i < 0 || i >= (int)Kind::kCount) return "unsupported";
+  return kKindNames[i];
+}
+
+Kind kind_from_name(const std::string& name) {
+  for (int i = 0; i < (int)Kind::kCount; i++)
+    if (name == kKindNames[i]) return (Kind)i;
+  // The reference spells these without the trailing underscore in diagnostics.
+  if (name == "and") return Kind::and_;
+  if (name == "or") return Kind::or_;
+  if (name == "xor") return Kind::xor_;
+  if (name == "not") return Kind::not_;
+  if (name == "while") return Kind::while_;
+  return Kind::unsupported;
+}
+
+static const std::vector<int64_t> kEmptyList;
+
+const std::vector<int64_t>& Instruction::list(const char* name) const {
+  auto it = attrs.find(name);
+  return it == attrs.end() ? kEmptyList : it->second;
+}
+
+int64_t Instruction::scalar(const char* name, int64_t fallback) const {
+  auto it = attrs.find(name);
+  if (it == attrs.end() || it->second.empty()) return fallback;
+  return it->second[0];
+}
+
+std::vector<uint32_t> Plan::parameter_ids() const {
+  std::vector<uint32_t> ids;
+  for (const Value& v : values)
+    if (v.role == ValueRole::parameter) ids.push_back(v.id);
+  return ids;
+}
+
+namespace {
+
+bool is_unary_kind(Kind k) {
+  switch (k) {
+    case Kind::copy_arg0: case Kind::negate: case Kind::exp: case Kind::expm1: case Kind::tanh:
+    case Kind::sqrt: case Kind::rsqrt: case Kind::abs: case Kind::cbrt: case Kind::ceil:
+    case Kind::floor: case Kind::log: case Kind::log1p: case Kind::logistic: case Kind::sine:
+    case Kind::cosine: case Kind::not_: case Kind::sign: case Kind::is_finite:
+    case Kind::round_nearest_afz: case Kind::round_nearest_even: case Kind::popcnt:
+    case Kind::count_leading_zeros: case Kind::convert: case Kind::bitcast_convert:
+    case Kind::reshape: case Kind::transpose: case Kind::broadcast_in_dim: case Kind::slice:
+    case Kind::top_k: case Kind::reverse: case Kind::cholesky: case Kind::fft:
+    case Kind::get_tuple_element: case Kind::imag: case Kind::real: case Kind::reduce_precision:
+    case Kind::all_reduce: case Kind::all_gather:
+      return true;
+    default:
+      return false;
+  }
+}
+
+bool is_binary_kind(Kind k) {
+  switch (k) {
+    case Kind::add: case Kind::subtract: case Kind::multiply: case Kind::divide:
+    case Kind::maximum: case Kind::minimum: case Kind::power: case Kind::atan2:
+    case Kind::remainder: case Kind::and_: case Kind::or_: case Kind::xor_:
+    case Kind::shift_left: case Kind::shift_right_arithmetic: case Kind::shift_right_logical:
+    case Kind::dot_general: case Kind::compare: case Kind::gather: case Kind::pad:
+    case Kind::complex: case Kind::convolution: case Kind::triangular_solve:
+      return true;
+    default:
+      return false;
+  }
+}
+
+// Fixed operand count of a kind, or -1 when it varies
+// (src/compiler/executable_plan_verify.zig:19-30).
+int expected_arity(Kind k) {
+  switch (k) {
+    case Kind::constant: case Kind::iota: case Kind::partition_id: return 0;
+    case Kind::select: case Kind::clamp: return 3;
+    case Kind::dynamic_slice: case Kind::dynamic_update_slice: case Kind::concatenate:
+    case Kind::custom_call: case Kind::optimization_barrier: case Kind::rng_bit_generator:
+    case Kind::scatter: case Kind::sort: case Kind::tuple: case Kind::while_:
+    case Kind::reduce_sum: case Kind::reduce_max: case Kind::reduce_min: case Kind::reduce_and:
+    case Kind::reduce_or: case Kind::rng: case Kind::unsupported:
+      return -1;
+    default:
+      if (is_unary_kind(k)) return 1;
+      if (is_binary_kind(k)) return 2;
+      return -1;
+  }
+}
+
+std::string fail(long instruction, long value, const std::string& detail, const char* feature) {
+  std::string s = "invalid executable plan: pass=pjrtx-plan-verify";
+  if (instruction >= 0) s += strfmt(" instruction=%ld", instruction);
+  if (value >= 0) s += strfmt(" value=%ld", value);
+  s += " detail=\"" + detail + "\" feature=" + feature;
+  return s;
+}
+
+bool elementwise_same_shape_kind(Kind k) {
+  switch (k) {
+    case Kind::add: case Kind::subtract: case Kind::multiply: case Kind::divide:
+    case Kind::maximum: case Kind::minimum: case Kind::power: case Kind::atan2:
+    case Kind::remainder: case Kind::and_: case Kind::or_: case Kind::xor_:
+    case Kind::shift_left: case Kind::shift_right_arithmetic: case Kind::shift_right_logical:
+    case Kind::negate: case Kind::exp: case Kind::expm1: case Kind::tanh: case Kind::sqrt:
+    case Kind::rsqrt: case Kind::abs: case Kind::cbrt: case Kind::ceil: case Kind::floor:
+    case Kind::log: case Kind::log1p: case Kind::logistic: case Kind::sine: case Kind::cosine:
+    case Kind::not_: case Kind::sign: case Kind::round_nearest_afz:
+    case Kind::round_nearest_even: case Kind::popcnt: case Kind::count_leading_zeros:
+      return true;
+    default:
+      return false;
+  }
+}
+
+}  // namespace
+
+std::string verify_plan(const Plan& plan) {
+  if (plan.num_replicas < 1 || plan.num_partitions < 1)
+    return fail(-1, -1, "replica and partition counts must be positive", "topology");
+  size_t slots = (size_t)plan.num_replicas * (size_t)plan.num_partitions;
+  if (plan.device_assignment.size() < slots)
+    return fail(-1, -1, "device assignment is shorter than replicas*partitions", "topology");
+  if (plan.values.empty())
+    return fail(-1, -1, "executable plan has no values", "value-graph");
+
+  std::vector<char> defined(plan.values.size(), 0);
+  size_t parameter_count = 0;
+  for (size_t i = 0; i < plan.values.size(); i++) {
+    const Value& v = plan.values[i];
+    if (v.id != i) return fail(-1, (long)i, "value id does not match its table index", "value-graph");
+    for (int64_t d : v.dims)
+      if (d < 0) return fail(-1, (long)i, "value has a negative dimension", "value-storage");
+    if (v.role == ValueRole::parameter) {
+      defined[i] = 1;
+      parameter_count++;
+    }
+  }
+  if (plan.parameter_shardings.size() != parameter_count)
+    return strfmt(
+        "invalid executable plan: pass=pjrtx-plan-verify detail=\"parameter sharding count must match "
+        "parameter value count: shardings=%zu parameters=%zu\" feature=sharding",
+        plan.parameter_shardings.size(), parameter_count);
+  if (plan.output_ids.size() != plan.output_shardings.size())
+    return fail(-1, -1, "output sharding count must match output count", "sharding");
+
+  for (size_t n = 0; n < plan.instructions.size(); n++) {
+    const Instruction& ins = plan.instructions[n];
+    if (ins.kind == Kind::unsupported || ins.kind == Kind::kCount)
+      return fail((long)n, -1, "unsupported instruction kind entered the plan", "instruction-kind");
+    int arity = expected_arity(ins.kind);
+    if (arity >= 0 && (int)ins.inputs.size() != arity)
+      return fail((long)n, -1,
+                  strfmt("%s expects %d operands, got %zu", kind_name(ins.kind), arity, ins.inputs.size()),
+                  "instruction-arity");
+    for (uint32_t in : ins.inputs) {
+      if (in >= plan.values.size())
+        return fail((long)n, (long)in, "instruction input is outside the value table", "value-graph");
+      if (!defined[in])
+        return fail((long)n, (long)in, "instruction input is used before it is defined", "value-graph");
+    }
+    if (ins.outputs.empty())
+      return fail((long)n, -1, "instruction defines no value", "value-graph");
+    for (uint32_t out : ins.outputs) {
+      if (out >= plan.values.size())
+        return fail((long)n, (long)out, "instruction output is outside the value table", "value-graph");
+      if (defined[out])
+        return fail((long)n, (long)out, "value is defined more than once", "value-graph");
+      ValueRole role = plan.values[out].role;
+      if (role == ValueRole::parameter)
+        return fail((long)n, (long)out, "instruction result has parameter role", "value-role");
+      defined[out] = 1;
+    }
+    const Value& out0 = plan.values[ins.outputs[0]];
+    if (ins.kind == Kind::constant) {
+      if (ins.literal.size() != out0.bytes())
+        return fail((long)n, (long)out0.id, "constant literal size does not match its descriptor", "value-storage");
+    }
+    if (elementwise_same_shape_kind(ins.kind)) {
+      for (uint32_t in : ins.inputs) {
+        const Value& v = plan.values[in];
+        if (v.dims != out0.dims)
+          return fail((long)n, (long)in, "elementwise operand shape differs from result shape", "value-storage");
+        if (v.dtype != out0.dtype)
+          return fail((long)n, (long)in, "elementwise operand type differs from result type", "value-storage");
+      }
+    }
+    if (ins.kind == Kind::compare || ins.kind == Kind::select || ins.kind == Kind::clamp) {
+      for (uint32_t in : ins.inputs) {
+        const Value& v = plan.values[in];
+        // select/clamp accept rank-0 predicate / bounds.
+        if (v.dims != out0.dims && !v.dims.empty())
+          return fail((long)n, (long)in, "operand shape differs from result shape", "value-storage");
+      }
+      if (ins.kind == Kind::compare && out0.dtype != kPred)
+        return fail((long)n, (long)out0.id, "compare result must be a predicate", "value-storage");
+    }
+    if (ins.kind == Kind::reshape) {
+      if (plan.values[ins.inputs[0]].count() != out0.count())
+        return fail((long)n, (long)out0.id, "reshape changes the element count", "value-storage");
+    }
+    if (ins.kind == Kind::transpose) {
+      const auto& perm = ins.list("permutation");
+      const Value& src = plan.values[ins.inputs[0]];
+      if (perm.size() != src.dims.size() || out0.dims.size() != src.dims.size())
+        return fail((long)n, -1, "transpose permutation rank mismatch", "value-storage");
+      for (size_t d = 0; d < perm.size(); d++)
+        if (perm[d] < 0 || perm[d] >= (int64_t)src.dims.size() || out0.dims[d] != src.dims[perm[d]])
+          return fail((long)n, -1, "transpose permutation does not produce the result shape", "value-storage");
+    }
+  }
+  for (size_t i = 0; i < plan.values.size(); i++)
+    if (!defined[i] && plan.values[i].role != ValueRole::parameter)
+      return fail(-1, (long)i, "value is never defined", "value-graph");
+
+  for (uint32_t id : plan.output_ids)
+    if (id >= plan.values.size())
+      return fail(-1, (long)id, "output id is outside the value table", "value-graph");
+  for (uint32_t p : plan.donated_parameter_indices)
+    if (p >= parameter_count) return fail(-1, -1, "donated parameter index is out of range", "donation-alias");
+  for (const OutputAlias& a : plan.output_aliases) {
+    if (a.output_index >= plan.output_ids.size())
+      return fail(-1, -1, "output alias names an unknown output", "donation-alias");
+    if (a.parameter_index >= parameter_count)
+      return fail(-1, -1, "output alias names an unknown parameter", "donation-alias");
+    bool donated = false;
+    for (uint32_t p : plan.donated_parameter_indices) donated |= (p == a.parameter_index);
+    if (!donated) return fail(-1, -1, "output alias parameter is not donated", "donation-alias");
+  }
+  return "";
+}
+
+}  // namespace pjrtx

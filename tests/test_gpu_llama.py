@@ -1,0 +1,102 @@
+"""GPU parity of the Llama-shaped decode / prefill programs against the CPU oracle (teacher-forced)."""
+import numpy as np
+import pytest
+
+from pjrtx_b200 import plan as P
+from pjrtx_b200.programs import llama
+from tests.util import assert_close, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _decode_args(cfg, names, weights, caches, tokens, pos):
+    return [np.asarray(tokens, np.int32), np.array(pos, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_tiny_decode_steps_teacher_forced(gpu_backend, batch):
+    """Four decode steps; every step the backend gets the oracle's token and caches' history.
+
+    Logits: bf16 rel 2e-2 with max-abs error reported; next token: equal wherever the oracle's top-2 logits are
+    further apart than the logit error; KV caches: bf16 rel 2e-2. The graph-replayed executable is reused across steps.
+    """
+    be = gpu_backend
+    cfg = llama.TINY
+    max_len, filled = 64, 40
+    builder, names = llama.build_decode_step(cfg, batch, max_len, return_logits=True)
+    weights = llama.make_weights(cfg, seed=0)
+    caches = llama.make_kv_cache(cfg, batch, max_len, filled)
+    exe = be.compile_executable(builder, [0])
+    wbufs = [be.buffer_from_host(weights[n]) for n in names[2:2 + len(weights)]]
+    cbufs = [be.buffer_from_host(c) for c in caches]
+    tokens = np.arange(3, 3 + batch, dtype=np.int32)
+    oracle_caches = caches
+    worst = 0.0
+    for step in range(4):
+        pos = filled + step
+        want = run_oracle(builder, _decode_args(cfg, names, weights, oracle_caches, tokens, pos))
+        outs = be.execute_executable(exe, [be.buffer_from_host(tokens), be.buffer_from_host(np.array(pos, np.int32))] + wbufs + cbufs)
+        got_tok, got_logits = outs[0].to_numpy(), outs[1].to_numpy()
+        assert_close(got_logits, want[1], 2e-2, what=f"step {step} logits")
+        err = float(np.max(np.abs(got_logits.astype(np.float32) - want[1].astype(np.float32))))
+        worst = max(worst, err)
+        ref = want[1].astype(np.float32)
+        top2 = np.sort(ref, axis=1)[:, -2:]
+        decisive = (top2[:, 1] - top2[:, 0]) > 2 * err
+        assert np.array_equal(got_tok[decisive], want[0][decisive]), f"step {step}"
+        for l, (g, w) in enumerate(zip(outs[2:], want[2:])):
+            assert_close(g.to_numpy(), w, 2e-2, what=f"step {step} cache {l}")
+        cbufs = outs[2:]                      # donated caches come back as outputs
+        oracle_caches = want[2:]
+        tokens = want[0]                      # teacher forcing
+    stats = exe.stats()
+    assert stats["execute_count"] == 4 and stats["donation_alias_output_count"] == 4 * 2 * cfg.layers
+    assert stats["graph_capture_count"] == 1 and stats["graph_launch_count"] == 4
+    print(f"logits max-abs error over 4 steps: {worst:.4e}")
+
+
+def test_argmax_of_decode_is_bit_exact_on_identical_logits(gpu_backend):
+    """Greedy choice on the oracle's own logits must be the oracle's token, ties included."""
+    from pjrtx_b200 import PlanBuilder
+    from tests.util import run_backend
+
+    rng = np.random.default_rng(4)
+    logits = (rng.standard_normal((3, 1024), dtype=np.float32) * 0.05).astype(P.np_dtype(P.BF16_CODE))
+    b = PlanBuilder()
+    p = b.parameter(P.BF16_CODE, logits.shape)
+    _, idx = b.argmax(p, 1)
+    b.set_outputs([idx])
+    assert np.array_equal(run_backend(gpu_backend, b, [logits])[0], run_oracle(b, [logits])[0])
+
+
+def test_tiny_prefill(gpu_backend):
+    be = gpu_backend
+    cfg = llama.TINY
+    batch, seq = 2, 32
+    builder, names = llama.build_prefill(cfg, batch, seq)
+    weights = llama.make_weights(cfg, seed=0)
+    tokens = np.random.default_rng(2).integers(0, cfg.vocab, size=(batch, seq), dtype=np.int32)
+    args = [tokens] + [weights[n] for n in names[1:]]
+    want = run_oracle(builder, args)
+    exe = be.compile_executable(builder, [0])
+    outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
+    for l, (g, w) in enumerate(zip(outs[1:], want[1:])):
+        assert_close(g.to_numpy(), w, 2e-2, what=f"kv {l}")
+    assert outs[0].to_numpy().shape == (batch,)
+
+
+def test_int8_weight_only_decode(gpu_backend):
+    """Dequantisation written as convert + multiply feeding dot_general."""
+    import dataclasses
+
+    be = gpu_backend
+    cfg = dataclasses.replace(llama.TINY, int8_weights=True)
+    batch, max_len, filled = 2, 64, 40
+    builder, names = llama.build_decode_step(cfg, batch, max_len, return_logits=True)
+    weights = llama.make_weights(cfg, seed=0)
+    caches = llama.make_kv_cache(cfg, batch, max_len, filled)
+    args = [np.array([5, 9], np.int32), np.array(filled, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
+    want = run_oracle(builder, args)
+    exe = be.compile_executable(builder, [0])
+    outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
+    assert_close(outs[1].to_numpy(), want[1], 2e-2, what="int8 logits")

@@ -1,0 +1,224 @@
+"""GPU parity: every case runs through the C ABI on a B200 and is compared with the CPU oracle.
+
+Bar: integer / predicate / index results bit-exact; f32 rel 1e-5; f16 / bf16 rel 2e-2 (atol = rtol * max|want|).
+"""
+import os
+
+import numpy as np
+import pytest
+
+from pjrtx_b200 import PlanBuilder
+from pjrtx_b200 import backend as be_mod
+from pjrtx_b200 import plan as P
+from tests import cases
+from tests.util import assert_close, assert_outputs, run_backend, run_oracle
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+CASES = ["dot_rhs_transposed", "dot_batched", "attention_scores_context", "argmax_ties", "sdpa_single", "sdpa_gqa",
+         "elementwise_float_chain", "reshape_transpose_broadcast", "reduce_cases", "float_unary_math", "is_finite_case",
+         "int_ops", "i8_negate_sub", "predicate_logic", "structural_ops", "matmul_small"]
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_case_matches_oracle(gpu_backend, name):
+    b, args = getattr(cases, name)()
+    got = run_backend(gpu_backend, b, args)
+    assert_outputs(b, got, run_oracle(b, args), name)
+
+
+def test_u8_chain_values_and_stats(gpu_backend):
+    """Known answers and counters of src/backend/mlx_metal/execution_call.zig:147-390."""
+    be = gpu_backend
+    b, _ = cases.u8_chain()
+    exe = be.compile_executable(b, [0])
+    s = exe.stats()
+    assert s["resident_constant_count"] == 1 and s["resident_constant_bytes"] == 4
+    assert (s["program_value_count"], s["program_node_count"], s["program_edge_count"]) == (4, 3, 3)
+    assert s["program_schedule_item_count"] == 3 and s["program_fusion_group_count"] == 1
+    assert s["program_materialization_boundary_count"] == 1
+    assert s["program_planned_release_count"] == 1 and s["program_planned_release_bytes"] == 4
+    assert s["program_peak_live_value_count"] == 4 and s["program_peak_live_bytes"] == 16
+    assert s["program_device_count"] == 1 and s["execute_count"] == 0
+    assert s["last_execute_device_index"] == 2**64 - 1 and s["last_execute_local_hardware_id"] == -1
+    lhs = be.buffer_from_host(np.array([1, 2, 3, 4], np.uint8))
+    # wrong device index, missing and surplus arguments are refused and leave the counters alone
+    for bad_args, dev in (([lhs], 1), ([], 0), ([lhs, lhs], 0)):
+        with pytest.raises(be_mod.BackendError):
+            be.execute_executable(exe, bad_args, device_index=dev)
+    assert exe.stats()["execute_count"] == 0
+    out = be.execute_executable(exe, [lhs])
+    assert len(out) == 1 and out[0].dtype == P.U8 and out[0].dims == (4,)
+    assert out[0].to_numpy().tolist() == [6, 15, 28, 45]
+    s = exe.stats()
+    assert s["execute_count"] == 1 and s["last_execute_device_index"] == 0 and s["last_execute_local_hardware_id"] == 0
+    second = be.buffer_from_host(np.array([2, 4, 6, 8], np.uint8))
+    out2 = be.execute_executable(exe, [second])
+    assert out2[0].to_numpy().tolist() == [8, 21, 40, 65]
+    assert exe.stats()["execute_count"] == 2 and exe.stats()["resident_constant_count"] == 1
+
+
+@pytest.mark.parametrize("dtype", [P.F16, P.BF16_CODE, P.F32])
+def test_dot_2x2_known_answer(gpu_backend, dtype):
+    b, args = cases.dot_2x2(dtype)
+    assert run_backend(gpu_backend, b, args)[0].reshape(-1).tolist() == [19.0, 22.0, 43.0, 50.0]
+
+
+@pytest.mark.parametrize("dtype", [P.F16, P.BF16_CODE])
+def test_reduce_rows_known_answer(gpu_backend, dtype):
+    s, mx, mn = run_backend(gpu_backend, *cases.reduce_rows(dtype))
+    assert s.tolist() == [3.0, 7.0] and mx.tolist() == [2.0, 4.0] and mn.tolist() == [1.0, 3.0]
+
+
+def test_argmax_ties_and_nan(gpu_backend):
+    val, idx = run_backend(gpu_backend, *cases.argmax_ties())
+    assert val.tolist() == [7.0, 5.0] and idx.tolist() == [1, 1]
+    v = np.array([[1.0, np.nan, 7.0, np.nan], [np.nan, 2.0, 3.0, 4.0]], np.float32)
+    val, idx = run_backend(gpu_backend, *cases.argmax_ties(v))
+    assert np.isnan(val).all() and idx.tolist() == [1, 0]
+
+
+def test_argmax_bit_exact_on_wide_rows_with_ties(gpu_backend):
+    """bf16 logits over a 128256-wide vocabulary tie often; the index must be the oracle's."""
+    rng = np.random.default_rng(5)
+    logits = (rng.standard_normal((4, 128256), dtype=np.float32) * 0.3).astype(P.np_dtype(P.BF16_CODE))
+    logits[2, :] = logits[2, 7]  # a whole row of ties
+    b = PlanBuilder()
+    p = b.parameter(P.BF16_CODE, logits.shape)
+    val, idx = b.argmax(p, 1)
+    b.set_outputs([val, idx])
+    got = run_backend(gpu_backend, b, [logits])
+    want = run_oracle(b, [logits])
+    assert np.array_equal(got[1], want[1]) and got[1][2] == 0
+    assert np.array_equal(got[0].view(np.uint16), want[0].view(np.uint16))
+
+
+@pytest.mark.parametrize("dtype", [P.F32, P.F16, P.BF16_CODE])
+def test_sdpa_random(gpu_backend, dtype):
+    b, args = cases.sdpa_random(dtype)
+    assert_outputs(b, run_backend(gpu_backend, b, args), run_oracle(b, args), "sdpa")
+
+
+@pytest.mark.parametrize("name", ["tiny", "medium"])
+def test_llama_like_block_golden(gpu_backend, name):
+    """Against the reference's NumPy reference (rtol = atol = 2e-4, jax_llama_like_inference.py:246-252)."""
+    data = np.load(os.path.join(GOLDEN, f"llama_like_{name}.npz"))
+    keys = ("x", "norm_w", "wq", "wk", "wv", "wo", "w1", "w2", "w3")
+    b, args = cases.llama_like_block(*[data[k] for k in keys])
+    be = gpu_backend
+    exe = be.compile_executable(b, [0])
+    weight_bytes = sum(data[k].nbytes for k in keys[1:])
+    assert exe.stats()["resident_constant_bytes"] - weight_bytes <= 4096  # resident-constant overhead budget
+    for _ in range(3):
+        got = run_backend(be, b, args, exe=exe)[0]
+        np.testing.assert_allclose(got, data["expected"], rtol=2e-4, atol=2e-4)
+    assert exe.stats()["execute_count"] == 3
+
+
+def test_config1_fused_chain_and_reductions(gpu_backend):
+    """f32 [4096,4096]: z = x*y + sin(x) - log1p(|y|), row sum / max / argmax in one kernel."""
+    b, args = cases.op_suite_config1()
+    got = run_backend(gpu_backend, b, args)
+    want = run_oracle(b, args)
+    x, y = (a.astype(np.float64) for a in args)
+    z_abs_sum = np.sum(np.abs(x * y) + np.abs(np.sin(x)) + np.abs(np.log1p(np.abs(y))), axis=1)
+    # row sums: relative to the magnitude that was summed (cancellation makes |sum| << sum|terms|)
+    assert np.max(np.abs(got[0].astype(np.float64) - want[0]) / z_abs_sum) <= 1e-5
+    assert_close(got[1], want[1], 1e-5, what="row max")
+    # argmax is bit-exact wherever the f32 maximum itself is unambiguous; elsewhere the chosen element must hold the max
+    z32 = want[1]
+    same = got[2] == want[2]
+    zf = (x * y + np.sin(x) - np.log1p(np.abs(y)))
+    picked = zf[np.arange(zf.shape[0]), got[2]]
+    assert same.mean() >= 0.999 and np.all(np.abs(picked - z32) <= 1e-5 * np.abs(z32) + 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [P.F32, P.F16])
+def test_config1_matmul_1024(gpu_backend, dtype):
+    b, args = cases.matmul_config1(1024, dtype)
+    got = run_backend(gpu_backend, b, args)[0].astype(np.float64)
+    a64, b64 = args[0].astype(np.float64), args[1].astype(np.float64)
+    want = a64 @ b64
+    mag = np.abs(a64) @ np.abs(b64)  # error scales with the summed magnitudes
+    rtol = 1e-5 if dtype == P.F32 else 2e-2
+    assert np.max(np.abs(got - want) / mag) <= rtol
+    if dtype == P.F16:
+        assert_close(got, want.astype(np.float16), 2e-2, what="f16 matmul")
+
+
+def test_streaming_dot_paths_against_f64(gpu_backend):
+    """Skinny contractions: rhs[K,N] (split-K) and rhs[N,K] for m = 1..8, bf16 and f32."""
+    rng = np.random.default_rng(9)
+    for dtype, rtol in ((P.BF16_CODE, 2e-2), (P.F32, 1e-5), (P.F16, 2e-2)):
+        dt = P.np_dtype(dtype)
+        for m, k, n in ((1, 4096, 1024), (4, 512, 2048), (8, 1000, 264), (3, 64, 40)):
+            lhs = rng.standard_normal((m, k), dtype=np.float32).astype(dt)
+            rkn = rng.standard_normal((k, n), dtype=np.float32).astype(dt)
+            b = PlanBuilder()
+            pl, pr = b.parameter(dtype, lhs.shape), b.parameter(dtype, rkn.shape)
+            prt = b.parameter(dtype, (n, k))
+            b.set_outputs([b.dot_general(pl, pr, [1], [0]), b.dot_general(pl, prt, [1], [1])])
+            rnk = np.ascontiguousarray(rkn.T)
+            got = run_backend(gpu_backend, b, [lhs, rkn, rnk])
+            want = lhs.astype(np.float64) @ rkn.astype(np.float64)
+            mag = np.abs(lhs.astype(np.float64)) @ np.abs(rkn.astype(np.float64))
+            for g in got:
+                err = np.abs(g.astype(np.float64) - want)
+                assert np.all(err <= rtol * mag + rtol * np.abs(want)), (dtype, m, k, n, float((err / mag).max()))
+            # both layouts agree and repeated runs are bit-identical (fixed reduction order)
+            again = run_backend(gpu_backend, b, [lhs, rkn, rnk])
+            assert all(np.array_equal(a.view(np.uint8), c.view(np.uint8)) for a, c in zip(got, again))
+
+
+def test_donated_slice_update_is_in_place(gpu_backend):
+    be = gpu_backend
+    b = PlanBuilder()
+    cache = b.parameter(P.BF16_CODE, [2, 16, 2, 8])
+    upd = b.parameter(P.BF16_CODE, [2, 1, 2, 8])
+    pos = b.parameter(P.S32, [])
+    zero = b.constant(np.int32(0))
+    out = b.dynamic_update_slice(cache, upd, [zero, pos, zero, zero])
+    b.set_outputs([out, b.reduce("reduce_sum", b.convert(out, P.F32), [0, 1, 2, 3])], donate={0: 0})
+    exe = be.compile_executable(b, [0])
+    rng = np.random.default_rng(2)
+    c0 = rng.standard_normal((2, 16, 2, 8), dtype=np.float32).astype(P.np_dtype(P.BF16_CODE))
+    u = rng.standard_normal((2, 1, 2, 8), dtype=np.float32).astype(P.np_dtype(P.BF16_CODE))
+    want = run_oracle(b, [c0, u, np.array(5, np.int32)])
+    cb, ub, pb = be.buffer_from_host(c0), be.buffer_from_host(u), be.buffer_from_host(np.array(5, np.int32))
+    outs = be.execute_executable(exe, [cb, ub, pb])
+    assert cb.is_donated and not ub.is_donated
+    assert np.array_equal(outs[0].to_numpy().view(np.uint16), want[0].view(np.uint16))
+    assert_close(outs[1].to_numpy(), want[1], 1e-5, atol_scale=float(np.abs(c0.astype(np.float32)).sum()))
+    assert exe.stats()["donation_alias_output_count"] == 1
+    with pytest.raises(be_mod.BackendError):  # a donated buffer cannot be used again
+        be.execute_executable(exe, [cb, ub, pb])
+    # position beyond the end clamps to the last row
+    outs2 = be.execute_executable(exe, [outs[0], ub, be.buffer_from_host(np.array(99, np.int32))])
+    got = outs2[0].to_numpy()
+    assert np.array_equal(got[:, 15].view(np.uint16), u[:, 0].view(np.uint16))
+
+
+def test_buffer_round_trip_and_errors(gpu_backend):
+    be = gpu_backend
+    for dt in (np.float32, np.int32, np.uint8, np.int8, np.uint16, np.uint32, np.uint64, np.int64, np.float16, np.bool_):
+        a = (np.arange(24).reshape(2, 3, 4) % 5).astype(dt)
+        buf = be.buffer_from_host(a)
+        assert buf.dims == (2, 3, 4) and buf.nbytes == a.nbytes
+        assert np.array_equal(buf.to_numpy(), a)
+        clone = be.clone_buffer(buf)
+        assert np.array_equal(clone.to_numpy(), a)
+    empty = be.buffer_from_host(np.zeros((0, 4), np.float32))
+    assert empty.nbytes == 0 and empty.to_numpy().shape == (0, 4)
+    z = be.allocate_buffer(P.F32, [3, 3])
+    assert not z.to_numpy().any()
+    big = np.arange(1 << 20, dtype=np.float32)  # larger than the pinned staging slot
+    assert np.array_equal(be.buffer_from_host(big).to_numpy(), big)
+    stats = be.memory_stats()
+    assert stats["host_to_device_bytes"] >= big.nbytes and stats["device_to_host_bytes"] >= big.nbytes
+    with pytest.raises(be_mod.BackendError):
+        be.buffer_from_host(np.zeros(4, np.float32), device=99)
+    # undersized destination
+    import ctypes
+    dst = np.zeros(2, np.float32)
+    assert be.lib.pjrtx_b200_buffer_copy_to_host(z.handle, dst.ctypes.data_as(ctypes.c_void_p), dst.nbytes) == 0

@@ -1,0 +1,222 @@
+"""Host logic on CPU: C-ABI exports, plan verifier, program graph counters, legalization, kernel planner, codegen."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from pjrtx_b200 import PlanBuilder
+from pjrtx_b200 import backend as be_mod
+from pjrtx_b200 import plan as P
+from pjrtx_b200.programs import llama
+from tests import cases
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(backend):
+    header = open(os.path.join(ROOT, "include", "pjrtx_b200.h")).read()
+    declared = set(re.findall(r"\b(pjrtx_b200_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    raw = ctypes.CDLL(be_mod.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(raw, name), f"{name} is declared in include/pjrtx_b200.h but not exported"
+    assert declared == set(be_mod.SYMBOLS), declared ^ set(be_mod.SYMBOLS)
+
+
+def test_capabilities_and_version(backend):
+    caps = backend.capabilities()
+    assert caps["name"] == "b200_cuda" and caps["supports_device_buffers"] and not caps["supports_unified_memory"]
+    assert backend.lib.pjrtx_b200_version_major() == 0
+
+
+def test_program_graph_matches_reference_counters(backend):
+    """Same plan and same expectations as src/backend/mlx_metal/execution_call.zig:147-298."""
+    b, _ = cases.u8_chain()
+    d = backend.describe_program(b)
+    assert d["node_count"] == 3 and d["schedule_item_count"] == 3 and d["value_count"] == 4 and d["edge_count"] == 3
+    assert [s["kind"] for s in d["schedule"]] == ["node", "fusion_group", "materialization_boundary"]
+    assert d["schedule"][1] == {"kind": "fusion_group", "index": 0, "count": 2}
+    assert [n["kind"] for n in d["nodes"]] == ["constant", "elementwise", "elementwise"]
+    assert [n["fusion_group"] for n in d["nodes"]] == [-1, 0, 0]
+    g = d["fusion_groups"][0]
+    assert (g["first_node"], g["last_node"], g["node_count"]) == (1, 2, 2)
+    assert g["input_values"] == [0, 1] and g["output_values"] == [3]
+    assert d["edges"] == [[1, 0, 1], [2, 1, 2], [1, 0, 2]]
+    assert d["materialization_boundaries"] == [3]
+    v = d["values"]
+    assert v[0]["producer_node"] == -1 and v[0]["last_use_node"] == 1 and not v[0]["is_output"]
+    assert v[1]["producer_node"] == 0 and v[1]["last_use_node"] == 2
+    assert v[2]["producer_node"] == 1 and v[2]["last_use_node"] == 2
+    assert v[3]["producer_node"] == 2 and v[3]["is_output"] and v[3]["materialization_boundary"] == 0
+    assert d["planned_release_count"] == 1 and d["planned_release_bytes"] == 4
+    assert d["peak_live_value_count"] == 4 and d["peak_live_bytes"] == 16
+
+
+def test_fusion_groups_close_on_reductions_and_dots(backend):
+    """Reference rule (program_build.zig:79-99, 224-263): reductions and dots never join a view+elementwise group."""
+    b = PlanBuilder()
+    x = b.parameter(P.F32, [4, 8])
+    y = b.unary("exp", x * x)
+    s = b.reduce("reduce_sum", y, [1])
+    z = b.unary("sqrt", s)
+    w = b.matmul(b.reshape(z, [1, 4]), b.transpose(x, [0, 1]))
+    b.set_outputs([w])
+    d = backend.describe_program(b)
+    kinds = [n["kind"] for n in d["nodes"]]
+    assert kinds == ["elementwise", "elementwise", "reduction", "elementwise", "view", "view", "matmul"]
+    assert [n["fusion_group"] for n in d["nodes"]] == [0, 0, -1, 1, 1, 1, -1]
+    assert d["fusion_group_count"] == 2
+
+
+def test_plan_verifier_diagnostics(backend):
+    b = PlanBuilder()
+    x = b.parameter(P.F32, [4])
+    b.set_outputs([x + x])
+    assert backend.verify_plan(b) == ""
+    # use before definition
+    bad = PlanBuilder()
+    p = bad.parameter(P.F32, [4])
+    out = bad._value(P.ROLE_RESULT, P.F32, [4])
+    later = bad._value(P.ROLE_RESULT, P.F32, [4])
+    bad.instructions.append(P.Instr("add", [p.id, later.id], [out.id], {}))
+    bad.instructions.append(P.Instr("negate", [p.id], [later.id], {}))
+    bad.set_outputs([out])
+    msg = backend.verify_plan(bad)
+    assert msg.startswith("invalid executable plan: pass=pjrtx-plan-verify instruction=0 value=2")
+    assert "feature=value-graph" in msg
+    # arity
+    bad2 = PlanBuilder()
+    p = bad2.parameter(P.F32, [4])
+    o = bad2._value(P.ROLE_RESULT, P.F32, [4])
+    bad2.instructions.append(P.Instr("add", [p.id], [o.id], {}))
+    bad2.set_outputs([o])
+    assert "feature=instruction-arity" in backend.verify_plan(bad2)
+    # alias to a parameter that is not donated
+    bad3 = PlanBuilder()
+    p = bad3.parameter(P.F32, [4])
+    bad3.set_outputs([p + p])
+    bad3.aliases = [(0, 0)]
+    assert "feature=donation-alias" in backend.verify_plan(bad3)
+    # topology
+    bad4 = PlanBuilder(num_partitions=2, device_assignment=[0])
+    p = bad4.parameter(P.F32, [4])
+    bad4.set_outputs([p + p])
+    assert "feature=topology" in backend.verify_plan(bad4)
+
+
+def test_legalization_diagnostics(backend):
+    """Format of src/backend/mlx_metal/lowering_diagnostic.zig:31-45; unknown custom call reports its target as the feature."""
+    b = PlanBuilder()
+    x = b.parameter(P.F32, [4])
+    b.set_outputs([b.custom_call("my.unknown.target", [x], P.F32, [4])])
+    msg = backend.write_executable_lowering_diagnostic(b)
+    assert msg.startswith("invalid executable plan: pass=b200-backend-legalization instruction=0 op=custom_call")
+    assert msg.endswith("feature=my.unknown.target") and "dtype=f32 rank=1 shape=[4] sharding=internal" in msg
+    # mixed-type dot is rejected: dequantisation must be convert + multiply feeding a same-type dot
+    b = PlanBuilder()
+    x = b.parameter(P.F16, [2, 4])
+    w = b.parameter(P.S8, [4, 3])
+    b._emit("dot_general", [x, w], P.F16, [2, 3], {"lhs_contracting_dimensions": [1], "rhs_contracting_dimensions": [0],
+                                                   "lhs_batch_dimensions": [], "rhs_batch_dimensions": []})
+    b.set_outputs([P.Val(b, len(b.values) - 1)])
+    assert "feature=b200-dot-general" in backend.write_executable_lowering_diagnostic(b)
+    # complex is out of scope
+    b = PlanBuilder()
+    x = b.parameter(P.C64, [2])
+    b.set_outputs([b._emit("negate", [x], P.C64, [2])])
+    assert "feature=b200-element-type" in backend.write_executable_lowering_diagnostic(b)
+    # no device
+    ok = PlanBuilder()
+    x = ok.parameter(P.F32, [4])
+    ok.set_outputs([x + x])
+    assert backend.write_executable_lowering_diagnostic(ok, 1) == ""
+    assert "feature=b200-device-assignment" in backend.write_executable_lowering_diagnostic(ok, 0)
+
+
+def test_registered_custom_calls_become_fusible(backend):
+    v0 = backend.custom_call_registry_version()
+    backend.register_custom_call("test.unary.sqrt", "sqrt", 1)
+    backend.register_custom_call("test.identity", "identity", 1)
+    assert backend.custom_call_registry_version() == v0 + 2
+    b = PlanBuilder()
+    x = b.parameter(P.F32, [8])
+    y = b.custom_call("test.unary.sqrt", [x], P.F32, [8])
+    b.set_outputs([b.custom_call("test.identity", [y + y], P.F32, [8])])
+    k = backend.describe_kernels(b)
+    assert [s["type"] for s in k["steps"]] == ["fused"] and "sqrtf" in k["steps"][0]["source"]
+    backend.unregister_custom_call("test.unary.sqrt")
+    backend.unregister_custom_call("test.identity")
+    assert "feature=test.unary.sqrt" in backend.write_executable_lowering_diagnostic(b)
+    with pytest.raises(be_mod.BackendError):
+        backend.register_custom_call("test.bad", "dot_general", 2)
+
+
+def test_config1_is_one_row_kernel_and_compiles(backend):
+    b, _ = cases.op_suite_config1(rows=64, cols=4096)
+    k = backend.describe_kernels(b)
+    assert len(k["steps"]) == 1
+    st = k["steps"][0]
+    assert st["row"] and st["rows"] == 64 and st["cols"] == 4096 and st["reduces"] == 3 and st["vec"] == 4
+    assert st["inputs"] == 2 and st["outputs"] == 3
+    assert "ldvec<float, 4>" in st["source"] and "block_reduce" in st["source"] and "arg_better" in st["source"]
+    assert backend.compile_check(st["source"]) == ""
+
+
+def test_decode_step_kernel_plan(backend):
+    cfg = llama.TINY
+    b, names = llama.build_decode_step(cfg, 2, 64)
+    assert backend.verify_plan(b) == ""
+    k = backend.describe_kernels(b)
+    types = [s["type"] for s in k["steps"]]
+    # per layer: 7 projections + scores + context, two cache updates in place, and the fused groups between them
+    assert types.count("dot") == 9 * cfg.layers + 1
+    assert types.count("slice_update") == 2 * cfg.layers
+    assert all(s["in_place"] for s in k["steps"] if s["type"] == "slice_update")
+    fused = [s for s in k["steps"] if s["type"] == "fused"]
+    # RMSNorm (+ residual add) and softmax are single row kernels
+    assert sum(1 for s in fused if s["row"] and s["cols"] == cfg.d_model) == 2 * cfg.layers + 1
+    assert sum(1 for s in fused if s["row"] and s["cols"] == 64 and s["reduces"] == 2) == cfg.layers
+    assert sum(1 for s in fused if s["row"] and s["cols"] == cfg.vocab) == 1  # argmax over the vocabulary
+    for src in {s["source"] for s in fused}:
+        assert backend.compile_check(src) == ""
+    # streaming paths are chosen for every projection (m = batch <= 8)
+    assert all(s["path"] in (1, 2) for s in k["steps"] if s["type"] == "dot")
+
+
+def test_all_cases_plan_and_compile(backend):
+    names = ["u8_chain", "dot_rhs_transposed", "dot_batched", "attention_scores_context", "argmax_ties", "sdpa_single",
+             "sdpa_gqa", "sdpa_random", "elementwise_float_chain", "reshape_transpose_broadcast", "reduce_cases",
+             "float_unary_math", "is_finite_case", "int_ops", "i8_negate_sub", "predicate_logic", "structural_ops",
+             "matmul_small"]
+    for name in names:
+        b, _ = getattr(cases, name)()
+        assert backend.verify_plan(b) == "", name
+        k = backend.describe_kernels(b)
+        for s in k["steps"]:
+            if s["type"] == "fused":
+                log = backend.compile_check(s["source"])
+                assert log == "", f"{name}: {log[:800]}"
+
+
+def test_tensor_parallel_partition_plan(backend):
+    cfg = llama.TINY
+    b, names = llama.build_decode_step(cfg, 2, 64, num_partitions=2)
+    for part in range(2):
+        k = backend.describe_kernels(b, partition=part)
+        types = [s["type"] for s in k["steps"]]
+        assert types.count("all_reduce") == 2 * cfg.layers       # after o_proj and down_proj
+        assert types.count("all_gather") == 1                     # vocabulary-split logits before argmax
+        dots = [s for s in k["steps"] if s["type"] == "dot"]
+        assert any(s["n"] == cfg.q_dim // 2 for s in dots) and any(s["k"] == cfg.ffn // 2 for s in dots)
+
+
+def test_execute_requires_gpu_and_fails_loudly(backend):
+    if backend.lib.pjrtx_b200_device_count() > 0:
+        pytest.skip("a device is present")
+    b, _ = cases.u8_chain()
+    with pytest.raises(be_mod.BackendError):
+        backend.compile_executable(b, [0])
+    with pytest.raises(be_mod.BackendError):
+        backend.buffer_from_host(np.zeros(4, np.float32))
