@@ -275,10 +275,11 @@ class Backend:
 
     # -- buffers --
     def buffer_from_host(self, array: np.ndarray, device: int = 0, dtype: Optional[int] = None) -> DeviceBuffer:
+        shape = np.shape(array)  # ascontiguousarray promotes rank 0 to rank 1
         arr = np.ascontiguousarray(array)
         code = dtype if dtype is not None else plan_mod.dtype_code(arr.dtype)
-        dims = (ctypes.c_int64 * arr.ndim)(*arr.shape)
-        h = self.lib.pjrtx_b200_buffer_from_host_typed(device, arr.ctypes.data_as(ctypes.c_void_p), arr.nbytes, code, dims, arr.ndim)
+        dims = (ctypes.c_int64 * len(shape))(*shape)
+        h = self.lib.pjrtx_b200_buffer_from_host_typed(device, arr.ctypes.data_as(ctypes.c_void_p), arr.nbytes, code, dims, len(shape))
         if not h:
             raise BackendError("BufferAllocationFailed", self._err())
         return DeviceBuffer(self.lib, h)
