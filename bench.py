@@ -1,0 +1,417 @@
+"""Headline benchmark: greedy decode throughput of Llama-3-shaped programs through the backend's C ABI.
+
+  python bench.py --gpus 1 --steps K --warmup W          8B-shaped bf16 decode, batch 1, KV prefilled to 2048
+  torchrun ... bench.py --gpus N (N = 2, 4, 8)            70B-shaped bf16 decode, batch 32, KV 4096, tensor parallel over N
+  python bench.py --impl reference ...                     the CPU arm: the plan interpreter on the host cores
+
+One "step" is one decode step (one token per sequence): embedding gather, all layers, greedy argmax. Weights are
+random-init N(0, 0.02) and the KV cache N(0, 1), generated on the device by seeded plans (programs/random_init.py).
+`value` keeps every input resident in HBM (the next token is fed back on the device); `e2e` uploads token and
+position from pinned host memory and reads the next token back every step.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from pjrtx_b200 import plan as P  # noqa: E402
+from pjrtx_b200.programs import llama, random_init  # noqa: E402
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def device_tensor(be, cache, builder_fn, key, seed, device):
+    """Runs (and caches by shape key) a random-init plan on the device."""
+    if key not in cache:
+        cache[key] = be.compile_executable(builder_fn(), [device])
+    sbuf = be.buffer_from_host(seed, device)
+    out = be.execute_executable(cache[key], [sbuf])[0]
+    sbuf.destroy()
+    return out
+
+
+def make_device_weights(be, cfg, names, values, device, rank, world, seed=0):
+    """Random-init parameters in program order; with tensor parallelism each rank generates its own shard."""
+    gen_cache = {}
+    bufs = []
+    for index, name in enumerate(names):
+        full = values[name]["full"]
+        local = values[name]["local"]
+        split = values[name]["split"]
+        dtype = values[name]["dtype"]
+        rows = int(np.prod(local[:-1])) if len(local) > 1 else 1
+        cols = local[-1]
+        full_cols = full[-1]
+        row_off = col_off = 0
+        if split is not None:
+            if split == len(full) - 1:
+                col_off = rank * cols
+            else:
+                inner = int(np.prod(local[split + 1:-1])) if len(local) > split + 2 else 1
+                row_off = rank * local[split] * inner if split == 0 else 0
+                if split not in (0, len(full) - 1):
+                    row_off = 0  # caches: every shard is independent N(0,1); offsets are irrelevant
+        short = name.split(".")[-1]
+        if short.endswith("norm"):
+            fn = lambda: random_init.build_normal(rows, cols, dtype, 0.02, 1.0, full_cols, row_off, col_off)
+            key = ("norm", rows, cols, dtype)
+        elif short.endswith("cache"):
+            fn = lambda: random_init.build_normal(rows, cols, dtype, 1.0, 0.0, full_cols, 0, 0)
+            key = ("cache", rows, cols, dtype)
+        elif short == "scale":
+            fn = lambda: random_init.build_uniform(rows, cols, dtype, 0.001, 0.01, full_cols, row_off, col_off)
+            key = ("scale", rows, cols, dtype, col_off)
+        elif dtype == P.S8:
+            fn = lambda: random_init.build_uniform_int8(rows, cols, full_cols, row_off, col_off)
+            key = ("int8", rows, cols, full_cols, row_off, col_off)
+        else:
+            fn = lambda: random_init.build_normal(rows, cols, dtype, 0.02, 0.0, full_cols, row_off, col_off)
+            key = ("w", rows, cols, dtype, full_cols, row_off, col_off)
+        sd = random_init.tensor_seed(seed + (rank + 1) * 7919 if short.endswith("cache") else seed, index)
+        t = device_tensor(be, gen_cache, fn, key, sd, device)
+        bufs.append((t, tuple(local)))
+    for exe in gen_cache.values():
+        exe.destroy()
+    return bufs
+
+
+def reshape_buffer(be, buf, dims, device):
+    """The generators emit rank-2 tensors; parameters of other ranks get a reshaped view through a tiny plan."""
+    if tuple(buf.dims) == tuple(dims):
+        return buf
+    from pjrtx_b200 import PlanBuilder
+    b = PlanBuilder()
+    p = b.parameter(buf.dtype, buf.dims)
+    b.set_outputs([b.reshape(p, dims)], donate={0: 0})
+    exe = be.compile_executable(b, [device])
+    out = be.execute_executable(exe, [buf])[0]
+    exe.destroy()
+    return out
+
+
+def param_table(cfg, builder, names, world):
+    table = {}
+    for pid, name, (kind, mesh, split) in zip(builder.parameter_ids, names, builder.parameter_shardings):
+        v = builder.values[pid]
+        full = list(v.dims)
+        local = list(v.dims)
+        sp = None
+        if kind == P.PARTITIONED and split >= 0 and world > 1:
+            local[split] //= world
+            sp = split
+        table[name] = {"full": full, "local": local, "split": sp, "dtype": v.dtype}
+    return table
+
+
+def algorithmic_bytes(cfg, batch, kv_len, world):
+    """Bytes one decode step must move per GPU: all weights once, KV cache up to the current position, activations ~0."""
+    esize = 1 if cfg.int8_weights else 2
+    per_layer = cfg.d_model * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.d_model + 3 * cfg.d_model * cfg.ffn
+    weights = (cfg.layers * per_layer + cfg.d_model * cfg.vocab) * esize / world + (2 * cfg.layers + 1) * cfg.d_model * 2
+    kv = cfg.layers * 2 * batch * kv_len * cfg.kv_dim * 2 / world
+    return weights + kv + batch * cfg.d_model * 2
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import pjrtx_b200
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("gloo")  # host-side plumbing only: unique-id exchange, barriers, max over ranks
+    be = pjrtx_b200.Backend()
+    device = local_rank
+    be.enumerate_devices()
+    if world == 1:
+        cfg, batch, filled, workload = llama.LLAMA3_8B, 1, 2048, "llama3-8b-shape bf16 decode batch 1, KV prefilled 2048"
+    else:
+        cfg, batch, filled = llama.LLAMA3_70B, 32, 4096
+        workload = f"llama3-70b-shape bf16 decode batch 32, KV 4096, TP={world}"
+    if args.layers:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, layers=args.layers)
+        workload += f" (truncated to {args.layers} layers)"
+    total_steps = args.warmup + args.steps
+    max_len = filled + max(256, 2 * total_steps + 8)
+    builder, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=world)
+    if world > 1:
+        uid = [be.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        be.comm_init(device, uid[0], rank, world)
+    t0 = time.time()
+    exe = be.compile_executable(builder, [device], partition=rank if world > 1 else None)
+    compile_s = time.time() - t0
+    table = param_table(cfg, builder, names, world)
+    t0 = time.time()
+    gen = make_device_weights(be, cfg, names[2:], table, device, rank, world)
+    params = [reshape_buffer(be, buf, dims, device) for buf, dims in gen]
+    be.synchronize(device)
+    setup_s = time.time() - t0
+    n_cache = 2 * cfg.layers
+    weights, caches = params[:-n_cache], params[-n_cache:]
+
+    def barrier():
+        be.synchronize(device)
+        if world > 1:
+            dist.barrier()
+
+    pos_bufs = [be.buffer_from_host(np.array(filled + i, np.int32), device) for i in range(2 * total_steps)]
+    token = be.buffer_from_host(np.full((batch,), 1, np.int32), device)
+
+    def step(tok, pos_buf, caches):
+        outs = be.execute_executable(exe, [tok, pos_buf] + weights + caches)
+        return outs[0], outs[1:]
+
+    # ---- device-resident loop -------------------------------------------------
+    pi = 0
+    for _ in range(args.warmup):
+        token, caches = step(token, pos_bufs[pi], caches); pi += 1
+    barrier()
+    launches0 = exe.stats()["kernel_launch_total"]
+    sampler = ClockSampler(device)
+    if rank == 0:
+        sampler.start()
+    start = be.record_event(device)
+    for _ in range(args.steps):
+        token, caches = step(token, pos_bufs[pi], caches); pi += 1
+    stop = be.record_event(device)
+    ms = be.elapsed_ms(start, stop)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = exe.stats()["kernel_launch_total"] - launches0
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- end to end: pinned host -> device every step, token read back every step ----
+    pinned_tok = torch.empty((batch,), dtype=torch.int32).pin_memory()
+    pinned_pos = torch.empty((1,), dtype=torch.int32).pin_memory()
+    pinned_out = torch.empty((batch,), dtype=torch.int32).pin_memory()
+    pinned_tok.copy_(torch.from_numpy(token.to_numpy()))
+    barrier()
+    e2e_start = be.record_event(device)
+    t_wall = time.perf_counter()
+    for i in range(args.steps):
+        pinned_pos[0] = filled + pi
+        tb = be.buffer_from_pointer(pinned_tok.data_ptr(), 4 * batch, P.S32, [batch], device)
+        pb = be.buffer_from_pointer(pinned_pos.data_ptr(), 4, P.S32, [], device)
+        outs = be.execute_executable(exe, [tb, pb] + weights + caches)
+        caches = outs[1:]
+        be.copy_to_pointer(outs[0], pinned_out.data_ptr(), 4 * batch)
+        pinned_tok.copy_(pinned_out)
+        pi += 1
+    e2e_stop = be.record_event(device)
+    e2e_ms = be.elapsed_ms(e2e_start, e2e_stop)
+    e2e_wall_ms = (time.perf_counter() - t_wall) * 1e3
+    e2e_ms = max(e2e_ms, e2e_wall_ms)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    # ---- per-kernel device times for the roofline of the dominant kernel ------------
+    exe.set_profiling(True)
+    per_type = {}
+    reps = 3
+    desc = exe.describe()["kernel_plan"]["steps"]
+    acc = np.zeros(len(desc))
+    for _ in range(reps):
+        pbuf = be.buffer_from_host(np.array(filled + pi, np.int32), device)
+        outs = be.execute_executable(exe, [be.buffer_from_host(np.full((batch,), 1, np.int32), device), pbuf] + weights + caches)
+        caches = outs[1:]
+        acc += np.array(exe.step_times_ms())
+        pi += 1
+    exe.set_profiling(False)
+    acc /= reps
+    esize = 2
+    stream_bytes = stream_ms = 0.0
+    for st, t in zip(desc, acc):
+        label = st["type"] + (f"/path{st['path']}" if st["type"] == "dot" else ("/row" if st.get("row") else ""))
+        per_type.setdefault(label, [0, 0.0])
+        per_type[label][0] += 1
+        per_type[label][1] += float(t)
+        if st["type"] == "dot" and st["path"] == 1 and st["b0"] * st["b1"] == 1:
+            stream_bytes += st["k"] * st["n"] * esize + st["m"] * (st["k"] + st["n"]) * esize
+            stream_ms += float(t)
+    peak, peak_kind = measured_peaks()
+    step_ms = ms / args.steps
+    kv_mid = filled + args.warmup + args.steps // 2
+    alg = algorithmic_bytes(cfg, batch, kv_mid, world)
+    achieved = stream_bytes / (stream_ms * 1e-3) / 1e9 if stream_ms > 0 else 0.0
+    result = {
+        "metric": "decode tok/s + % HBM roofline: 8B-shape on 1 GPU, 70B-shape TP 2/4/8",
+        "value": batch * args.steps / (ms * 1e-3),
+        "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload, "batch": batch, "kv_prefill": filled, "kv_buffer": max_len, "layers": cfg.layers,
+                   "parallelism": f"tp{world}", "l2": "inputs (weights) exceed L2 by >100x; no flush needed",
+                   "weights": "N(0,0.02) generated on device by seeded plans"},
+        "e2e": {"value": batch * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * batch + 4,
+                "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "stream_kn_kernel (weight-streaming contraction)", "peak_kind": f"of {peak_kind}",
+                     "launches_per_step": sum(1 for s in desc if s["type"] == "dot" and s["path"] == 1),
+                     "whole_step": {"algorithmic_bytes": alg, "achieved": alg / (step_ms * 1e-3) / 1e9,
+                                    "frac": alg / (step_ms * 1e-3) / 1e9 / peak, "frac_of_8tbs": alg / (step_ms * 1e-3) / 8e12}},
+        "clocks": clocks,
+        "kernel_time_ms_per_step": {k: {"launches": v[0], "ms": round(v[1], 4)} for k, v in sorted(per_type.items())},
+        "compile_s": round(compile_s, 2), "setup_s": round(setup_s, 2),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(llama.LLAMA3_8B, 1, filled, budget_layers=args.cpu_layers)
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(cfg, batch, filled, budget_layers=2, steps=2):
+    """Times the CPU plan interpreter (float32 BLAS contractions, all host threads) on a truncated copy of the
+    workload: `budget_layers` decoder layers plus the full LM head, then scales the layer time to the full depth."""
+    import dataclasses
+
+    from oracle import plan_interp
+
+    small = dataclasses.replace(cfg, layers=budget_layers)
+    builder, names = llama.build_decode_step(small, batch, filled + 64)
+    weights = llama.make_weights(small, seed=0, threads=os.cpu_count() or 8)
+    caches = llama.make_kv_cache(small, batch, filled + 64, filled)
+    wlist = [weights[n] for n in names[2:2 + len(weights)]]
+    cache = {}
+    tok = np.full((batch,), 1, np.int32)
+
+    def run(b, w, c, n):
+        nonlocal tok
+        t0 = time.perf_counter()
+        for i in range(n):
+            outs = plan_interp.run_plan(b, [tok, np.array(filled + i, np.int32)] + w + c, fast_dot=True, weight_cache=cache)
+            tok, c = outs[0], list(outs[1:])
+        return (time.perf_counter() - t0) / n
+
+    run(builder, wlist, caches, 1)  # warm-up: widens and caches the weights
+    t_small = run(builder, wlist, caches, steps)
+    # head-only program to separate the per-layer cost from the fixed cost
+    zero = dataclasses.replace(cfg, layers=0)
+    b0, n0 = llama.build_decode_step(zero, batch, filled + 64)
+    w0 = [weights[n] for n in n0[2:]]
+    cache.clear()
+    run(b0, w0, [], 1)
+    t_head = run(b0, w0, [], steps)
+    per_layer = max(t_small - t_head, 0.0) / budget_layers
+    full = t_head + per_layer * cfg.layers
+    return {"value": batch / full, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{budget_layers} of {cfg.layers} layers + full LM head, {steps} tokens, layer time scaled linearly; "
+                      f"NumPy plan interpreter with f32 BLAS contractions ({t_small:.3f} s/token sample, {t_head:.3f} s head)"}
+
+
+def run_reference(args):
+    """CPU arm: the plan interpreter (the stand-in for `jax.jit(..., backend='cpu')`, which is not installed) on the
+    same workload, every step a bounded sample."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg, batch, filled = (llama.LLAMA3_8B, 1, 2048) if world == 1 else (llama.LLAMA3_70B, 32, 4096)
+    base = cpu_baseline(cfg, batch, filled, budget_layers=args.cpu_layers, steps=max(1, min(args.steps, 2)))
+    workload = ("llama3-8b-shape bf16 decode batch 1, KV prefilled 2048" if world == 1
+                else f"llama3-70b-shape bf16 decode batch 32, KV 4096, TP={world}")
+    line = {
+        "impl": "reference", "metric": "decode tok/s + % HBM roofline: 8B-shape on 1 GPU, 70B-shape TP 2/4/8",
+        "value": base["value"], "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * batch / base["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": {"workload": workload, "batch": batch, "kv_prefill": filled},
+        "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="truncate the decoder (debugging only; changes the workload)")
+    ap.add_argument("--cpu-layers", type=int, default=2, help="decoder layers in the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -73,6 +73,7 @@ typedef struct PjrtxB200Plan PjrtxB200Plan;
 typedef struct PjrtxB200Executable PjrtxB200Executable;
 typedef struct PjrtxB200ExecutionEvent PjrtxB200ExecutionEvent;
 typedef struct PjrtxB200AsyncHostToDeviceTransfer PjrtxB200AsyncHostToDeviceTransfer;
+typedef struct PjrtxB200DeviceEvent PjrtxB200DeviceEvent;
 
 /* Replaces PjrtxMlxMetalDeviceInfo (api.h:12-18). */
 typedef struct PjrtxB200DeviceInfo {
@@ -175,6 +176,14 @@ int pjrtx_b200_device_memory_stats(int device_ordinal, PjrtxB200MemoryStats *out
 /* Blocks until everything queued on the device's stream is done (mlx synchronize, api.cc:1512-1520). */
 int pjrtx_b200_device_synchronize(int device_ordinal);
 
+/* Device-side timing on the stream every buffer and executable of the device uses. The reference measures the same
+ * interval on the host around a forced device sync (PJRTX_PROFILE_DEVICE_SYNC, src/backend/mlx_metal/api.cc:65-75,
+ * PjrtxMlxMetalProgramExecuteProfile.device_sync_wait_us, api.h:25-32). `record` enqueues an event; `elapsed_ms`
+ * waits for `stop` and returns the device time between the two. */
+PjrtxB200DeviceEvent *pjrtx_b200_device_event_record(int device_ordinal);
+int pjrtx_b200_device_event_elapsed_ms(PjrtxB200DeviceEvent *start, PjrtxB200DeviceEvent *stop, double *out_ms);
+void pjrtx_b200_device_event_destroy(PjrtxB200DeviceEvent *event);
+
 /* ---- buffers ----------------------------------------------------------- */
 /* pjrtx_mlx_metal_buffer_from_host_typed (api.h:208-211); Backend.bufferFromHost (backend.zig:104-106).
  * The host memory may be reused as soon as the call returns. */
@@ -266,6 +275,12 @@ void pjrtx_b200_execution_event_destroy(PjrtxB200ExecutionEvent *event);
 /* Backend.executableStats (backend.zig:146). Set out->struct_size before the call. */
 int pjrtx_b200_executable_stats(PjrtxB200Executable *executable, PjrtxB200ExecutableStats *out);
 uint64_t pjrtx_b200_executable_describe(PjrtxB200Executable *executable, char *out, uint64_t capacity);
+/* Per-step device times (the reference's `backend_schedule_item` profile events, src/backend/mlx_metal/
+ * profiling_writer.zig:160). While enabled, executions run the step list without graph replay and time every step
+ * with a CUDA event pair; step_times copies the latest execution's durations (ms, step order) and returns the
+ * step count. */
+int pjrtx_b200_executable_set_profiling(PjrtxB200Executable *executable, int enabled);
+uint64_t pjrtx_b200_executable_step_times(PjrtxB200Executable *executable, float *out_ms, uint64_t capacity);
 /* Backend.destroyExecutable (backend.zig:148). */
 void pjrtx_b200_executable_destroy(PjrtxB200Executable *executable);
 

@@ -251,8 +251,40 @@ def _sdpa(q, k, v, token) -> np.ndarray:
     return out if has_batch else out[0]
 
 
-def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce=None) -> List[np.ndarray]:
-    """Evaluates the recorded plan on host arrays and returns its outputs (storage dtypes)."""
+def _dot_general_f32(a, b, ins, cache, key):
+    """BLAS path for the timed CPU baseline: operands widened to f32 (the widened copy of a parameter is cached
+    across calls, as a CPU backend would keep its weights), f32 accumulate, any layout via einsum."""
+    lb, rb = ins.attrs.get("lhs_batch_dimensions", []), ins.attrs.get("rhs_batch_dimensions", [])
+    lc, rc = ins.attrs["lhs_contracting_dimensions"], ins.attrs["rhs_contracting_dimensions"]
+    bf = cache.get(key) if cache is not None and key is not None else None
+    if bf is None:
+        bf = np.asarray(b).astype(np.float32)
+        if cache is not None and key is not None:
+            cache[key] = bf
+    af = np.asarray(a).astype(np.float32)
+    if not lb and a.ndim == 2 and b.ndim == 2 and lc == [1] and rc == [0]:
+        return af @ bf
+    lf = [d for d in range(a.ndim) if d not in lb and d not in lc]
+    rf = [d for d in range(b.ndim) if d not in rb and d not in rc]
+    letters = iter("abcdefghijklmnopqrstuvwxyz")
+    la, lbl, out = [None] * a.ndim, [None] * b.ndim, []
+    for x, y in zip(lb, rb):
+        c = next(letters); la[x] = c; lbl[y] = c; out.append(c)
+    for x, y in zip(lc, rc):
+        c = next(letters); la[x] = c; lbl[y] = c
+    for x in lf:
+        c = next(letters); la[x] = c; out.append(c)
+    for y in rf:
+        c = next(letters); lbl[y] = c; out.append(c)
+    return np.einsum(f"{''.join(la)},{''.join(lbl)}->{''.join(out)}", af, bf, optimize=True)
+
+
+def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce=None, fast_dot: bool = False,
+             weight_cache: Dict[int, np.ndarray] = None) -> List[np.ndarray]:
+    """Evaluates the recorded plan on host arrays and returns its outputs (storage dtypes).
+
+    `fast_dot` switches contractions from float64 einsum to float32 BLAS (used only when the oracle is timed as the
+    CPU baseline); `weight_cache` keeps widened copies of parameters between calls."""
     env: Dict[int, np.ndarray] = {}
     assert len(arguments) == len(builder.parameter_ids)
     for vid, arr in zip(builder.parameter_ids, arguments):
@@ -335,7 +367,11 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
             ids = np.clip(x[1].astype(np.int64).reshape(-1), 0, x[0].shape[0] - 1)
             r = x[0][ids].reshape(dims)
         elif k == "dot_general":
-            r = _round_to(_dot_general(x[0], x[1], ins), code)
+            if fast_dot:
+                key = ins.inputs[1] if ins.inputs[1] in builder.parameter_ids else None
+                r = _round_to(_dot_general_f32(x[0], x[1], ins, weight_cache, key), code)
+            else:
+                r = _round_to(_dot_general(x[0], x[1], ins), code)
         elif k in P.REDUCE and len(ins.outputs) == 1:
             axes = tuple(ins.attrs["reduce_dimensions"])
             src = builder.values[ins.inputs[0]].dtype

@@ -83,6 +83,9 @@ SYMBOLS = {
     "pjrtx_b200_copy_devices": (ctypes.c_int, [ctypes.POINTER(DeviceInfo), ctypes.c_int]),
     "pjrtx_b200_device_memory_stats": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(MemoryStats)]),
     "pjrtx_b200_device_synchronize": (ctypes.c_int, [ctypes.c_int]),
+    "pjrtx_b200_device_event_record": (_P, [ctypes.c_int]),
+    "pjrtx_b200_device_event_elapsed_ms": (ctypes.c_int, [_P, _P, ctypes.POINTER(ctypes.c_double)]),
+    "pjrtx_b200_device_event_destroy": (None, [_P]),
     "pjrtx_b200_buffer_from_host_typed": (_P, [ctypes.c_int, _P, ctypes.c_uint64, ctypes.c_int, _I64P, ctypes.c_uint64]),
     "pjrtx_b200_buffer_zeros": (_P, [ctypes.c_int, ctypes.c_int, _I64P, ctypes.c_uint64]),
     "pjrtx_b200_buffer_clone": (_P, [_P]),
@@ -123,6 +126,8 @@ SYMBOLS = {
     "pjrtx_b200_execution_event_destroy": (None, [_P]),
     "pjrtx_b200_executable_stats": (ctypes.c_int, [_P, ctypes.POINTER(ExecutableStats)]),
     "pjrtx_b200_executable_describe": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
+    "pjrtx_b200_executable_set_profiling": (ctypes.c_int, [_P, ctypes.c_int]),
+    "pjrtx_b200_executable_step_times": (ctypes.c_uint64, [_P, ctypes.POINTER(ctypes.c_float), ctypes.c_uint64]),
     "pjrtx_b200_executable_destroy": (None, [_P]),
     "pjrtx_b200_register_custom_call": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int]),
     "pjrtx_b200_unregister_custom_call": (None, [ctypes.c_char_p]),
@@ -225,6 +230,15 @@ class Executable:
     def describe(self) -> dict:
         return json.loads(_text(self._lib, self._lib.pjrtx_b200_executable_describe, self.handle))
 
+    def set_profiling(self, enabled: bool) -> None:
+        self._lib.pjrtx_b200_executable_set_profiling(self.handle, 1 if enabled else 0)
+
+    def step_times_ms(self) -> List[float]:
+        n = self._lib.pjrtx_b200_executable_step_times(self.handle, None, 0)
+        buf = (ctypes.c_float * max(int(n), 1))()
+        self._lib.pjrtx_b200_executable_step_times(self.handle, buf, n)
+        return [buf[i] for i in range(int(n))]
+
     def destroy(self):
         if self.handle:
             self._lib.pjrtx_b200_executable_destroy(self.handle)
@@ -268,6 +282,22 @@ class Backend:
         if not self.lib.pjrtx_b200_device_memory_stats(device, ctypes.byref(m)):
             raise BackendError("InvalidDeviceCount", self._err())
         return {n: getattr(m, n) for n, _ in MemoryStats._fields_}
+
+    def record_event(self, device: int = 0):
+        """Enqueues a timing event on the device's stream; pair two of them with `elapsed_ms`."""
+        h = self.lib.pjrtx_b200_device_event_record(device)
+        if not h:
+            raise BackendError("CommandSubmissionFailed", self._err())
+        return h
+
+    def elapsed_ms(self, start, stop, destroy: bool = True) -> float:
+        out = ctypes.c_double(0.0)
+        if not self.lib.pjrtx_b200_device_event_elapsed_ms(start, stop, ctypes.byref(out)):
+            raise BackendError("CommandSubmissionFailed", self._err())
+        if destroy:
+            self.lib.pjrtx_b200_device_event_destroy(start)
+            self.lib.pjrtx_b200_device_event_destroy(stop)
+        return out.value
 
     def synchronize(self, device: int = 0) -> None:
         if not self.lib.pjrtx_b200_device_synchronize(device):

@@ -27,6 +27,10 @@ struct PjrtxB200ExecutionEvent {
   int device;
   cudaEvent_t event;
 };
+struct PjrtxB200DeviceEvent {
+  int device;
+  cudaEvent_t event;
+};
 struct PjrtxB200AsyncHostToDeviceTransfer {
   int device;
   int dtype;
@@ -116,6 +120,29 @@ int pjrtx_b200_device_memory_stats(int device_ordinal, PjrtxB200MemoryStats* out
 int pjrtx_b200_device_synchronize(int device_ordinal) {
   GUARD_INT(Device* d = get_device(device_ordinal); if (!d) return 0; cudaSetDevice(d->ordinal);
             return check_cuda(cudaStreamSynchronize(d->stream), "cudaStreamSynchronize") ? 1 : 0;)
+}
+
+PjrtxB200DeviceEvent* pjrtx_b200_device_event_record(int device_ordinal) {
+  GUARD_PTR(Device* d = get_device(device_ordinal); if (!d) return nullptr; cudaSetDevice(d->ordinal);
+            auto* ev = new PjrtxB200DeviceEvent{device_ordinal, nullptr};
+            if (!check_cuda(cudaEventCreate(&ev->event), "cudaEventCreate") ||
+                !check_cuda(cudaEventRecord(ev->event, d->stream), "cudaEventRecord")) {
+              if (ev->event) cudaEventDestroy(ev->event);
+              delete ev;
+              return nullptr;
+            } return ev;)
+}
+
+int pjrtx_b200_device_event_elapsed_ms(PjrtxB200DeviceEvent* start, PjrtxB200DeviceEvent* stop, double* out_ms) {
+  GUARD_INT(if (!start || !stop || !out_ms) return 0; if (!check_cuda(cudaEventSynchronize(stop->event), "cudaEventSynchronize")) return 0;
+            float ms = 0.f; if (!check_cuda(cudaEventElapsedTime(&ms, start->event, stop->event), "cudaEventElapsedTime")) return 0;
+            *out_ms = ms; return 1;)
+}
+
+void pjrtx_b200_device_event_destroy(PjrtxB200DeviceEvent* event) {
+  if (!event) return;
+  if (event->event) cudaEventDestroy(event->event);
+  delete event;
 }
 
 PjrtxB200Buffer* pjrtx_b200_buffer_from_host_typed(int device_ordinal, const void* data, uint64_t byte_size, int dtype,
@@ -418,6 +445,15 @@ int pjrtx_b200_executable_stats(PjrtxB200Executable* executable, PjrtxB200Execut
       r.graph_capture_count = s.graph_capture_count; r.graph_launch_count = s.graph_launch_count;
       r.kernel_launch_total = s.kernel_launch_total;
       uint64_t n = out->struct_size ? std::min<uint64_t>(out->struct_size, sizeof r) : sizeof r; memcpy(out, &r, n); return 1;)
+}
+
+int pjrtx_b200_executable_set_profiling(PjrtxB200Executable* executable, int enabled) {
+  GUARD_INT(if (!executable || !executable->exe) return 0; executable_set_profiling(executable->exe, enabled != 0); return 1;)
+}
+
+uint64_t pjrtx_b200_executable_step_times(PjrtxB200Executable* executable, float* out_ms, uint64_t capacity) {
+  GUARD_INT(if (!executable || !executable->exe) return 0; std::vector<float> t = executable_step_times(executable->exe);
+            for (uint64_t k = 0; k < t.size() && k < capacity && out_ms; k++) out_ms[k] = t[k]; return t.size();)
 }
 
 uint64_t pjrtx_b200_executable_describe(PjrtxB200Executable* executable, char* out, uint64_t capacity) {

@@ -748,6 +748,9 @@ struct Executable {
   std::vector<DeviceState> devices;
   ExecutableStats stats;
   bool use_graph = false;
+  bool profiling = false;
+  std::vector<float> step_ms;
+  std::vector<cudaEvent_t> step_events;
   std::mutex mu;
 };
 
@@ -784,10 +787,22 @@ struct Pointers {
   }
 };
 
-bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* launches, std::string* error) {
+bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* launches, std::string* error,
+               bool timed = false) {
   Device* dev = ds.dev;
   const KernelPlan& kp = exe->kp;
+  if (timed) {
+    while (exe->step_events.size() < kp.steps.size() + 1) {
+      cudaEvent_t e;
+      cudaEventCreate(&e);
+      exe->step_events.push_back(e);
+    }
+    cudaEventRecord(exe->step_events[0], dev->stream);
+  }
+  size_t step_index = 0;
   for (const Step& st : kp.steps) {
+    if (timed && step_index > 0) cudaEventRecord(exe->step_events[step_index], dev->stream);
+    step_index++;
     switch (st.type) {
       case Step::kFused: {
         std::vector<void*> addr;
@@ -865,10 +880,26 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
     *error = std::string("kernel launch failed: ") + cudaGetErrorString(e);
     return false;
   }
+  if (timed) {
+    cudaEventRecord(exe->step_events[kp.steps.size()], dev->stream);
+    cudaEventSynchronize(exe->step_events[kp.steps.size()]);
+    exe->step_ms.assign(kp.steps.size(), 0.f);
+    for (size_t k = 0; k < kp.steps.size(); k++) cudaEventElapsedTime(&exe->step_ms[k], exe->step_events[k], exe->step_events[k + 1]);
+  }
   return true;
 }
 
 }  // namespace
+
+void executable_set_profiling(Executable* exe, bool enabled) {
+  std::lock_guard<std::mutex> lock(exe->mu);
+  exe->profiling = enabled;
+}
+
+std::vector<float> executable_step_times(Executable* exe) {
+  std::lock_guard<std::mutex> lock(exe->mu);
+  return exe->step_ms;
+}
 
 Executable* compile_executable(const Plan& plan, const std::vector<int>& device_ordinals, std::string* error) {
   if (device_ordinals.empty()) {
@@ -1011,7 +1042,7 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
       if (b) buffer_free(b);
   };
 
-  if (exe->use_graph) {
+  if (exe->use_graph && !exe->profiling) {
     // Small parameters are staged into fixed slots; the graph reads the slots.
     std::vector<void*> graph_ptrs = param_ptrs;
     uint64_t dynamic_inputs = 0;
@@ -1083,7 +1114,7 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
       ptr.fresh[r] = b->ptr;
       outs[o] = b;
     }
-    if (!run_steps(exe, ds, ptr, &launches, error)) {
+    if (!run_steps(exe, ds, ptr, &launches, error, exe->profiling)) {
       cleanup();
       return false;
     }
@@ -1175,6 +1206,8 @@ void destroy_executable(Executable* exe) {
   for (DeviceState& ds : exe->devices) {
     cudaSetDevice(ds.dev->ordinal);
     if (ds.graph) cudaGraphExecDestroy(ds.graph);
+    for (cudaEvent_t e : exe->step_events) cudaEventDestroy(e);
+    exe->step_events.clear();
     for (size_t k = 0; k < ds.constants.size(); k++)
       device_free(ds.dev, ds.constants[k], exe->kp.plan.instructions[exe->kp.constants[k]].literal.size());
     device_free(ds.dev, ds.arena, exe->kp.arena_bytes);

@@ -87,6 +87,12 @@ Executable* compile_executable(const Plan& plan, const std::vector<int>& device_
 bool execute_executable(Executable* exe, size_t device_index, Buffer* const* args, size_t nargs,
                         std::vector<Buffer*>* outputs, std::string* error);
 ExecutableStats executable_stats(Executable* exe);
+// Per-step device times: when enabled, the next executions run the step list directly (no graph replay) with a
+// CUDA event pair around every step; step_times returns the durations of the latest such execution in
+// milliseconds, in step order (the reference prints the same information as `backend_schedule_item` profile
+// events, src/backend/mlx_metal/profiling_writer.zig:160).
+void executable_set_profiling(Executable* exe, bool enabled);
+std::vector<float> executable_step_times(Executable* exe);
 std::string executable_describe(Executable* exe);
 void destroy_executable(Executable* exe);
 
