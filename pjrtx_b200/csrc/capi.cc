@@ -119,7 +119,7 @@ int pjrtx_b200_device_memory_stats(int device_ordinal, PjrtxB200MemoryStats* out
 
 int pjrtx_b200_device_synchronize(int device_ordinal) {
   GUARD_INT(Device* d = get_device(device_ordinal); if (!d) return 0; cudaSetDevice(d->ordinal);
-            return check_cuda(cudaStreamSynchronize(d->stream), "cudaStreamSynchronize") ? 1 : 0;)
+            if (!check_cuda(cudaStreamSynchronize(d->stream), "cudaStreamSynchronize")) return 0; return check_device_flag(d) ? 1 : 0;)
 }
 
 PjrtxB200DeviceEvent* pjrtx_b200_device_event_record(int device_ordinal) {

@@ -59,9 +59,21 @@ Device* get_device(int ordinal) {
   dev->staging_size = 1 << 20;
   if (!check_cuda(cudaMallocHost((void**)&dev->staging, dev->staging_size), "cudaMallocHost")) return nullptr;
   cudaEventCreateWithFlags(&dev->staging_wrap_event, cudaEventDisableTiming);
+  if (!check_cuda(cudaHostAlloc((void**)&dev->error_flag_host, sizeof(int), cudaHostAllocMapped), "cudaHostAlloc")) return nullptr;
+  *dev->error_flag_host = 0;
+  if (!check_cuda(cudaHostGetDevicePointer((void**)&dev->error_flag_dev, dev->error_flag_host, 0), "cudaHostGetDevicePointer")) return nullptr;
   Device* raw = dev.get();
   g_devices[ordinal] = std::move(dev);
   return raw;
+}
+
+bool check_device_flag(Device* dev) {
+  if (!dev->error_flag_host) return true;
+  int code = *(volatile int*)dev->error_flag_host;
+  if (code == 0) return true;
+  *(volatile int*)dev->error_flag_host = 0;
+  set_last_error("a kernel on device %d gave up a bounded wait (code %d); results of this stream are invalid", dev->ordinal, code);
+  return false;
 }
 
 void* device_malloc(Device* dev, uint64_t bytes) {
@@ -167,6 +179,7 @@ bool buffer_to_host(Buffer* b, void* dst, uint64_t dst_size) {
   if (b->bytes == 0) return true;
   if (!check_cuda(cudaMemcpyAsync(dst, b->ptr, b->bytes, cudaMemcpyDeviceToHost, dev->stream), "cudaMemcpyAsync d2h")) return false;
   if (!check_cuda(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize")) return false;
+  if (!check_device_flag(dev)) return false;
   dev->d2h_bytes += b->bytes;
   return true;
 }

@@ -28,6 +28,9 @@ struct Device {
   uint8_t* staging = nullptr;
   size_t staging_size = 0, staging_head = 0;
   cudaEvent_t staging_wrap_event = nullptr;
+  // Written by kernels whose bounded waits give up (host-mapped so the host reads it without a copy).
+  int* error_flag_host = nullptr;
+  int* error_flag_dev = nullptr;
   // Tensor-parallel communicator (void* = ncclComm_t), set by comm_init.
   void* comm = nullptr;
   int comm_rank = 0, comm_world = 1;
@@ -39,6 +42,8 @@ struct Device {
 int device_count();                 // 0 when no CUDA device is usable
 Device* get_device(int ordinal);    // nullptr + last_error on failure
 bool check_cuda(cudaError_t e, const char* what);
+// After a stream synchronize: false (with last_error set) when a kernel reported a timed-out device-side wait.
+bool check_device_flag(Device* dev);
 
 struct Buffer {
   int device = 0;

@@ -605,6 +605,33 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     i++;
   }
 
+  // Adjacent streaming contractions that read the same lhs become one launch
+  // (q/k/v and gate/up projections).
+  {
+    std::vector<Step> merged;
+    for (Step& st : kp->steps) {
+      Step* prev = merged.empty() ? nullptr : &merged.back();
+      bool can = prev && prev->type == Step::kDot && st.type == Step::kDot && prev->dot_scratch.path == 1 &&
+                 st.dot_scratch.path == 1 && prev->inputs[0] == st.inputs[0] && prev->dot.b0 * prev->dot.b1 == 1 &&
+                 st.dot.b0 * st.dot.b1 == 1 && prev->dot.m == st.dot.m && prev->dot.k == st.dot.k &&
+                 prev->dot.dtype == st.dot.dtype && prev->dot.lhs_m == st.dot.lhs_m && prev->dot.lhs_k == st.dot.lhs_k &&
+                 std::max<size_t>(prev->dot_group.size(), 1) < (size_t)kDotGroupMax;
+      if (can)
+        for (uint32_t o : prev->outputs) can &= (o != st.inputs[1]);
+      if (!can) {
+        merged.push_back(std::move(st));
+        continue;
+      }
+      if (prev->dot_group.empty()) prev->dot_group.push_back(prev->dot);
+      prev->dot_group.push_back(st.dot);
+      prev->nodes.push_back(st.nodes[0]);
+      prev->inputs.push_back(st.inputs[1]);
+      prev->outputs.push_back(st.outputs[0]);
+      prev->dot_scratch = dot_group_plan(prev->dot_group.data(), (int)prev->dot_group.size(), sm_count);
+    }
+    kp->steps = std::move(merged);
+  }
+
   // Storage: parameters, constants, arena intervals for everything produced by a step.
   kp->storage.assign(nv, Storage{});
   for (size_t p = 0; p < kp->params.size(); p++) kp->storage[kp->params[p]] = Storage{Storage::kParameter, 0, (uint32_t)p};
@@ -656,17 +683,32 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     }
   }
   kp->arena_bytes = high;
+  // Contractions whose rhs no step ever writes may start copying it before their predecessor finishes.
+  {
+    std::set<uint32_t> written;
+    for (const Step& st : kp->steps)
+      for (uint32_t r : st.outputs) written.insert(r);
+    for (Step& st : kp->steps) {
+      if (st.type != Step::kDot) continue;
+      bool ok = true;
+      for (size_t g = 1; g < st.inputs.size(); g++) {
+        const Storage& sg = kp->storage[st.inputs[g]];
+        ok &= (sg.kind == Storage::kParameter || sg.kind == Storage::kConstant) && !written.count(st.inputs[g]);
+      }
+      st.early_rhs = ok;
+    }
+  }
   // Scratch for split-K partials and their counters (counters first: they must start at zero).
   uint64_t scratch = 0;
   for (Step& st : kp->steps)
-    if (st.type == Step::kDot && st.dot_scratch.ksplit > 1) {
+    if (st.type == Step::kDot && st.dot_scratch.counter_bytes) {
       st.counter_offset = scratch;
       scratch += align_up(st.dot_scratch.counter_bytes);
     }
   uint64_t counters_end = scratch;
   uint64_t partial_max = 0;
   for (Step& st : kp->steps)
-    if (st.type == Step::kDot && st.dot_scratch.ksplit > 1) {
+    if (st.type == Step::kDot && st.dot_scratch.partial_bytes) {
       st.scratch_offset = counters_end;  // partials are consumed inside the launch that wrote them: one shared region
       partial_max = std::max(partial_max, align_up(st.dot_scratch.partial_bytes));
     }
@@ -704,9 +746,14 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
         s += ",\"source\":\"" + esc + "\"";
       }
     } else if (st.type == Step::kDot) {
-      s += strfmt(",\"path\":%d,\"ksplit\":%d,\"b0\":%lld,\"b1\":%lld,\"m\":%lld,\"n\":%lld,\"k\":%lld", st.dot_scratch.path,
-                  st.dot_scratch.ksplit, (long long)st.dot.b0, (long long)st.dot.b1, (long long)st.dot.m, (long long)st.dot.n,
-                  (long long)st.dot.k);
+      long long n_total = st.dot.n;
+      if (st.dot_group.size() > 1) {
+        n_total = 0;
+        for (const DotShape& d : st.dot_group) n_total += d.n;
+      }
+      s += strfmt(",\"path\":%d,\"tma\":%d,\"grid\":%d,\"ksplit\":%d,\"b0\":%lld,\"b1\":%lld,\"m\":%lld,\"n\":%lld,\"k\":%lld,\"group\":%zu",
+                  st.dot_scratch.path, st.dot_scratch.tma, st.dot_scratch.grid, st.dot_scratch.ksplit, (long long)st.dot.b0, (long long)st.dot.b1, (long long)st.dot.m,
+                  n_total, (long long)st.dot.k, std::max<size_t>(st.dot_group.size(), 1));
     } else if (st.type == Step::kSliceUpdate) {
       s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");
     }
@@ -748,6 +795,7 @@ struct Executable {
   std::vector<DeviceState> devices;
   ExecutableStats stats;
   bool use_graph = false;
+  bool pdl = false;  // programmatic dependent launch between consecutive kernels
   bool profiling = false;
   std::vector<float> step_ms;
   std::vector<cudaEvent_t> step_events;
@@ -820,10 +868,22 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         break;
       }
       case Step::kDot: {
-        void* partials = st.dot_scratch.ksplit > 1 ? (char*)ds.scratch + st.scratch_offset : nullptr;
-        void* counters = st.dot_scratch.ksplit > 1 ? (char*)ds.scratch + st.counter_offset : nullptr;
-        int n = dot_launch(st.dot, st.dot_scratch, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.outputs[0]), partials,
-                           counters, dev->stream);
+        void* partials = st.dot_scratch.partial_bytes ? (char*)ds.scratch + st.scratch_offset : nullptr;
+        void* counters = st.dot_scratch.counter_bytes ? (char*)ds.scratch + st.counter_offset : nullptr;
+        int n;
+        if (st.dot_group.size() > 1) {
+          const void* rhs[kDotGroupMax];
+          void* out[kDotGroupMax];
+          for (size_t g = 0; g < st.dot_group.size(); g++) {
+            rhs[g] = ptr.of(st.inputs[1 + g]);
+            out[g] = ptr.of(st.outputs[g]);
+          }
+          n = dot_group_launch(st.dot_group.data(), (int)st.dot_group.size(), st.dot_scratch, ptr.of(st.inputs[0]), rhs, out,
+                               partials, counters, dev->error_flag_dev, st.early_rhs, exe->pdl, dev->stream);
+        } else {
+          n = dot_launch(st.dot, st.dot_scratch, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.outputs[0]), partials,
+                         counters, dev->error_flag_dev, st.early_rhs, exe->pdl, dev->stream);
+        }
         if (n == 0) {
           *error = "dot_general kernel refused the shape";
           return false;

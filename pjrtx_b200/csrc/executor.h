@@ -57,10 +57,12 @@ struct Step {
   FusedKernel fused;
   JitKernel* jit = nullptr;
   DotShape dot;
+  std::vector<DotShape> dot_group;  // more than one entry: contractions sharing inputs[0], launched together
   DotScratch dot_scratch;
   uint64_t scratch_offset = 0, counter_offset = 0;
   SliceUpdateShape dus;
   bool in_place = false;
+  bool early_rhs = false;  // every rhs of the contraction is a parameter or constant no step writes
   SdpaShape sdpa;
   uint64_t bytes = 0;  // kCopy / collectives
   uint64_t count = 0;

@@ -17,8 +17,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "../common.h"
 #include "kernels.h"
+#include "stream_tma.cuh"
 
 namespace pjrtx {
 
@@ -83,26 +86,45 @@ __global__ void dot_generic_kernel(DotShape s, const T* __restrict__ lhs, const 
 }
 
 // ---------------------------------------------------------------- stream_kn
-constexpr int kKnWarps = 4;
-constexpr int kKnThreads = kKnWarps * 32;
 constexpr int kKnUnroll = 8;
+constexpr int kKnChunk = 512;  // lhs elements staged in shared memory per pass
 
-template <typename T, int M>
-__global__ void __launch_bounds__(kKnThreads)
-stream_kn_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out,
-                 float* __restrict__ partials, unsigned* __restrict__ counters, int ksplit, int kslice) {
+// Up to four contractions that share lhs, m and k run as one launch: the column
+// tiles of all of them form one grid (q/k/v or gate/up projections; the reference
+// groups dots that share an lhs the same way, src/backend/mlx_metal/metal_graph_dot.zig:70-152).
+struct KnGroup {
+  int count;
+  int tile_begin[kDotGroupMax + 1];
+  const void* rhs[kDotGroupMax];
+  void* out[kDotGroupMax];
+  long long n[kDotGroupMax];
+  long long rhs_k[kDotGroupMax];
+  long long partial_offset[kDotGroupMax];  // in floats
+};
+
+template <typename T, int M, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+stream_kn_kernel(DotShape s, KnGroup grp, const T* __restrict__ lhs, float* __restrict__ partials,
+                 unsigned* __restrict__ counters, int ksplit, int kslice) {
   constexpr int V = Vec16<T>::N;
   constexpr int TILE = 32 * V;
-  __shared__ float red[kKnWarps - 1][M][TILE];
-  __shared__ T xs[M][1024];
+  constexpr int THREADS = WARPS * 32;
+  __shared__ float red[WARPS - 1][M][TILE];
+  __shared__ T xs[M][kKnChunk];
   __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int g = 0;
+#pragma unroll
+  for (int q = 1; q < kDotGroupMax; q++)
+    if (q < grp.count && (int)blockIdx.x >= grp.tile_begin[q]) g = q;
+  const int64_t n_cols = grp.n[g], ldb = grp.rhs_k[g];
   const int64_t batch = blockIdx.z, b0 = batch / s.b1, b1 = batch % s.b1;
-  const int64_t col = (int64_t)blockIdx.x * TILE + lane * V;
+  const int64_t col = (int64_t)((int)blockIdx.x - grp.tile_begin[g]) * TILE + lane * V;
   const int64_t k_begin = (int64_t)blockIdx.y * kslice;
   const int64_t k_end = min(k_begin + (int64_t)kslice, s.k);
   const T* a = lhs + b0 * s.lhs_b0 + b1 * s.lhs_b1;
-  const T* b = rhs + b0 * s.rhs_b0 + b1 * s.rhs_b1;
+  const T* b = static_cast<const T*>(grp.rhs[g]) + b0 * s.rhs_b0 + b1 * s.rhs_b1;
+  T* out = static_cast<T*>(grp.out[g]);
   const int rows = (int)min((int64_t)M, s.m);
 
   float acc[M][V];
@@ -111,36 +133,36 @@ stream_kn_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rh
 #pragma unroll
     for (int v = 0; v < V; v++) acc[m][v] = 0.f;
 
-  const bool col_ok = col < s.n;
-  for (int64_t kc = k_begin; kc < k_end; kc += 1024) {
-    const int chunk = (int)min((int64_t)1024, k_end - kc);
+  const bool col_ok = col < n_cols;
+  for (int64_t kc = k_begin; kc < k_end; kc += kKnChunk) {
+    const int chunk = (int)min((int64_t)kKnChunk, k_end - kc);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * chunk; idx += kKnThreads) {
+    for (int idx = threadIdx.x; idx < rows * chunk; idx += THREADS) {
       const int m = idx / chunk, kk = idx % chunk;
       xs[m][kk] = a[m * s.lhs_m + (kc + kk) * s.lhs_k];
     }
     __syncthreads();
     if (col_ok) {
-      const T* bp = b + (kc + warp) * s.rhs_k + col;
+      const T* bp = b + (kc + warp) * ldb + col;
       int kk = warp;
-      for (; kk + (kKnUnroll - 1) * kKnWarps < chunk; kk += kKnUnroll * kKnWarps) {
+      for (; kk + (kKnUnroll - 1) * WARPS < chunk; kk += kKnUnroll * WARPS) {
         Vec16<T> w[kKnUnroll];
 #pragma unroll
-        for (int u = 0; u < kKnUnroll; u++) w[u].raw = ld_stream(bp + (int64_t)u * kKnWarps * s.rhs_k);
-        bp += (int64_t)kKnUnroll * kKnWarps * s.rhs_k;
+        for (int u = 0; u < kKnUnroll; u++) w[u].raw = ld_stream(bp + (int64_t)u * WARPS * ldb);
+        bp += (int64_t)kKnUnroll * WARPS * ldb;
 #pragma unroll
         for (int u = 0; u < kKnUnroll; u++)
 #pragma unroll
           for (int m = 0; m < M; m++) {
-            const float x = to_f(xs[m][kk + u * kKnWarps]);
+            const float x = to_f(xs[m][kk + u * WARPS]);
 #pragma unroll
             for (int v = 0; v < V; v++) acc[m][v] = fmaf(x, w[u].get(v), acc[m][v]);
           }
       }
-      for (; kk < chunk; kk += kKnWarps) {
+      for (; kk < chunk; kk += WARPS) {
         Vec16<T> w;
         w.raw = ld_stream(bp);
-        bp += (int64_t)kKnWarps * s.rhs_k;
+        bp += (int64_t)WARPS * ldb;
 #pragma unroll
         for (int m = 0; m < M; m++) {
           const float x = to_f(xs[m][kk]);
@@ -158,6 +180,7 @@ stream_kn_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rh
       for (int v = 0; v < V; v++) red[warp - 1][m][lane * V + v] = acc[m][v];
   }
   __syncthreads();
+  float* part = partials + grp.partial_offset[g];
   if (warp == 0 && col_ok) {
 #pragma unroll
     for (int m = 0; m < M; m++)
@@ -165,25 +188,25 @@ stream_kn_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rh
       for (int v = 0; v < V; v++) {
         float t = acc[m][v];
 #pragma unroll
-        for (int w = 0; w < kKnWarps - 1; w++) t += red[w][m][lane * V + v];
+        for (int w = 0; w < WARPS - 1; w++) t += red[w][m][lane * V + v];
         acc[m][v] = t;
       }
     if (ksplit == 1) {
 #pragma unroll
       for (int m = 0; m < M; m++) {
         if (m < rows) {
-          T* o = out + b0 * s.out_b0 + b1 * s.out_b1 + m * s.out_m + col;
+          T* o = out + b0 * s.out_b0 + b1 * s.out_b1 + m * n_cols + col;
 #pragma unroll
           for (int v = 0; v < V; v++) o[v] = from_f<T>(acc[m][v]);
         }
       }
     } else {
-      float* p = partials + ((batch * ksplit + blockIdx.y) * (int64_t)M) * s.n + col;
+      float* p = part + ((batch * ksplit + blockIdx.y) * (int64_t)M) * n_cols + col;
 #pragma unroll
       for (int m = 0; m < M; m++)
         if (m < rows) {
 #pragma unroll
-          for (int v = 0; v < V; v++) p[(int64_t)m * s.n + v] = acc[m][v];
+          for (int v = 0; v < V; v++) p[(int64_t)m * n_cols + v] = acc[m][v];
         }
     }
   }
@@ -198,13 +221,23 @@ stream_kn_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rh
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < rows * TILE; idx += kKnThreads) {
+  const int64_t slice_stride = (int64_t)M * n_cols;
+  for (int idx = threadIdx.x; idx < rows * TILE; idx += THREADS) {
     const int m = idx / TILE;
-    const int64_t c = (int64_t)blockIdx.x * TILE + idx % TILE;
-    if (c >= s.n) continue;
+    const int64_t c = (int64_t)((int)blockIdx.x - grp.tile_begin[g]) * TILE + idx % TILE;
+    if (c >= n_cols) continue;
+    const float* p = part + (batch * ksplit * (int64_t)M + m) * n_cols + c;
     float t = 0.f;
-    for (int ks = 0; ks < ksplit; ks++) t += __ldcg(partials + ((batch * ksplit + ks) * (int64_t)M + m) * s.n + c);
-    out[b0 * s.out_b0 + b1 * s.out_b1 + m * s.out_m + c] = from_f<T>(t);
+    int ks = 0;
+    for (; ks + 8 <= ksplit; ks += 8) {  // loads first, then the adds in slice order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) v[u] = __ldcg(p + (int64_t)(ks + u) * slice_stride);
+#pragma unroll
+      for (int u = 0; u < 8; u++) t += v[u];
+    }
+    for (; ks < ksplit; ks++) t += __ldcg(p + (int64_t)ks * slice_stride);
+    out[b0 * s.out_b0 + b1 * s.out_b1 + m * n_cols + c] = from_f<T>(t);
   }
   if (threadIdx.x == 0) counters[batch * gridDim.x + blockIdx.x] = 0;  // ready for the next launch
 }
@@ -304,6 +337,39 @@ tile_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T*
 }
 
 template <typename T>
+int launch_group_typed(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
+                       void* const* out, void* partials, void* counters, cudaStream_t stream) {
+  constexpr int V = 16 / sizeof(T);
+  const int tile = 32 * V;
+  const DotShape& s = shapes[0];
+  const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
+  KnGroup grp{};
+  grp.count = count;
+  int tiles = 0;
+  long long poff = 0;
+  for (int g = 0; g < count; g++) {
+    grp.tile_begin[g] = tiles;
+    tiles += (int)((shapes[g].n + tile - 1) / tile);
+    grp.rhs[g] = rhs[g];
+    grp.out[g] = out[g];
+    grp.n[g] = shapes[g].n;
+    grp.rhs_k[g] = shapes[g].rhs_k;
+    grp.partial_offset[g] = poff;
+    poff += (long long)s.b0 * s.b1 * plan.ksplit * M * shapes[g].n;
+  }
+  for (int g = count; g <= kDotGroupMax; g++) grp.tile_begin[g] = tiles;
+  dim3 grid((unsigned)tiles, (unsigned)plan.ksplit, (unsigned)(s.b0 * s.b1));
+  const int kslice = (int)((s.k + plan.ksplit - 1) / plan.ksplit);
+  const T* a = static_cast<const T*>(lhs);
+  float* p = static_cast<float*>(partials);
+  unsigned* c = static_cast<unsigned*>(counters);
+#define KN(MM, WW) stream_kn_kernel<T, MM, WW><<<grid, WW * 32, 0, stream>>>(s, grp, a, p, c, plan.ksplit, kslice)
+  if (M == 1) KN(1, 8); else if (M == 2) KN(2, 8); else if (M == 4) KN(4, 8); else KN(8, 4);
+#undef KN
+  return 1;
+}
+
+template <typename T>
 int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
                  void* counters, cudaStream_t stream) {
   const T* a = static_cast<const T*>(lhs);
@@ -312,15 +378,10 @@ int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, con
   constexpr int V = 16 / sizeof(T);
   const int64_t batch = s.b0 * s.b1;
   if (plan.path == 1) {
-    const int tile = 32 * V;
-    dim3 grid((unsigned)((s.n + tile - 1) / tile), (unsigned)plan.ksplit, (unsigned)batch);
-    const int kslice = (int)((s.k + plan.ksplit - 1) / plan.ksplit);
-    float* p = static_cast<float*>(partials);
-    unsigned* c = static_cast<unsigned*>(counters);
-#define KN(MM) stream_kn_kernel<T, MM><<<grid, kKnThreads, 0, stream>>>(s, a, b, o, p, c, plan.ksplit, kslice)
-    if (s.m <= 1) KN(1); else if (s.m <= 2) KN(2); else if (s.m <= 4) KN(4); else KN(8);
-#undef KN
-    return 1;
+    const DotShape* one = &s;
+    const void* rhs_list[1] = {rhs};
+    void* out_list[1] = {out};
+    return launch_group_typed<T>(one, 1, plan, lhs, rhs_list, out_list, partials, counters, stream);
   }
   if (plan.path == 2) {
     int group = 32;
@@ -345,6 +406,161 @@ int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, con
 
 }  // namespace
 
+DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count) {
+  DotScratch p;
+  p.path = 1;
+  const DotShape& s = shapes[0];
+  const int esize = (int)dtype_size(s.dtype);
+  const int V = 16 / esize;
+  const int64_t batch = s.b0 * s.b1;
+  int64_t tiles = 0, n_total = 0;
+  for (int g = 0; g < count; g++) {
+    tiles += (shapes[g].n + 32 * V - 1) / (32 * V);
+    n_total += shapes[g].n;
+  }
+  const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
+  if (batch == 1) {
+    // Persistent TMA kernel: equal shares of (column tile, 64-row chunk) units per CTA.
+    p.tma = 1;
+    const int chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
+    const int64_t units = tiles * chunks;
+    const size_t red = (size_t)tma::kConsumerWarps * M * 32 * V * sizeof(float);
+    const bool two_per_sm = red <= 16 * 1024;
+    p.stages = two_per_sm ? 3 : (M <= 4 ? 5 : 4);
+    const int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(units, (int64_t)sm_count * (two_per_sm ? 2 : 1)));
+    p.per_cta = (units + ctas - 1) / ctas;
+    p.grid = (int)((units + p.per_cta - 1) / p.per_cta);
+    p.max_contrib = (int)((chunks + p.per_cta - 1) / p.per_cta) + 1;
+    p.smem = tma::smem_bytes(p.stages, M, 32 * V);
+    p.ksplit = p.max_contrib;
+    p.partial_bytes = (uint64_t)tiles * p.max_contrib * M * 32 * V * sizeof(float);
+    p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+    return p;
+  }
+  // About two CTAs per SM, every CTA streaming at least 256 rows of its tile.
+  const int64_t want = ((int64_t)sm_count * 2 + tiles * batch - 1) / (tiles * batch);
+  const int64_t max_split = std::max<int64_t>(1, s.k / 256);
+  p.ksplit = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, max_split), 32));
+  if (p.ksplit > 1) {
+    p.partial_bytes = (uint64_t)batch * p.ksplit * M * n_total * sizeof(float);
+    p.counter_bytes = (uint64_t)batch * tiles * sizeof(unsigned);
+  }
+  return p;
+}
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+template <typename T, int M>
+int launch_tma_m(const tma::Params& prm, const tma::Maps& maps, const DotScratch& plan, bool pdl, cudaStream_t stream) {
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(tma::stream_tma_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 0;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  cfg.blockDim = dim3(tma::kThreads);
+  cfg.dynamicSmemBytes = plan.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tma::stream_tma_kernel<T, M>, prm, maps) == cudaSuccess ? 1 : 0;
+}
+
+template <typename T>
+int launch_tma(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs, void* const* out,
+               void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int COLS = 32 * V;
+  const DotShape& s = shapes[0];
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return 0;
+  tma::Params p{};
+  tma::Maps maps{};
+  p.lhs = lhs;
+  p.lhs_m = s.lhs_m;
+  p.lhs_k = s.lhs_k;
+  p.m = (int)s.m;
+  p.k = (int)s.k;
+  p.batch = 1;
+  p.count = count;
+  int tiles = 0;
+  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  for (int g = 0; g < count; g++) {
+    p.tile_begin[g] = tiles;
+    tiles += (int)((shapes[g].n + COLS - 1) / COLS);
+    p.rhs[g] = rhs[g];
+    p.out[g] = out[g];
+    p.n[g] = shapes[g].n;
+    p.ldb[g] = shapes[g].rhs_k;
+    cuuint64_t gdim[2] = {(cuuint64_t)shapes[g].n, (cuuint64_t)s.k};
+    cuuint64_t gstride[1] = {(cuuint64_t)shapes[g].rhs_k * sizeof(T)};
+    cuuint32_t box[2] = {(cuuint32_t)COLS, (cuuint32_t)tma::kUnitRows};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&maps.map[g], dt, 2, const_cast<void*>(rhs[g]), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return 0;
+  }
+  for (int g = count; g <= tma::kGroupMax; g++) p.tile_begin[g] = tiles;
+  for (int g = count; g < tma::kGroupMax; g++) maps.map[g] = maps.map[0];
+  p.chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
+  p.units = (long long)tiles * p.chunks;
+  p.per_cta = plan.per_cta;
+  p.max_contrib = plan.max_contrib;
+  p.partials = static_cast<float*>(partials);
+  p.counters = static_cast<unsigned*>(counters);
+  p.error_flag = error_flag;
+  p.stages = plan.stages;
+  p.early_rhs = early_rhs ? 1 : 0;
+  const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
+  switch (M) {
+    case 1: return launch_tma_m<T, 1>(p, maps, plan, pdl, stream);
+    case 2: return launch_tma_m<T, 2>(p, maps, plan, pdl, stream);
+    case 4: return launch_tma_m<T, 4>(p, maps, plan, pdl, stream);
+    default: return launch_tma_m<T, 8>(p, maps, plan, pdl, stream);
+  }
+}
+
+}  // namespace
+
+int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
+                     void* const* out, void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl,
+                     cudaStream_t stream) {
+  if (count < 1 || count > kDotGroupMax) return 0;
+  if (plan.tma) {
+    switch (shapes[0].dtype) {
+      case kF32: return launch_tma<float>(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
+      case kF16: return launch_tma<__half>(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
+      case kBF16: return launch_tma<__nv_bfloat16>(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
+      default: return 0;
+    }
+  }
+  switch (shapes[0].dtype) {
+    case kF32: return launch_group_typed<float>(shapes, count, plan, lhs, rhs, out, partials, counters, stream);
+    case kF16: return launch_group_typed<__half>(shapes, count, plan, lhs, rhs, out, partials, counters, stream);
+    case kBF16: return launch_group_typed<__nv_bfloat16>(shapes, count, plan, lhs, rhs, out, partials, counters, stream);
+    default: return 0;
+  }
+}
+
 DotScratch dot_plan(const DotShape& s, int sm_count) {
   DotScratch p;
   const int esize = (int)dtype_size(s.dtype);
@@ -356,17 +572,8 @@ DotScratch dot_plan(const DotShape& s, int sm_count) {
   if (s.m <= 8 && s.rhs_n == 1 && s.n % V == 0 && aligned(s.rhs_k) && aligned(s.rhs_b0) && aligned(s.rhs_b1) &&
       batches_fit && s.k >= 1) {
     p.path = 1;
-    const int64_t tiles = (s.n + 32 * V - 1) / (32 * V);
-    // Enough CTAs to cover every SM several times, slices of at least 64 rows.
-    int64_t want = ((int64_t)sm_count * 6 + tiles * batch - 1) / (tiles * batch);
-    int64_t max_split = std::max<int64_t>(1, s.k / 64);
-    p.ksplit = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, max_split), 64));
-    if (p.ksplit > 1) {
-      const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
-      p.partial_bytes = (uint64_t)batch * p.ksplit * M * s.n * sizeof(float);
-      p.counter_bytes = (uint64_t)batch * tiles * sizeof(unsigned);
-    }
-    return p;
+    const DotShape one = s;
+    return dot_group_plan(&one, 1, sm_count);
   }
   if (s.m <= 8 && s.rhs_k == 1 && s.lhs_k == 1 && s.k % V == 0 && aligned(s.rhs_n) && aligned(s.rhs_b0) &&
       aligned(s.rhs_b1) && aligned(s.lhs_m) && aligned(s.lhs_b0) && aligned(s.lhs_b1) && batches_fit) {
@@ -382,8 +589,13 @@ DotScratch dot_plan(const DotShape& s, int sm_count) {
 }
 
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
-               void* counters, cudaStream_t stream) {
+               void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
   if (s.b0 * s.b1 * s.m * s.n == 0) return 1;
+  if (plan.path == 1 && plan.tma) {
+    const void* rhs_list[1] = {rhs};
+    void* out_list[1] = {out};
+    return dot_group_launch(&s, 1, plan, lhs, rhs_list, out_list, partials, counters, error_flag, early_rhs, pdl, stream);
+  }
   switch (s.dtype) {
     case kF32: return launch_typed<float>(s, plan, lhs, rhs, out, partials, counters, stream);
     case kF16: return launch_typed<__half>(s, plan, lhs, rhs, out, partials, counters, stream);

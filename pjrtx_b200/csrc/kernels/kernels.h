@@ -26,12 +26,28 @@ struct DotScratch {
   uint64_t counter_bytes = 0;
   int ksplit = 1;
   int path = 0;  // 0 generic, 1 streaming rhs[K,N] (N contiguous), 2 streaming rhs[N,K] (K contiguous), 3 f32 tile
+  // Path 1 without batch axes runs the TMA-fed persistent kernel (stream-K decomposition).
+  int tma = 0;
+  int grid = 0, stages = 0, max_contrib = 0;
+  long long per_cta = 0;
+  uint64_t smem = 0;
 };
+
+constexpr int kDotGroupMax = 4;
+
+// Streaming contractions (path 1) that share lhs, m, k, dtype and have no batch axes can run as one launch.
+DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count);
+// `error_flag` (device-visible int) receives a non-zero code if a bounded device-side wait gives up.
+// `early_rhs`: the rhs operands are never written by earlier work of the same stream, so their copies may start
+// before the preceding kernel has finished (programmatic dependent launch).
+int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
+                     void* const* out, void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl,
+                     cudaStream_t stream);
 
 // Chooses the kernel for a shape and sizes its scratch.
 DotScratch dot_plan(const DotShape& s, int sm_count);
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out,
-               void* partials, void* counters, cudaStream_t stream);
+               void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream);
 
 // dynamic_update_slice: writes `update` into `dst` (already holding the operand)
 // at start indices read from device scalars, clamped as StableHLO requires.

@@ -170,8 +170,11 @@ def test_decode_step_kernel_plan(backend):
     assert backend.verify_plan(b) == ""
     k = backend.describe_kernels(b)
     types = [s["type"] for s in k["steps"]]
-    # per layer: 7 projections + scores + context, two cache updates in place, and the fused groups between them
-    assert types.count("dot") == 9 * cfg.layers + 1
+    # per layer: q/k/v as one grouped launch, scores, context, o_proj, gate/up as one grouped launch, down_proj
+    dots = [s for s in k["steps"] if s["type"] == "dot"]
+    assert len(dots) == 6 * cfg.layers + 1
+    assert sum(1 for s in dots if s["group"] == 3 and s["n"] == cfg.q_dim + 2 * cfg.kv_dim) == cfg.layers
+    assert sum(1 for s in dots if s["group"] == 2 and s["n"] == 2 * cfg.ffn) == cfg.layers
     assert types.count("slice_update") == 2 * cfg.layers
     assert all(s["in_place"] for s in k["steps"] if s["type"] == "slice_update")
     fused = [s for s in k["steps"] if s["type"] == "fused"]
