@@ -212,7 +212,7 @@ def test_tensor_parallel_partition_plan(backend):
         assert types.count("all_reduce") == 2 * cfg.layers       # after o_proj and down_proj
         assert types.count("all_gather") == 1                     # vocabulary-split logits before argmax
         dots = [s for s in k["steps"] if s["type"] == "dot"]
-        assert any(s["n"] == cfg.q_dim // 2 for s in dots) and any(s["k"] == cfg.ffn // 2 for s in dots)
+        assert any(s["n"] == (cfg.q_dim + 2 * cfg.kv_dim) // 2 for s in dots) and any(s["k"] == cfg.ffn // 2 for s in dots)
 
 
 def test_execute_requires_gpu_and_fails_loudly(backend):
