@@ -296,6 +296,26 @@ int pjrtx_b200_comm_unique_id(uint8_t out_id[128]);
 int pjrtx_b200_comm_init(int device_ordinal, const uint8_t id[128], int rank, int world_size);
 void pjrtx_b200_comm_destroy(int device_ordinal);
 
+/* ---- contraction without allocation ---------------------------------------- */
+/* No counterpart in the reference. out[m, n] = lhs[m, k] . rhs[k, n] for dense row-major device pointers, 1 <= m <= 8,
+ * element type f32 / f16 / bf16, n a multiple of 16 bytes' worth of elements, rhs and out 16-byte aligned.
+ *
+ * For callers that cannot allocate device memory where they need the product: a runtime whose arena already owns all
+ * of HBM, code running under another allocator's lock, a serving loop that forbids allocator calls after start-up.
+ * The split-K scratch of the streaming kernel (f32 partial sums, per-tile counters) comes from a fixed 8 MiB + 64 KiB
+ * array inside the library image, so the call makes no cudaMalloc / cudaFree / pool call. Consequences:
+ *  - problems whose scratch does not fit are refused with a message that names the sizes (m <= 8 against rhs up to
+ *    4096 x 128256 fits);
+ *  - every GPU that loads the library holds the array until the process exits;
+ *  - all calls share the array, and it keeps the previous call's contents (the counters and the error word are
+ *    cleared on the stream before each launch): two calls that overlap on the GPU race, so keep them on one stream
+ *    or order them with events;
+ *  - the first call on a device resolves the array's address and raises the kernel's shared-memory limit; make that
+ *    first call before any stream capture begins.
+ * `stream` is a cudaStream_t (NULL = the default stream). Returns 1 on success, 0 with pjrtx_b200_last_error() set. */
+int pjrtx_b200_dot_static_scratch(int device_ordinal, int dtype, const void *lhs, const void *rhs, void *out, int64_t m,
+                                  int64_t k, int64_t n, void *stream);
+
 /* ---- generated-kernel check (no device needed) ---------------------------- */
 /* Compiles CUDA source for sm_100a with the run-time compiler; 1 when it compiles. The log goes to `out`. */
 int pjrtx_b200_compile_check(const char *source, char *out, uint64_t capacity);

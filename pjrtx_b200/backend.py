@@ -135,6 +135,8 @@ SYMBOLS = {
     "pjrtx_b200_comm_unique_id": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint8)]),
     "pjrtx_b200_comm_init": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint8), ctypes.c_int, ctypes.c_int]),
     "pjrtx_b200_comm_destroy": (None, [ctypes.c_int]),
+    "pjrtx_b200_dot_static_scratch": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _P, _P, _P, ctypes.c_int64, ctypes.c_int64,
+                                                      ctypes.c_int64, _P]),
     "pjrtx_b200_compile_check": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint64]),
 }
 
@@ -444,6 +446,20 @@ class Backend:
     def comm_init(self, device: int, unique_id: bytes, rank: int, world: int) -> None:
         buf = (ctypes.c_uint8 * 128)(*unique_id)
         if not self.lib.pjrtx_b200_comm_init(device, buf, rank, world):
+            raise BackendError("CommandSubmissionFailed", self._err())
+
+    def dot_static_scratch(self, dtype: int, lhs_ptr: int, rhs_ptr: int, out_ptr: int, m: int, k: int, n: int, device: int = 0,
+                           stream: int = 0) -> None:
+        """out[m, n] = lhs[m, k] . rhs[k, n] on raw device pointers without any device allocation.
+
+        For callers that may not allocate where they need the product (all of HBM already owned by their own arena,
+        code under another allocator's lock, allocation-free serving loops): the kernel's split-K scratch is a fixed
+        8 MiB array inside the library, shared by all calls; calls that overlap on the GPU race. Oversized problems
+        raise with the sizes in the message. Make the first call on a device outside stream capture.
+        """
+        ok = self.lib.pjrtx_b200_dot_static_scratch(device, dtype, ctypes.c_void_p(lhs_ptr), ctypes.c_void_p(rhs_ptr),
+                                                    ctypes.c_void_p(out_ptr), m, k, n, ctypes.c_void_p(stream))
+        if not ok:
             raise BackendError("CommandSubmissionFailed", self._err())
 
     def compile_check(self, source: str) -> str:

@@ -499,6 +499,11 @@ void pjrtx_b200_comm_destroy(int device_ordinal) {
   }
 }
 
+int pjrtx_b200_dot_static_scratch(int device_ordinal, int dtype, const void* lhs, const void* rhs, void* out, int64_t m, int64_t k,
+                                  int64_t n, void* stream) {
+  GUARD_INT(return stream_dot_static_scratch(device_ordinal, dtype, lhs, rhs, out, m, k, n, (cudaStream_t)stream);)
+}
+
 int pjrtx_b200_compile_check(const char* source, char* out, uint64_t capacity) {
   GUARD_INT(if (!source) return 0; std::vector<char> cubin; std::string log; bool ok = jit_compile_cubin(source, &cubin, &log);
             write_text(log, out, capacity); if (!ok) set_last_error("%s", log.c_str()); return ok ? 1 : 0;)

@@ -49,6 +49,11 @@ DotScratch dot_plan(const DotShape& s, int sm_count);
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out,
                void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream);
 
+// out[m, n] = lhs[m, k] . rhs[k, n] (dense row-major device pointers) with split-K scratch taken from a fixed
+// array in the library image instead of an allocation. 1 on success, 0 with last_error set.
+int stream_dot_static_scratch(int device, int dtype, const void* lhs, const void* rhs, void* out, int64_t m, int64_t k,
+                              int64_t n, cudaStream_t stream);
+
 // dynamic_update_slice: writes `update` into `dst` (already holding the operand)
 // at start indices read from device scalars, clamped as StableHLO requires.
 struct SliceUpdateShape {
