@@ -238,6 +238,10 @@ class Gen {
     k.source = std::string(kPreamble) + strfmt("typedef %s idx_t;\n", wide_index_ ? "long long" : "int") +
                strfmt("extern \"C\" __global__ void __launch_bounds__(%d) pjrtx_fused(%s) {\n", k.block,
                       sig.c_str()) +
+               // Programmatic dependent launch: let the next kernel of the stream start its prologue now, and wait
+               // for the previous one before the first global access.
+               "  asm volatile(\"griddepcontrol.launch_dependents;\" ::: \"memory\");\n"
+               "  asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n" +
                body + "}\n";
     k.inputs = inputs_;
     k.outputs = outputs_;

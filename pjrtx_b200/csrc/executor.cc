@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cstdlib>
+#include <cmath>
 #include <cstring>
 #include <map>
 #include <set>
@@ -347,6 +348,7 @@ bool lowering_issue(const Plan& plan, size_t device_count, Issue* out) {
       }
       case Kind::custom_call: {
         SdpaShape s;
+        if (ins.custom_call_target == "pjrtx.b200.internal.attention_decode") break;
         if (is_sdpa_target(ins.custom_call_target)) {
           if (!analyze_sdpa(plan, ins, &s, &why)) {
             *out = Issue{(long)i, -1, why, ins.custom_call_target};
@@ -384,6 +386,210 @@ bool lowering_issue(const Plan& plan, size_t device_count, Issue* out) {
 // ---------------------------------------------------------------------------
 // Kernel planning.
 
+// ---------------------------------------------------------------------------
+// Decode-attention recognition: dot_general(q, K) -> [convert] -> * scale -> select(key <= pos, ., -inf) -> max ->
+// exp(. - max) -> sum -> / sum -> [convert] -> dot_general(., V) becomes one internal attention call, so the split-KV
+// kernel reads the cache once instead of three kernels round-tripping scores and probabilities through memory.
+// Anything that deviates from this exact dataflow is left alone and runs as separate steps.
+
+const char* kAttnDecodeTarget = "pjrtx.b200.internal.attention_decode";
+
+struct AttnMatch {
+  size_t d1 = 0, d2 = 0;
+  std::vector<size_t> consumed;
+  uint32_t q = 0, k = 0, v = 0, pos = 0, out = 0;
+  float scale = 1.f;
+};
+
+void fuse_decode_attention(Plan* plan) {
+  const size_t nv = plan->values.size();
+  std::vector<long> producer(nv, -1);
+  std::vector<std::vector<size_t>> users(nv);
+  std::vector<char> is_output(nv, 0);
+  for (uint32_t id : plan->output_ids) is_output[id] = 1;
+  for (size_t i = 0; i < plan->instructions.size(); i++) {
+    for (uint32_t v : plan->instructions[i].inputs) users[v].push_back(i);
+    for (uint32_t v : plan->instructions[i].outputs) producer[v] = (long)i;
+  }
+  auto ins_of = [&](uint32_t v) -> const Instruction* { return producer[v] < 0 ? nullptr : &plan->instructions[producer[v]]; };
+  auto sole_user = [&](uint32_t v) -> long {
+    if (is_output[v] || users[v].size() != 1) return -1;
+    return (long)users[v][0];
+  };
+  // broadcast_in_dim (or nothing, for rank 0) of a one-element constant: its value as float.
+  auto splat_constant = [&](uint32_t v, float* value) {
+    const Instruction* b = ins_of(v);
+    if (!b) return false;
+    if (b->kind == Kind::broadcast_in_dim) {
+      if (plan->values[b->inputs[0]].count() != 1) return false;
+      b = ins_of(b->inputs[0]);
+      if (!b) return false;
+    }
+    if (b->kind != Kind::constant || plan->values[b->outputs[0]].count() != 1) return false;
+    const Value& cv = plan->values[b->outputs[0]];
+    if (cv.dtype == kF32 && b->literal.size() == 4) {
+      memcpy(value, b->literal.data(), 4);
+      return true;
+    }
+    return false;
+  };
+  auto is_list = [](const std::vector<int64_t>& l, std::initializer_list<int64_t> want) { return l == std::vector<int64_t>(want); };
+
+  std::vector<AttnMatch> matches;
+  std::vector<char> taken(plan->instructions.size(), 0);
+  for (size_t i = 0; i < plan->instructions.size(); i++) {
+    const Instruction& d1 = plan->instructions[i];
+    if (d1.kind != Kind::dot_general || d1.inputs.size() != 2) continue;
+    const Value& q = plan->values[d1.inputs[0]];
+    const Value& k = plan->values[d1.inputs[1]];
+    if (q.dims.size() != 4 || k.dims.size() != 4 || !dtype_is_float(q.dtype)) continue;
+    if (!is_list(d1.list("lhs_batch_dimensions"), {0, 1}) || !is_list(d1.list("rhs_batch_dimensions"), {0, 2}) ||
+        !is_list(d1.list("lhs_contracting_dimensions"), {3}) || !is_list(d1.list("rhs_contracting_dimensions"), {3}))
+      continue;
+    AttnMatch m;
+    m.d1 = i;
+    m.q = d1.inputs[0];
+    m.k = d1.inputs[1];
+    m.consumed.push_back(i);
+    uint32_t x = d1.outputs[0];
+    const std::vector<int64_t> sdims = plan->values[x].dims;  // [B, G, rep, S]
+    long u = sole_user(x);
+    if (u < 0) continue;
+    const Instruction* n = &plan->instructions[u];
+    if (n->kind == Kind::convert && plan->values[n->outputs[0]].dtype == kF32) {
+      m.consumed.push_back(u);
+      x = n->outputs[0];
+      if ((u = sole_user(x)) < 0) continue;
+      n = &plan->instructions[u];
+    }
+    if (n->kind == Kind::multiply) {
+      uint32_t other = n->inputs[0] == x ? n->inputs[1] : n->inputs[0];
+      if (!splat_constant(other, &m.scale)) continue;
+      m.consumed.push_back(u);
+      x = n->outputs[0];
+      if ((u = sole_user(x)) < 0) continue;
+      n = &plan->instructions[u];
+    }
+    // select(key_index <= pos, x, -inf)
+    if (n->kind != Kind::select || n->inputs[1] != x) continue;
+    {
+      float neg = 0.f;
+      if (!splat_constant(n->inputs[2], &neg) || !(neg == -INFINITY)) continue;
+      const Instruction* cmp = ins_of(n->inputs[0]);
+      if (!cmp || cmp->kind != Kind::compare || cmp->scalar("compare_direction", -1) != (int64_t)CompareOp::le) continue;
+      const Instruction* io = ins_of(cmp->inputs[0]);
+      const Instruction* pb = ins_of(cmp->inputs[1]);
+      if (!io || io->kind != Kind::iota || io->scalar("iota_dimension", -1) != 3) continue;
+      if (!pb || pb->kind != Kind::broadcast_in_dim || plan->values[pb->inputs[0]].count() != 1 ||
+          !plan->values[pb->inputs[0]].dims.empty() || !dtype_is_int(plan->values[pb->inputs[0]].dtype))
+        continue;
+      m.pos = pb->inputs[0];
+    }
+    m.consumed.push_back(u);
+    x = n->outputs[0];
+    if (is_output[x] || users[x].size() != 2) continue;
+    // max over the key axis, subtract, exp
+    long rmax = -1, sub = -1;
+    for (size_t w : users[x]) {
+      const Instruction& c = plan->instructions[w];
+      if (c.kind == Kind::reduce_max && c.outputs.size() == 1 && is_list(c.list("reduce_dimensions"), {3})) rmax = (long)w;
+      if (c.kind == Kind::subtract && c.inputs[0] == x) sub = (long)w;
+    }
+    if (rmax < 0 || sub < 0) continue;
+    {
+      const Instruction* bm = ins_of(plan->instructions[sub].inputs[1]);
+      if (!bm || bm->kind != Kind::broadcast_in_dim || bm->inputs[0] != plan->instructions[rmax].outputs[0] ||
+          !is_list(bm->list("broadcast_dimensions"), {0, 1, 2}) || sole_user(plan->instructions[rmax].outputs[0]) != producer[bm->outputs[0]] ||
+          sole_user(bm->outputs[0]) != sub)
+        continue;
+      m.consumed.push_back(rmax);
+      m.consumed.push_back(producer[bm->outputs[0]]);
+      m.consumed.push_back(sub);
+    }
+    x = plan->instructions[sub].outputs[0];
+    if ((u = sole_user(x)) < 0 || plan->instructions[u].kind != Kind::exp) continue;
+    m.consumed.push_back(u);
+    x = plan->instructions[u].outputs[0];
+    if (is_output[x] || users[x].size() != 2) continue;
+    long rsum = -1, div = -1;
+    for (size_t w : users[x]) {
+      const Instruction& c = plan->instructions[w];
+      if (c.kind == Kind::reduce_sum && is_list(c.list("reduce_dimensions"), {3})) rsum = (long)w;
+      if (c.kind == Kind::divide && c.inputs[0] == x) div = (long)w;
+    }
+    if (rsum < 0 || div < 0) continue;
+    {
+      const Instruction* bz = ins_of(plan->instructions[div].inputs[1]);
+      if (!bz || bz->kind != Kind::broadcast_in_dim || bz->inputs[0] != plan->instructions[rsum].outputs[0] ||
+          !is_list(bz->list("broadcast_dimensions"), {0, 1, 2}) || sole_user(plan->instructions[rsum].outputs[0]) != producer[bz->outputs[0]] ||
+          sole_user(bz->outputs[0]) != div)
+        continue;
+      m.consumed.push_back(rsum);
+      m.consumed.push_back(producer[bz->outputs[0]]);
+      m.consumed.push_back(div);
+    }
+    x = plan->instructions[div].outputs[0];
+    if ((u = sole_user(x)) < 0) continue;
+    n = &plan->instructions[u];
+    if (n->kind == Kind::convert && plan->values[n->outputs[0]].dtype == q.dtype) {
+      m.consumed.push_back(u);
+      x = n->outputs[0];
+      if ((u = sole_user(x)) < 0) continue;
+      n = &plan->instructions[u];
+    }
+    if (n->kind != Kind::dot_general || n->inputs[0] != x) continue;
+    if (!is_list(n->list("lhs_batch_dimensions"), {0, 1}) || !is_list(n->list("rhs_batch_dimensions"), {0, 2}) ||
+        !is_list(n->list("lhs_contracting_dimensions"), {3}) || !is_list(n->list("rhs_contracting_dimensions"), {1}))
+      continue;
+    const Value& vv = plan->values[n->inputs[1]];
+    if (vv.dims != k.dims || vv.dtype != q.dtype || k.dtype != q.dtype || plan->values[x].dtype != q.dtype) continue;
+    if (producer[n->inputs[1]] > (long)i || producer[m.pos] > (long)i) continue;  // every input exists before the first dot
+    m.d2 = (size_t)u;
+    m.v = n->inputs[1];
+    m.out = n->outputs[0];
+    m.consumed.push_back(u);
+    // The split-KV kernel must support the shape.
+    AttnDecodeShape shape;
+    shape.dtype = q.dtype;
+    shape.batch = q.dims[0];
+    shape.kv_heads = q.dims[1];
+    shape.heads = q.dims[1] * q.dims[2];
+    shape.head_dim = q.dims[3];
+    shape.kv_len = k.dims[1];
+    shape.q_batch_stride = shape.heads * shape.head_dim;
+    shape.q_head_stride = shape.head_dim;
+    shape.kv_batch_stride = k.dims[1] * k.dims[2] * k.dims[3];
+    shape.kv_row_stride = k.dims[2] * k.dims[3];
+    shape.kv_head_stride = k.dims[3];
+    if (k.dims[0] != q.dims[0] || k.dims[2] != q.dims[1] || k.dims[3] != q.dims[3] || !attn_decode_supported(shape)) continue;
+    bool clash = false;
+    for (size_t c : m.consumed) clash |= taken[c] != 0;
+    if (clash) continue;
+    for (size_t c : m.consumed) taken[c] = 1;
+    matches.push_back(m);
+  }
+  if (matches.empty()) return;
+  std::vector<char> erase(plan->instructions.size(), 0);
+  for (const AttnMatch& m : matches) {
+    for (size_t c : m.consumed) erase[c] = 1;
+    erase[m.d1] = 0;
+    Instruction call;
+    call.kind = Kind::custom_call;
+    call.custom_call_target = kAttnDecodeTarget;
+    call.inputs = {m.q, m.k, m.v, m.pos};
+    call.outputs = {m.out};
+    uint32_t bits;
+    memcpy(&bits, &m.scale, 4);
+    call.attrs["scale_bits"] = {(int64_t)bits};
+    call.attrs["dims"] = plan->values[m.out].dims;
+    plan->instructions[m.d1] = call;
+  }
+  std::vector<Instruction> kept;
+  for (size_t i = 0; i < plan->instructions.size(); i++)
+    if (!erase[i]) kept.push_back(std::move(plan->instructions[i]));
+  plan->instructions = std::move(kept);
+}
+
 struct KernelPlan {
   Plan plan;  // rewritten
   Program program;
@@ -396,6 +602,12 @@ struct KernelPlan {
   std::vector<char> param_donated;
   uint64_t arena_bytes = 0, scratch_bytes = 0;
 };
+
+bool env_flag_local(const char* name, bool fallback) {
+  const char* v = getenv(name);
+  if (!v || !*v) return fallback;
+  return !(v[0] == '0' || v[0] == 'f' || v[0] == 'F' || v[0] == 'n' || v[0] == 'N');
+}
 
 constexpr uint64_t kAlign = 256;
 uint64_t align_up(uint64_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
@@ -420,6 +632,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     return false;
   }
   if (!build_program(plan, &kp->program, error)) return false;
+  if (env_flag_local("PJRTX_B200_FUSE_ATTENTION", true)) fuse_decode_attention(&kp->plan);
 
   const size_t nv = plan.values.size(), ni = plan.instructions.size();
   kp->params = plan.parameter_ids();
@@ -440,6 +653,25 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     }
     for (uint32_t v : plan.instructions[i].outputs) producer[v] = (long)i;
   }
+  // Dead instructions (left behind by rewrites, or simply unused) are skipped: nothing reads what they produce.
+  std::vector<char> dead(ni, 0);
+  {
+    std::vector<char> value_live(nv, 0);
+    for (uint32_t id : plan.output_ids) value_live[id] = 1;
+    for (size_t i = ni; i-- > 0;) {
+      bool live = false;
+      for (uint32_t v : plan.instructions[i].outputs) live |= value_live[v] != 0;
+      if (!live) {
+        dead[i] = 1;
+        continue;
+      }
+      for (uint32_t v : plan.instructions[i].inputs) value_live[v] = 1;
+    }
+    for (size_t v = 0; v < nv; v++) {
+      users[v].erase(std::remove_if(users[v].begin(), users[v].end(), [&](size_t u) { return dead[u] != 0; }), users[v].end());
+      last_read[v] = users[v].empty() ? -1 : (long)users[v].back();
+    }
+  }
 
   // Storage classes: pure aliases and in-place slice updates share their operand's storage.
   kp->root.resize(nv);
@@ -455,6 +687,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
   std::vector<char> dus_in_place(ni, 0);
   for (size_t i = 0; i < ni; i++) {
     const Instruction& ins = plan.instructions[i];
+    if (dead[i]) continue;
     auto join = [&](uint32_t out, uint32_t r) {
       kp->root[out] = r;
       class_last[r] = std::max(class_last[r], last_read[out]);
@@ -489,7 +722,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
   auto stored_roots = [&](size_t a, size_t b) {  // instruction range [a, b)
     std::vector<uint32_t> stored;
     for (size_t i = a; i < b; i++) {
-      if (plan.instructions[i].kind == Kind::constant) continue;
+      if (plan.instructions[i].kind == Kind::constant || dead[i]) continue;
       for (uint32_t v : plan.instructions[i].outputs) {
         bool needed = is_output[v];
         for (size_t u : users[v]) needed |= (u < a || u >= b);
@@ -501,15 +734,16 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     }
     return stored;
   };
+  auto skipped = [&](size_t i) { return plan.instructions[i].kind == Kind::constant || dead[i] != 0; };
   auto fusible_at = [&](size_t i) {
     const Instruction& ins = plan.instructions[i];
-    return ins.kind == Kind::constant || codegen_fusible(plan, ins);
+    return skipped(i) || codegen_fusible(plan, ins);
   };
 
   size_t i = 0;
   while (i < ni) {
     const Instruction& ins = plan.instructions[i];
-    if (ins.kind == Kind::constant) {
+    if (skipped(i)) {
       i++;
       continue;
     }
@@ -522,7 +756,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
         bool placed = false;
         std::string why;
         for (; b > a; b--) {
-          if (plan.instructions[b - 1].kind == Kind::constant && b - 1 > a) continue;  // never end a kernel on a constant
+          if (skipped(b - 1) && b - 1 > a) continue;  // never end a kernel on a skipped instruction
           std::vector<uint32_t> stored = stored_roots(a, b);
           if (stored.empty()) {
             placed = true;  // pure aliases: nothing to launch
@@ -530,7 +764,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
           }
           std::vector<size_t> nodes;
           for (size_t n = a; n < b; n++)
-            if (plan.instructions[n].kind != Kind::constant) nodes.push_back(n);
+            if (!skipped(n)) nodes.push_back(n);
           Step st;
           st.type = Step::kFused;
           if (generate_fused_kernel(plan, nodes, stored, sm_count, &st.fused, &why)) {
@@ -584,12 +818,58 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
         st.outputs = {kp->root[ins.outputs[0]]};
         break;
       }
-      case Kind::custom_call:
-        st.type = Step::kSdpa;
-        analyze_sdpa(plan, ins, &st.sdpa, &why);
+      case Kind::custom_call: {
         for (uint32_t v : ins.inputs) st.inputs.push_back(kp->root[v]);
         st.outputs = {ins.outputs[0]};
+        AttnDecodeShape& ad = st.attn;
+        if (ins.custom_call_target == kAttnDecodeTarget) {
+          const Value& q = plan.values[ins.inputs[0]];
+          const Value& k = plan.values[ins.inputs[1]];
+          ad.dtype = q.dtype;
+          ad.batch = q.dims[0];
+          ad.kv_heads = q.dims[1];
+          ad.heads = q.dims[1] * q.dims[2];
+          ad.head_dim = q.dims[3];
+          ad.kv_len = k.dims[1];
+          ad.round_scores = 1;
+          uint32_t bits = (uint32_t)ins.scalar("scale_bits", 0);
+          memcpy(&ad.scale, &bits, 4);
+          ad.token_dtype = plan.values[ins.inputs[3]].dtype;
+          st.type = Step::kAttnDecode;
+        } else {
+          st.type = Step::kSdpa;
+          analyze_sdpa(plan, ins, &st.sdpa, &why);
+          if (st.sdpa.q_len == 1) {  // decode-shaped call: the split-KV kernel
+            ad.dtype = st.sdpa.dtype;
+            ad.batch = st.sdpa.batch;
+            ad.heads = st.sdpa.heads;
+            ad.kv_heads = st.sdpa.kv_heads;
+            ad.head_dim = st.sdpa.head_dim;
+            ad.kv_len = st.sdpa.kv_len;
+            ad.round_scores = 0;
+            ad.scale = 1.0f / sqrtf((float)st.sdpa.head_dim);
+            ad.token_dtype = st.sdpa.token_dtype;
+            st.type = Step::kAttnDecode;
+          }
+        }
+        if (st.type == Step::kAttnDecode) {
+          ad.q_batch_stride = ad.heads * ad.head_dim;
+          ad.q_head_stride = ad.head_dim;
+          ad.kv_batch_stride = ad.kv_len * ad.kv_heads * ad.head_dim;
+          ad.kv_row_stride = ad.kv_heads * ad.head_dim;
+          ad.kv_head_stride = ad.head_dim;
+          if (!attn_decode_supported(ad)) {
+            if (ins.custom_call_target == kAttnDecodeTarget) {
+              *error = format_issue(plan, Issue{(long)i, -1, "internal attention call has an unsupported shape", "b200-attention"});
+              return false;
+            }
+            st.type = Step::kSdpa;
+          } else {
+            st.attn_plan = attn_decode_plan(ad, sm_count);
+          }
+        }
         break;
+      }
       case Kind::all_reduce: case Kind::all_gather:
         st.type = ins.kind == Kind::all_reduce ? Step::kAllReduce : Step::kAllGather;
         st.inputs = {kp->root[ins.inputs[0]]};
@@ -704,6 +984,9 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     if (st.type == Step::kDot && st.dot_scratch.counter_bytes) {
       st.counter_offset = scratch;
       scratch += align_up(st.dot_scratch.counter_bytes);
+    } else if (st.type == Step::kAttnDecode) {
+      st.counter_offset = scratch;
+      scratch += align_up(st.attn_plan.counter_bytes);
     }
   uint64_t counters_end = scratch;
   uint64_t partial_max = 0;
@@ -711,13 +994,16 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     if (st.type == Step::kDot && st.dot_scratch.partial_bytes) {
       st.scratch_offset = counters_end;  // partials are consumed inside the launch that wrote them: one shared region
       partial_max = std::max(partial_max, align_up(st.dot_scratch.partial_bytes));
+    } else if (st.type == Step::kAttnDecode) {
+      st.scratch_offset = counters_end;
+      partial_max = std::max(partial_max, align_up(st.attn_plan.workspace_bytes));
     }
   kp->scratch_bytes = counters_end + partial_max;
   return true;
 }
 
 std::string step_type_name(Step::Type t) {
-  static const char* names[] = {"fused", "dot", "slice_update", "sdpa", "all_reduce", "all_gather", "copy"};
+  static const char* names[] = {"fused", "dot", "slice_update", "sdpa", "all_reduce", "all_gather", "copy", "attention_decode"};
   return names[(int)t];
 }
 
@@ -756,6 +1042,9 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
                   n_total, (long long)st.dot.k, std::max<size_t>(st.dot_group.size(), 1));
     } else if (st.type == Step::kSliceUpdate) {
       s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");
+    } else if (st.type == Step::kAttnDecode) {
+      s += strfmt(",\"splits\":%d,\"batch\":%lld,\"heads\":%lld,\"kv_heads\":%lld,\"kv_len\":%lld,\"head_dim\":%lld",
+                  st.attn_plan.splits, st.attn.batch, st.attn.heads, st.attn.kv_heads, st.attn.kv_len, st.attn.head_dim);
     }
     s += "}";
   }
@@ -858,8 +1147,16 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         for (uint32_t v : st.fused.outputs) addr.push_back(ptr.of(v));
         std::vector<void*> args(addr.size());
         for (size_t k = 0; k < addr.size(); k++) args[k] = &addr[k];
-        cudaError_t e = cudaLaunchKernel((const void*)st.jit->kernel, dim3((unsigned)st.fused.grid), dim3((unsigned)st.fused.block),
-                                         args.data(), 0, dev->stream);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)st.fused.grid);
+        cfg.blockDim = dim3((unsigned)st.fused.block);
+        cfg.stream = dev->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = exe->pdl ? 1 : 0;
+        cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)st.jit->kernel, args.data());
         if (e != cudaSuccess) {
           *error = std::string("fused kernel launch failed: ") + cudaGetErrorString(e);
           return false;
@@ -902,16 +1199,25 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         }
         const void* starts[8] = {nullptr};
         for (int d = 0; d < st.dus.rank; d++) starts[d] = ptr.of(st.inputs[2 + d]);
-        if (!dus_launch(st.dus, dst, ptr.of(st.inputs[1]), starts, dev->stream)) {
+        if (!dus_launch(st.dus, dst, ptr.of(st.inputs[1]), starts, exe->pdl, dev->stream)) {
           *error = "dynamic_update_slice kernel refused the shape";
           return false;
         }
         (*launches)++;
         break;
       }
+      case Step::kAttnDecode:
+        if (!attn_decode_launch(st.attn, st.attn_plan, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]),
+                                ptr.of(st.inputs[3]), ptr.of(st.outputs[0]), (char*)ds.scratch + st.scratch_offset,
+                                (char*)ds.scratch + st.counter_offset, exe->pdl, dev->stream)) {
+          *error = "attention kernel refused the shape";
+          return false;
+        }
+        (*launches)++;
+        break;
       case Step::kSdpa:
         if (!sdpa_launch(st.sdpa, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]), ptr.of(st.inputs[3]),
-                         ptr.of(st.outputs[0]), dev->stream)) {
+                         ptr.of(st.outputs[0]), exe->pdl, dev->stream)) {
           *error = "attention kernel refused the shape";
           return false;
         }
@@ -1028,6 +1334,7 @@ Executable* compile_executable(const Plan& plan, const std::vector<int>& device_
     exe->devices.push_back(std::move(ds));
   }
   exe->use_graph = env_flag("PJRTX_B200_GRAPH", true) && kp.steps.size() >= 4;
+  exe->pdl = env_flag("PJRTX_B200_PDL", true);
   ExecutableStats& s = exe->stats;
   s.resident_constant_count = kp.constants.size();
   s.resident_constant_bytes = const_bytes;

@@ -50,7 +50,7 @@ struct ExecutableStats {
 };
 
 struct Step {
-  enum Type { kFused, kDot, kSliceUpdate, kSdpa, kAllReduce, kAllGather, kCopy } type = kFused;
+  enum Type { kFused, kDot, kSliceUpdate, kSdpa, kAllReduce, kAllGather, kCopy, kAttnDecode } type = kFused;
   std::vector<size_t> nodes;        // plan instructions this step covers
   std::vector<uint32_t> inputs;     // root values read
   std::vector<uint32_t> outputs;    // root values written
@@ -64,6 +64,8 @@ struct Step {
   bool in_place = false;
   bool early_rhs = false;  // every rhs of the contraction is a parameter or constant no step writes
   SdpaShape sdpa;
+  AttnDecodeShape attn;
+  AttnDecodePlan attn_plan;
   uint64_t bytes = 0;  // kCopy / collectives
   uint64_t count = 0;
   int dtype = 0;

@@ -74,6 +74,7 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 // ---------------------------------------------------------------- generic
 template <typename T>
 __global__ void dot_generic_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out) {
+  PJRTX_PDL_PROLOGUE();
   const int64_t total = s.b0 * s.b1 * s.m * s.n;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t n = i % s.n, m = (i / s.n) % s.m, b1 = (i / (s.n * s.m)) % s.b1, b0 = i / (s.n * s.m * s.b1);
@@ -106,6 +107,7 @@ template <typename T, int M, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 stream_kn_kernel(DotShape s, KnGroup grp, const T* __restrict__ lhs, float* __restrict__ partials,
                  unsigned* __restrict__ counters, int ksplit, int kslice) {
+  PJRTX_PDL_PROLOGUE();
   constexpr int V = Vec16<T>::N;
   constexpr int TILE = 32 * V;
   constexpr int THREADS = WARPS * 32;
@@ -246,6 +248,7 @@ stream_kn_kernel(DotShape s, KnGroup grp, const T* __restrict__ lhs, float* __re
 template <typename T, int M>
 __global__ void __launch_bounds__(256)
 stream_nk_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out, int group) {
+  PJRTX_PDL_PROLOGUE();
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int rows_per_warp = 32 / group;
@@ -289,6 +292,7 @@ constexpr int kTile = 64, kTileK = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 tile_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out) {
+  PJRTX_PDL_PROLOGUE();
   __shared__ float As[kTileK][kTile + 4];
   __shared__ float Bs[kTileK][kTile + 4];
   const int64_t batch = blockIdx.z, b0 = batch / s.b1, b1 = batch % s.b1;
@@ -338,7 +342,7 @@ tile_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T*
 
 template <typename T>
 int launch_group_typed(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
-                       void* const* out, void* partials, void* counters, cudaStream_t stream) {
+                       void* const* out, void* partials, void* counters, bool pdl, cudaStream_t stream) {
   constexpr int V = 16 / sizeof(T);
   const int tile = 32 * V;
   const DotShape& s = shapes[0];
@@ -363,15 +367,16 @@ int launch_group_typed(const DotShape* shapes, int count, const DotScratch& plan
   const T* a = static_cast<const T*>(lhs);
   float* p = static_cast<float*>(partials);
   unsigned* c = static_cast<unsigned*>(counters);
-#define KN(MM, WW) stream_kn_kernel<T, MM, WW><<<grid, WW * 32, 0, stream>>>(s, grp, a, p, c, plan.ksplit, kslice)
+  cudaError_t e;
+#define KN(MM, WW) e = launch_kernel(stream_kn_kernel<T, MM, WW>, grid, dim3(WW * 32), 0, stream, pdl, s, grp, a, p, c, plan.ksplit, kslice)
   if (M == 1) KN(1, 8); else if (M == 2) KN(2, 8); else if (M == 4) KN(4, 8); else KN(8, 4);
 #undef KN
-  return 1;
+  return e == cudaSuccess ? 1 : 0;
 }
 
 template <typename T>
 int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
-                 void* counters, cudaStream_t stream) {
+                 void* counters, bool pdl, cudaStream_t stream) {
   const T* a = static_cast<const T*>(lhs);
   const T* b = static_cast<const T*>(rhs);
   T* o = static_cast<T*>(out);
@@ -381,27 +386,26 @@ int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, con
     const DotShape* one = &s;
     const void* rhs_list[1] = {rhs};
     void* out_list[1] = {out};
-    return launch_group_typed<T>(one, 1, plan, lhs, rhs_list, out_list, partials, counters, stream);
+    return launch_group_typed<T>(one, 1, plan, lhs, rhs_list, out_list, partials, counters, pdl, stream);
   }
   if (plan.path == 2) {
     int group = 32;
     while (group > 1 && (int64_t)group * V > s.k) group >>= 1;
     const int rows_per_cta = 8 * (32 / group);
     dim3 grid((unsigned)((s.n + rows_per_cta - 1) / rows_per_cta), (unsigned)batch);
-#define NK(MM) stream_nk_kernel<T, MM><<<grid, 256, 0, stream>>>(s, a, b, o, group)
+    cudaError_t e;
+#define NK(MM) e = launch_kernel(stream_nk_kernel<T, MM>, grid, dim3(256), 0, stream, pdl, s, a, b, o, group)
     if (s.m <= 1) NK(1); else if (s.m <= 2) NK(2); else if (s.m <= 4) NK(4); else NK(8);
 #undef NK
-    return 1;
+    return e == cudaSuccess ? 1 : 0;
   }
   if (plan.path == 3) {
     dim3 grid((unsigned)((s.n + kTile - 1) / kTile), (unsigned)((s.m + kTile - 1) / kTile), (unsigned)batch);
-    tile_kernel<T><<<grid, 256, 0, stream>>>(s, a, b, o);
-    return 1;
+    return launch_kernel(tile_kernel<T>, grid, dim3(256), 0, stream, pdl, s, a, b, o) == cudaSuccess ? 1 : 0;
   }
   const int64_t total = batch * s.m * s.n;
   const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
-  dot_generic_kernel<T><<<blocks ? blocks : 1, 256, 0, stream>>>(s, a, b, o);
-  return 1;
+  return launch_kernel(dot_generic_kernel<T>, dim3(blocks ? blocks : 1), dim3(256), 0, stream, pdl, s, a, b, o) == cudaSuccess ? 1 : 0;
 }
 
 }  // namespace
@@ -554,9 +558,9 @@ int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, 
     }
   }
   switch (shapes[0].dtype) {
-    case kF32: return launch_group_typed<float>(shapes, count, plan, lhs, rhs, out, partials, counters, stream);
-    case kF16: return launch_group_typed<__half>(shapes, count, plan, lhs, rhs, out, partials, counters, stream);
-    case kBF16: return launch_group_typed<__nv_bfloat16>(shapes, count, plan, lhs, rhs, out, partials, counters, stream);
+    case kF32: return launch_group_typed<float>(shapes, count, plan, lhs, rhs, out, partials, counters, pdl, stream);
+    case kF16: return launch_group_typed<__half>(shapes, count, plan, lhs, rhs, out, partials, counters, pdl, stream);
+    case kBF16: return launch_group_typed<__nv_bfloat16>(shapes, count, plan, lhs, rhs, out, partials, counters, pdl, stream);
     default: return 0;
   }
 }
@@ -597,9 +601,9 @@ int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const
     return dot_group_launch(&s, 1, plan, lhs, rhs_list, out_list, partials, counters, error_flag, early_rhs, pdl, stream);
   }
   switch (s.dtype) {
-    case kF32: return launch_typed<float>(s, plan, lhs, rhs, out, partials, counters, stream);
-    case kF16: return launch_typed<__half>(s, plan, lhs, rhs, out, partials, counters, stream);
-    case kBF16: return launch_typed<__nv_bfloat16>(s, plan, lhs, rhs, out, partials, counters, stream);
+    case kF32: return launch_typed<float>(s, plan, lhs, rhs, out, partials, counters, pdl, stream);
+    case kF16: return launch_typed<__half>(s, plan, lhs, rhs, out, partials, counters, pdl, stream);
+    case kBF16: return launch_typed<__nv_bfloat16>(s, plan, lhs, rhs, out, partials, counters, pdl, stream);
     default: return 0;
   }
 }

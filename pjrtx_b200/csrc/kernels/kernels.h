@@ -8,6 +8,28 @@
 
 namespace pjrtx {
 
+// Launch with (optionally) programmatic stream serialization: the kernel may begin while its predecessor in the stream
+// is still running; kernels call griddepcontrol.wait before their first dependent access.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define PJRTX_PDL_PROLOGUE()                                              \
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");         \
+  asm volatile("griddepcontrol.wait;" ::: "memory")
+
 // Canonical contraction out[b0,b1,m,n] = sum_k lhs[b0,b1,m,k] * rhs[b0,b1,k,n]
 // with arbitrary element strides, as produced by analysing a dot_general
 // (src/backend/mlx_metal/api.cc:3349-3498 canonicalises the same way by
@@ -63,7 +85,7 @@ struct SliceUpdateShape {
   int64_t upd_dims[8] = {0};
   int start_dtype[8] = {0};
 };
-int dus_launch(const SliceUpdateShape& s, void* dst, const void* update, const void* const* start_ptrs,
+int dus_launch(const SliceUpdateShape& s, void* dst, const void* update, const void* const* start_ptrs, bool pdl,
                cudaStream_t stream);
 
 // Scaled dot-product attention custom call (src/backend/mlx_metal/custom_call.zig:120-152,
@@ -74,6 +96,27 @@ struct SdpaShape {
   int token_dtype = 0;
 };
 int sdpa_launch(const SdpaShape& s, const void* q, const void* k, const void* v, const void* token_index, void* out,
-                cudaStream_t stream);
+                bool pdl, cudaStream_t stream);
+
+// Decode attention (one query position per sequence, grouped-query heads) as one split-KV kernel.
+// q / out: [batch, heads, head_dim] through (q_batch_stride, q_head_stride); k / v: [batch, kv_len, kv_heads, head_dim]
+// through (kv_batch_stride, kv_row_stride, kv_head_stride); keys 0..token are visible.
+struct AttnDecodeShape {
+  int dtype = 0;
+  long long batch = 1, heads = 1, kv_heads = 1, kv_len = 1, head_dim = 1;
+  long long q_batch_stride = 0, q_head_stride = 0;
+  long long kv_batch_stride = 0, kv_row_stride = 0, kv_head_stride = 0;
+  int token_dtype = 0;
+  int round_scores = 0;  // round q.k to the element type before scaling (what an explicit dot_general does)
+  float scale = 1.f;
+};
+struct AttnDecodePlan {
+  int splits = 1;
+  uint64_t workspace_bytes = 0, counter_bytes = 0;
+};
+bool attn_decode_supported(const AttnDecodeShape& s);
+AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count);
+int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, const void* q, const void* k, const void* v,
+                       const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream);
 
 }  // namespace pjrtx

@@ -40,6 +40,7 @@ struct DusArgs {
 // (the reference passes them to MLX slice_update, src/backend/mlx_metal/api.cc:2552-2635).
 template <typename U>
 __global__ void dus_kernel(DusArgs a, U* __restrict__ dst, const U* __restrict__ upd) {
+  PJRTX_PDL_PROLOGUE();
   __shared__ int64_t start[8];
   if (threadIdx.x < a.rank) {
     const int d = threadIdx.x;
@@ -84,6 +85,7 @@ struct AttnArgs {
 template <typename T>
 __global__ void sdpa_simple_kernel(AttnArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                                    const void* __restrict__ token, T* __restrict__ out) {
+  PJRTX_PDL_PROLOGUE();
   const int64_t total = a.batch * a.q_len * a.heads;
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= total) return;
@@ -121,7 +123,7 @@ __global__ void sdpa_simple_kernel(AttnArgs a, const T* __restrict__ q, const T*
 
 }  // namespace
 
-int dus_launch(const SliceUpdateShape& s, void* dst, const void* update, const void* const* start_ptrs,
+int dus_launch(const SliceUpdateShape& s, void* dst, const void* update, const void* const* start_ptrs, bool pdl,
                cudaStream_t stream) {
   if (s.rank < 0 || s.rank > 8 || s.elem_size <= 0) return 0;
   int64_t upd[8] = {1}, dstd[8] = {1};
@@ -163,27 +165,27 @@ int dus_launch(const SliceUpdateShape& s, void* dst, const void* update, const v
   for (int d = 0; d <= t; d++) k.total_units *= k.upd_units[d];
   const unsigned blocks = (unsigned)std::min<int64_t>((k.total_units + 255) / 256, 148 * 16);
   switch (unit) {
-    case 16: dus_kernel<uint4><<<blocks, 256, 0, stream>>>(k, (uint4*)dst, (const uint4*)update); break;
-    case 8: dus_kernel<uint2><<<blocks, 256, 0, stream>>>(k, (uint2*)dst, (const uint2*)update); break;
-    case 4: dus_kernel<uint32_t><<<blocks, 256, 0, stream>>>(k, (uint32_t*)dst, (const uint32_t*)update); break;
-    case 2: dus_kernel<uint16_t><<<blocks, 256, 0, stream>>>(k, (uint16_t*)dst, (const uint16_t*)update); break;
-    case 1: dus_kernel<uint8_t><<<blocks, 256, 0, stream>>>(k, (uint8_t*)dst, (const uint8_t*)update); break;
+    case 16: launch_kernel(dus_kernel<uint4>, dim3(blocks), dim3(256), 0, stream, pdl, k, (uint4*)dst, (const uint4*)update); break;
+    case 8: launch_kernel(dus_kernel<uint2>, dim3(blocks), dim3(256), 0, stream, pdl, k, (uint2*)dst, (const uint2*)update); break;
+    case 4: launch_kernel(dus_kernel<uint32_t>, dim3(blocks), dim3(256), 0, stream, pdl, k, (uint32_t*)dst, (const uint32_t*)update); break;
+    case 2: launch_kernel(dus_kernel<uint16_t>, dim3(blocks), dim3(256), 0, stream, pdl, k, (uint16_t*)dst, (const uint16_t*)update); break;
+    case 1: launch_kernel(dus_kernel<uint8_t>, dim3(blocks), dim3(256), 0, stream, pdl, k, (uint8_t*)dst, (const uint8_t*)update); break;
     default: return 0;
   }
   return 1;
 }
 
 int sdpa_launch(const SdpaShape& s, const void* q, const void* k, const void* v, const void* token_index, void* out,
-                cudaStream_t stream) {
+                bool pdl, cudaStream_t stream) {
   AttnArgs a{s.batch, s.q_len, s.heads, s.kv_len, s.kv_heads, s.head_dim, s.token_dtype,
              1.0f / sqrtf((float)s.head_dim)};
   const int64_t total = s.batch * s.q_len * s.heads;
   if (total == 0) return 1;
   const unsigned blocks = (unsigned)((total + 63) / 64);
   switch (s.dtype) {
-    case kF32: sdpa_simple_kernel<float><<<blocks, 64, 0, stream>>>(a, (const float*)q, (const float*)k, (const float*)v, token_index, (float*)out); break;
-    case kF16: sdpa_simple_kernel<__half><<<blocks, 64, 0, stream>>>(a, (const __half*)q, (const __half*)k, (const __half*)v, token_index, (__half*)out); break;
-    case kBF16: sdpa_simple_kernel<__nv_bfloat16><<<blocks, 64, 0, stream>>>(a, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, token_index, (__nv_bfloat16*)out); break;
+    case kF32: launch_kernel(sdpa_simple_kernel<float>, dim3(blocks), dim3(64), 0, stream, pdl, a, (const float*)q, (const float*)k, (const float*)v, token_index, (float*)out); break;
+    case kF16: launch_kernel(sdpa_simple_kernel<__half>, dim3(blocks), dim3(64), 0, stream, pdl, a, (const __half*)q, (const __half*)k, (const __half*)v, token_index, (__half*)out); break;
+    case kBF16: launch_kernel(sdpa_simple_kernel<__nv_bfloat16>, dim3(blocks), dim3(64), 0, stream, pdl, a, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, token_index, (__nv_bfloat16*)out); break;
     default: return 0;
   }
   return 1;

@@ -100,3 +100,25 @@ def test_int8_weight_only_decode(gpu_backend):
     exe = be.compile_executable(builder, [0])
     outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
     assert_close(outs[1].to_numpy(), want[1], 2e-2, what="int8 logits")
+
+
+def test_unfused_attention_path_agrees(gpu_backend, monkeypatch):
+    """The recognised attention step and the plain dot -> softmax -> dot steps give the same logits within tolerance."""
+    be = gpu_backend
+    cfg = llama.TINY
+    batch, max_len, filled = 2, 64, 40
+    builder, names = llama.build_decode_step(cfg, batch, max_len, return_logits=True)
+    weights = llama.make_weights(cfg, seed=0)
+    caches = llama.make_kv_cache(cfg, batch, max_len, filled)
+    args = [np.array([5, 9], np.int32), np.array(filled, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
+    want = run_oracle(builder, args)
+    results = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("PJRTX_B200_FUSE_ATTENTION", flag)
+        exe = be.compile_executable(builder, [0])
+        kinds = [s["type"] for s in exe.describe()["kernel_plan"]["steps"]]
+        assert (kinds.count("attention_decode") == cfg.layers) == (flag == "1")
+        outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
+        results.append(outs[1].to_numpy())
+        assert_close(results[-1], want[1], 2e-2, what=f"logits fuse={flag}")
+    assert_close(results[0], results[1], 2e-2, what="fused vs unfused")

@@ -164,28 +164,34 @@ def test_config1_is_one_row_kernel_and_compiles(backend):
     assert backend.compile_check(st["source"]) == ""
 
 
-def test_decode_step_kernel_plan(backend):
+def test_decode_step_kernel_plan(backend, monkeypatch):
     cfg = llama.TINY
     b, names = llama.build_decode_step(cfg, 2, 64)
     assert backend.verify_plan(b) == ""
     k = backend.describe_kernels(b)
     types = [s["type"] for s in k["steps"]]
-    # per layer: q/k/v as one grouped launch, scores, context, o_proj, gate/up as one grouped launch, down_proj
+    # per layer: q/k/v as one grouped launch, o_proj, gate/up as one grouped launch, down_proj; the
+    # scores -> masked softmax -> context chain is recognised and becomes one split-KV attention step
     dots = [s for s in k["steps"] if s["type"] == "dot"]
-    assert len(dots) == 6 * cfg.layers + 1
+    assert len(dots) == 4 * cfg.layers + 1
     assert sum(1 for s in dots if s["group"] == 3 and s["n"] == cfg.q_dim + 2 * cfg.kv_dim) == cfg.layers
     assert sum(1 for s in dots if s["group"] == 2 and s["n"] == 2 * cfg.ffn) == cfg.layers
+    assert all(s["path"] == 1 and s["tma"] == 1 for s in dots)  # every projection streams through the TMA kernel
+    assert types.count("attention_decode") == cfg.layers
     assert types.count("slice_update") == 2 * cfg.layers
     assert all(s["in_place"] for s in k["steps"] if s["type"] == "slice_update")
     fused = [s for s in k["steps"] if s["type"] == "fused"]
-    # RMSNorm (+ residual add) and softmax are single row kernels
+    # RMSNorm (+ residual add) is a single row kernel, so is the argmax over the vocabulary
     assert sum(1 for s in fused if s["row"] and s["cols"] == cfg.d_model) == 2 * cfg.layers + 1
-    assert sum(1 for s in fused if s["row"] and s["cols"] == 64 and s["reduces"] == 2) == cfg.layers
-    assert sum(1 for s in fused if s["row"] and s["cols"] == cfg.vocab) == 1  # argmax over the vocabulary
+    assert sum(1 for s in fused if s["row"] and s["cols"] == cfg.vocab) == 1
     for src in {s["source"] for s in fused}:
         assert backend.compile_check(src) == ""
-    # streaming paths are chosen for every projection (m = batch <= 8)
-    assert all(s["path"] in (1, 2) for s in k["steps"] if s["type"] == "dot")
+    # without the recognition the same program runs as dot -> one softmax row kernel -> dot
+    monkeypatch.setenv("PJRTX_B200_FUSE_ATTENTION", "0")
+    k2 = backend.describe_kernels(b)
+    types2 = [s["type"] for s in k2["steps"]]
+    assert types2.count("attention_decode") == 0 and types2.count("dot") == 6 * cfg.layers + 1
+    assert sum(1 for s in k2["steps"] if s["type"] == "fused" and s["row"] and s["cols"] == 64 and s["reduces"] == 2) == cfg.layers
 
 
 def test_all_cases_plan_and_compile(backend):
