@@ -35,45 +35,44 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML (read-only queries) while the timed region runs."""
+    """Polls `nvidia-smi --query-gpu` (read-only) from a thread while the timed region runs; every call has a timeout."""
 
-    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, device: int):
         self.device = device
-        self.samples = []
-        self.reasons = set()
-        self.max_mhz = None
+        self.sm, self.mx, self.reasons = [], [], set()
         self._stop = threading.Event()
         self._thread = None
 
-    def start(self):
-        try:
-            import pynvml
+    def _poll_once(self):
+        import subprocess
 
-            pynvml.nvmlInit()
-            uuid = None
-            try:
-                visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-                index = int(visible.split(",")[self.device]) if visible and visible.replace(",", "").isdigit() else self.device
-            except Exception:
-                index = self.device
-            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        try:
+            out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.device)],
+                                 capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
         except Exception:
             return
+        for line in out:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                self.sm.append(float(f[0]))
+                self.mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(self.NAMES, f[3:7]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(name)
 
+    def start(self):
         def loop():
             while not self._stop.is_set():
-                try:
-                    self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
-                    mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
-                    for name, bit in self.REASONS:
-                        if mask & bit:
-                            self.reasons.add(name)
-                except Exception:
-                    pass
-                self._stop.wait(0.02)
+                self._poll_once()
+                self._stop.wait(0.1)
 
         self._thread = threading.Thread(target=loop, daemon=True)
         self._thread.start()
@@ -81,11 +80,13 @@ class ClockSampler:
     def stop(self):
         self._stop.set()
         if self._thread:
-            self._thread.join(timeout=2)
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+            self._thread.join(timeout=6)
+        if not self.sm:
+            self._poll_once()  # the region was shorter than one poll
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.sm)), "sm_max_mhz": float(max(self.mx)), "reasons": sorted(self.reasons),
+                "samples": len(self.sm)}
 
 
 def device_tensor(be, cache, builder_fn, key, seed, device):
@@ -180,6 +181,11 @@ def algorithmic_bytes(cfg, batch, kv_len, world):
     return weights + kv + batch * cfg.d_model * 2
 
 
+def _progress(msg):
+    if os.environ.get("PJRTX_BENCH_VERBOSE"):
+        print(f"[bench {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -211,7 +217,9 @@ def run_ours(args):
         dist.broadcast_object_list(uid, src=0)
         be.comm_init(device, uid[0], rank, world)
     t0 = time.time()
+    _progress("compiling")
     exe = be.compile_executable(builder, [device], partition=rank if world > 1 else None)
+    _progress("compiled")
     compile_s = time.time() - t0
     table = param_table(cfg, builder, names, world)
     t0 = time.time()
@@ -219,6 +227,7 @@ def run_ours(args):
     params = [reshape_buffer(be, buf, dims, device) for buf, dims in gen]
     be.synchronize(device)
     setup_s = time.time() - t0
+    _progress("weights ready")
     n_cache = 2 * cfg.layers
     weights, caches = params[:-n_cache], params[-n_cache:]
 
@@ -239,9 +248,10 @@ def run_ours(args):
     for _ in range(args.warmup):
         token, caches = step(token, pos_bufs[pi], caches); pi += 1
     barrier()
+    _progress("warm-up done")
     launches0 = exe.stats()["kernel_launch_total"]
     sampler = ClockSampler(device)
-    if rank == 0:
+    if rank == 0 and not os.environ.get("PJRTX_BENCH_NO_SAMPLER"):
         sampler.start()
     start = be.record_event(device)
     for _ in range(args.steps):
@@ -250,6 +260,7 @@ def run_ours(args):
     ms = be.elapsed_ms(start, stop)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    _progress(f"timed loop done: {ms / args.steps:.3f} ms/step")
     launches = exe.stats()["kernel_launch_total"] - launches0
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64)
@@ -282,6 +293,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
 
+    _progress(f"e2e loop done: {e2e_ms / args.steps:.3f} ms/step")
     # ---- per-kernel device times for the roofline of the dominant kernel ------------
     exe.set_profiling(True)
     per_type = {}
@@ -295,6 +307,7 @@ def run_ours(args):
         acc += np.array(exe.step_times_ms())
         pi += 1
     exe.set_profiling(False)
+    _progress("profiled replay done")
     acc /= reps
     esize = 2
     stream_bytes = stream_ms = 0.0

@@ -136,14 +136,15 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
   const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
   const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
 
-  // Each lane group walks keys j_begin + (warp*KPW + sub) + t * (kWarps*KPW).
+  // Each lane group walks keys j_begin + warp*KPW + sub + t*(kWarps*KPW). The loop bound is the same for every
+  // lane of the warp (the shuffles below need all 32 lanes); keys past the end are masked per lane.
   constexpr int STRIDE = kWarps * KPW;
-  for (long long j0 = j_begin + warp * KPW + sub; j0 < j_end; j0 += (long long)STRIDE * kKeysPerStep) {
+  for (long long base = j_begin + warp * KPW; base < j_end; base += (long long)STRIDE * kKeysPerStep) {
     uint4 kr[kKeysPerStep], vr[kKeysPerStep];
     bool ok[kKeysPerStep];
 #pragma unroll
     for (int u = 0; u < kKeysPerStep; u++) {
-      const long long j = j0 + (long long)u * STRIDE;
+      const long long j = base + sub + (long long)u * STRIDE;
       ok[u] = j < j_end;
       const long long jj = ok[u] ? j : j_begin;  // a valid row; its contribution is masked below
       kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + jj * a.kv_row_stride));

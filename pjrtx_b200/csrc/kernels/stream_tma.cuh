@@ -35,7 +35,7 @@ constexpr int kTileBytes = 512;     // bytes per row per unit (one warp x 16 B)
 constexpr int kStageBytes = kUnitRows * kTileBytes;  // 32 KiB
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr unsigned kSpinLimit = 1u << 26;
+constexpr unsigned kSpinLimit = 1u << 22;  // about a quarter of a second of polling
 
 struct Params {
   // Shared by all contractions of the launch.
