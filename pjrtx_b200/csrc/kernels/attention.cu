@@ -67,7 +67,7 @@ __device__ __forceinline__ long long load_scalar(const void* p, int dtype) {
   }
 }
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kKeysPerStep = 4;  // keys a lane group handles per loop iteration (loads issued together)
 
 struct DecodeArgs {
@@ -239,14 +239,37 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // Two passes over the splits with independent loads (issued in batches) instead of one dependent chain: first the
+  // overall maximum, then the weighted sums in split order.
   const float* base = a.workspace + tile * a.splits * (long long)REP * (HD + 2);
+  const long long split_stride = (long long)REP * (HD + 2);
   for (int idx = threadIdx.x; idx < REP * HD; idx += kWarps * 32) {
     const int r = idx / HD, d = idx % HD;
-    float mm = -INFINITY, ll = 0.f, oo = 0.f;
-    for (int sp = 0; sp < a.splits; sp++) {
-      const float* p = base + (long long)sp * REP * (HD + 2) + r * (HD + 2);
-      float o2 = __ldcg(p + d);
-      merge_state<1>(mm, ll, &oo, __ldcg(p + HD), __ldcg(p + HD + 1), &o2);
+    const float* p = base + r * (HD + 2);
+    float mm = -INFINITY;
+    for (int sp = 0; sp < a.splits; sp += 8) {
+      float mv[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) mv[e] = sp + e < a.splits ? __ldcg(p + (sp + e) * split_stride + HD) : -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 8; e++) mm = fmaxf(mm, mv[e]);
+    }
+    float ll = 0.f, oo = 0.f;
+    for (int sp = 0; sp < a.splits; sp += 4) {
+      float mv[4], lv[4], ov[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const bool in = sp + e < a.splits;
+        mv[e] = in ? __ldcg(p + (sp + e) * split_stride + HD) : -INFINITY;
+        lv[e] = in ? __ldcg(p + (sp + e) * split_stride + HD + 1) : 0.f;
+        ov[e] = in ? __ldcg(p + (sp + e) * split_stride + d) : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float w = mv[e] == -INFINITY ? 0.f : __expf(mv[e] - mm);
+        ll = fmaf(lv[e], w, ll);
+        oo = fmaf(ov[e], w, oo);
+      }
     }
     out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(ll > 0.f ? oo / ll : 0.f);
   }
@@ -290,7 +313,8 @@ bool attn_decode_supported(const AttnDecodeShape& s) {
 AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   AttnDecodePlan p;
   const long long tiles = s.batch * s.kv_heads;
-  long long want = (2LL * sm_count + tiles - 1) / tiles;
+  // About one CTA per SM; every split should still cover a few hundred keys' worth of rows.
+  long long want = ((long long)sm_count + tiles - 1) / tiles;
   long long max_splits = std::max<long long>(1, s.kv_len / 64);
   p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
   const long long rep = s.heads / s.kv_heads;

@@ -431,9 +431,10 @@ DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count) {
     const size_t red = (size_t)tma::kConsumerWarps * M * 32 * V * sizeof(float);
     const bool two_per_sm = red <= 16 * 1024;
     p.stages = two_per_sm ? 3 : (M <= 4 ? 5 : 4);
+    // A fixed grid of one or two CTAs per SM; units are dealt out evenly (shares differ by at most one unit).
     const int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(units, (int64_t)sm_count * (two_per_sm ? 2 : 1)));
-    p.per_cta = (units + ctas - 1) / ctas;
-    p.grid = (int)((units + p.per_cta - 1) / p.per_cta);
+    p.grid = (int)ctas;
+    p.per_cta = units / ctas;
     p.max_contrib = (int)((chunks + p.per_cta - 1) / p.per_cta) + 1;
     p.smem = tma::smem_bytes(p.stages, M, 32 * V);
     p.ksplit = p.max_contrib;

@@ -53,7 +53,7 @@ struct Params {
   // Decomposition.
   int chunks;                         // ceil(k / kUnitRows)
   long long units;                    // batch * tiles * chunks
-  long long per_cta;                  // ceil(units / gridDim.x)
+  long long per_cta;                  // floor(units / gridDim.x): CTA b owns units [b*units/grid, (b+1)*units/grid)
   int max_contrib;                    // partial slots per tile
   float* partials;                    // [batch * tiles][max_contrib][M][tile columns]
   unsigned* counters;                 // [batch * tiles], zero before the first launch, left zero by every launch
@@ -89,6 +89,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+// Arrival counter with release/acquire semantics at device scope: together with the CTA barriers around it, the
+// partial sums every thread of this CTA wrote are visible to whichever CTA observes the final count.
+__device__ __forceinline__ unsigned arrive_acq_rel(unsigned* counter) {
+  unsigned old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
+
 // One box of the tensor map: x = first column (must be a multiple of 16 bytes), y = first row.
 __device__ __forceinline__ void tensor_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -181,8 +189,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_tma_kernel(const Params p,
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long u_begin = (long long)blockIdx.x * p.per_cta;
-  const long long u_end = min(u_begin + p.per_cta, p.units);
+  const long long u_begin = (long long)blockIdx.x * p.units / gridDim.x;
+  const long long u_end = (long long)(blockIdx.x + 1) * p.units / gridDim.x;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; s++) {
       mbar_init(&full[s], 1);
@@ -248,9 +256,10 @@ __global__ void __launch_bounds__(kThreads, 1) stream_tma_kernel(const Params p,
 #pragma unroll
           for (int v = 0; v < V; v++) red[(warp * M + m) * COLS + lane * V + v] = acc[m][v];
         asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32));
+        // CTA that owns unit u: the largest b with b*units/grid <= u, i.e. ceil((u+1)*grid/units) - 1.
         const long long tile_units_begin = cur_tile * p.chunks;
-        const long long first_cta = tile_units_begin / p.per_cta;
-        const long long last_cta = (tile_units_begin + p.chunks - 1) / p.per_cta;
+        const long long first_cta = ((tile_units_begin + 1) * gridDim.x + p.units - 1) / p.units - 1;
+        const long long last_cta = ((tile_units_begin + p.chunks) * gridDim.x + p.units - 1) / p.units - 1;
         const int contributors = (int)(last_cta - first_cta + 1);
         const long long n = p.n[pos.group];
         const long long col0 = (long long)pos.tile_in_group * COLS;
@@ -268,23 +277,21 @@ __global__ void __launch_bounds__(kThreads, 1) stream_tma_kernel(const Params p,
           }
         }
         if (contributors > 1) {
-          __threadfence();
           asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32));
-          if (threadIdx.x == 0) flags[0] = atomicAdd(&p.counters[cur_tile], 1u) == (unsigned)contributors - 1;
+          if (threadIdx.x == 0) flags[0] = arrive_acq_rel(&p.counters[cur_tile]) == (unsigned)contributors - 1;
           asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32));
           if (flags[0]) {
-            __threadfence();
             const float* base = p.partials + (cur_tile * p.max_contrib * (long long)M) * COLS;
             for (int idx = threadIdx.x; idx < M * COLS; idx += kConsumerWarps * 32) {
               const int m = idx / COLS, c = idx % COLS;
               float t = 0.f;
               int q = 0;
-              for (; q + 4 <= contributors; q += 4) {
-                float v[4];
+              for (; q + 8 <= contributors; q += 8) {  // loads first, then the adds in CTA order
+                float v[8];
 #pragma unroll
-                for (int e = 0; e < 4; e++) v[e] = __ldcg(base + (long long)(q + e) * M * COLS + idx);
+                for (int e = 0; e < 8; e++) v[e] = __ldcg(base + (long long)(q + e) * M * COLS + idx);
 #pragma unroll
-                for (int e = 0; e < 4; e++) t += v[e];
+                for (int e = 0; e < 8; e++) t += v[e];
               }
               for (; q < contributors; q++) t += __ldcg(base + (long long)q * M * COLS + idx);
               if (m < p.m && col0 + c < n) out[(long long)m * n + col0 + c] = Unpack<T>::store(t);
@@ -303,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_tma_kernel(const Params p,
     }
     pos = next;
     advance(p, &next);
-    // This chunk's lhs values: lane l holds x[k0 + l] and x[k0 + 32 + l] for every lhs row (loaded before the wait
+    // This chunk's lhs values: lane l holds x[k0 + l] (and x[k0 + 32 + l] for 64-row units) for every lhs row (loaded before the wait
     // so the latency hides behind it); rows are then broadcast with shuffles.
     const int k0 = pos.chunk * kUnitRows;
     float xa[M], xb[M];
@@ -311,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_tma_kernel(const Params p,
     for (int m = 0; m < M; m++) {
       const T* xr = lhs + (long long)m * p.lhs_m + (long long)(k0 + lane) * p.lhs_k;
       xa[m] = (m < p.m && k0 + lane < p.k) ? Unpack<T>::one(*xr) : 0.f;
-      xb[m] = (m < p.m && k0 + 32 + lane < p.k) ? Unpack<T>::one(xr[32 * p.lhs_k]) : 0.f;
+      xb[m] = (kUnitRows > 32 && m < p.m && k0 + 32 + lane < p.k) ? Unpack<T>::one(xr[32 * p.lhs_k]) : 0.f;
     }
     if (!mbar_wait(&full[stage], phase)) {
       if (lane == 0) atomicExch(p.error_flag, 2);
