@@ -244,6 +244,9 @@ int pjrtx_b200_plan_set_donation(PjrtxB200Plan *plan, const uint32_t *donated_pa
 /* verifyExecutablePlan (src/compiler/executable_plan_verify.zig:328-449): 1 when valid; otherwise writes the
  * diagnostic line into `out` (truncated to capacity, always NUL terminated) and returns 0. */
 int pjrtx_b200_plan_verify(PjrtxB200Plan *plan, char *out, uint64_t capacity);
+/* The plan itself as JSON (values, instructions, attributes, constant payloads in hex, shardings, outputs): the
+ * inverse of the builder calls above, used to inspect what pjrtx_b200_plan_partition produced. Returns the full length. */
+uint64_t pjrtx_b200_plan_describe(PjrtxB200Plan *plan, char *out, uint64_t capacity);
 /* Backend program graph (nodes, edges, fusion groups, schedule, liveness) as JSON; needs no device.
  * Returns the full length; writes at most capacity-1 bytes. program_build.build (program_build.zig:10-207). */
 uint64_t pjrtx_b200_plan_describe_program(PjrtxB200Plan *plan, char *out, uint64_t capacity);

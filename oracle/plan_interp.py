@@ -280,7 +280,7 @@ def _dot_general_f32(a, b, ins, cache, key):
 
 
 def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce=None, fast_dot: bool = False,
-             weight_cache: Dict[int, np.ndarray] = None) -> List[np.ndarray]:
+             weight_cache: Dict[int, np.ndarray] = None, all_gather=None) -> List[np.ndarray]:
     """Evaluates the recorded plan on host arrays and returns its outputs (storage dtypes).
 
     `fast_dot` switches contractions from float64 einsum to float32 BLAS (used only when the oracle is timed as the
@@ -408,6 +408,8 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
                 raise NotImplementedError(f"custom call {ins.target}")
         elif k == "all_reduce":
             r = all_reduce(x[0], code) if all_reduce is not None else x[0]
+        elif k == "all_gather":
+            r = all_gather(x[0], code) if all_gather is not None else x[0][None]
         else:
             raise NotImplementedError(k)
         r = np.ascontiguousarray(np.asarray(r)).reshape(dims)

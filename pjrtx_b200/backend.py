@@ -112,6 +112,7 @@ SYMBOLS = {
     "pjrtx_b200_plan_set_output_sharding": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_int, ctypes.c_char_p, ctypes.c_int64]),
     "pjrtx_b200_plan_set_donation": (ctypes.c_int, [_P, _U32P, ctypes.c_uint64, _U32P, _U32P, ctypes.c_uint64]),
     "pjrtx_b200_plan_verify": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_uint64]),
+    "pjrtx_b200_plan_describe": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_program": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_kernels": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_partition": (_P, [_P, ctypes.c_int32, ctypes.c_int32]),
@@ -351,6 +352,20 @@ class Backend:
             buf = ctypes.create_string_buffer(4096)
             ok = self.lib.pjrtx_b200_plan_verify(plan, buf, 4096)
             return "" if ok else buf.value.decode()
+        finally:
+            self.lib.pjrtx_b200_plan_destroy(plan)
+
+    def partition_plan(self, builder: plan_mod.PlanBuilder, partition: int) -> plan_mod.PlanBuilder:
+        """The tensor-parallel plan of one partition, read back as a PlanBuilder (for inspection and the CPU oracle)."""
+        plan = builder.build(self.lib)
+        try:
+            part = self.lib.pjrtx_b200_plan_partition(plan, partition, builder.num_partitions)
+            if not part:
+                raise BackendError("InvalidProgram", self._err())
+            try:
+                return plan_mod.PlanBuilder.from_description(json.loads(_text(self.lib, self.lib.pjrtx_b200_plan_describe, part)))
+            finally:
+                self.lib.pjrtx_b200_plan_destroy(part)
         finally:
             self.lib.pjrtx_b200_plan_destroy(plan)
 

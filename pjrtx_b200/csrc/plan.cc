@@ -272,4 +272,57 @@ std::string verify_plan(const Plan& plan) {
   return "";
 }
 
+std::string describe_plan(const Plan& plan) {
+  auto ints = [](const std::vector<int64_t>& v) {
+    std::string r = "[";
+    for (size_t i = 0; i < v.size(); i++) r += strfmt(i ? ",%lld" : "%lld", (long long)v[i]);
+    return r + "]";
+  };
+  auto ids = [](const std::vector<uint32_t>& v) {
+    std::string r = "[";
+    for (size_t i = 0; i < v.size(); i++) r += strfmt(i ? ",%u" : "%u", v[i]);
+    return r + "]";
+  };
+  auto sharding = [](const Sharding& sh) {
+    return strfmt("{\"kind\":%d,\"mesh\":\"%s\",\"split_dim\":%lld}", (int)sh.kind, sh.mesh_name.c_str(), (long long)sh.split_dim);
+  };
+  std::string s = strfmt("{\"num_replicas\":%d,\"num_partitions\":%d,\"values\":[", plan.num_replicas, plan.num_partitions);
+  for (size_t i = 0; i < plan.values.size(); i++) {
+    const Value& v = plan.values[i];
+    s += strfmt("%s{\"role\":%d,\"dtype\":%d,\"dims\":%s}", i ? "," : "", (int)v.role, v.dtype, ints(v.dims).c_str());
+  }
+  s += "],\"instructions\":[";
+  for (size_t i = 0; i < plan.instructions.size(); i++) {
+    const Instruction& ins = plan.instructions[i];
+    s += strfmt("%s{\"kind\":\"%s\",\"inputs\":%s,\"outputs\":%s,\"attrs\":{", i ? "," : "", kind_name(ins.kind),
+                ids(ins.inputs).c_str(), ids(ins.outputs).c_str());
+    bool first = true;
+    for (const auto& kv : ins.attrs) {
+      s += strfmt("%s\"%s\":%s", first ? "" : ",", kv.first.c_str(), ints(kv.second).c_str());
+      first = false;
+    }
+    s += "}";
+    if (!ins.literal.empty()) {
+      static const char* hex = "0123456789abcdef";
+      std::string h(ins.literal.size() * 2, '0');
+      for (size_t b = 0; b < ins.literal.size(); b++) {
+        h[2 * b] = hex[ins.literal[b] >> 4];
+        h[2 * b + 1] = hex[ins.literal[b] & 15];
+      }
+      s += ",\"literal\":\"" + h + "\"";
+    }
+    if (!ins.custom_call_target.empty()) s += ",\"target\":\"" + ins.custom_call_target + "\"";
+    s += "}";
+  }
+  s += "],\"outputs\":" + ids(plan.output_ids) + ",\"parameter_shardings\":[";
+  for (size_t i = 0; i < plan.parameter_shardings.size(); i++) s += (i ? "," : "") + sharding(plan.parameter_shardings[i]);
+  s += "],\"output_shardings\":[";
+  for (size_t i = 0; i < plan.output_shardings.size(); i++) s += (i ? "," : "") + sharding(plan.output_shardings[i]);
+  std::vector<int64_t> donated(plan.donated_parameter_indices.begin(), plan.donated_parameter_indices.end());
+  s += "],\"donated\":" + ints(donated) + ",\"aliases\":[";
+  for (size_t i = 0; i < plan.output_aliases.size(); i++)
+    s += strfmt("%s[%u,%u]", i ? "," : "", plan.output_aliases[i].output_index, plan.output_aliases[i].parameter_index);
+  return s + "]}";
+}
+
 }  // namespace pjrtx

@@ -111,4 +111,7 @@ struct Plan {
 //   invalid executable plan: pass=pjrtx-plan-verify [instruction=N] [value=N] detail="..." feature=<label>
 std::string verify_plan(const Plan& plan);
 
+// The whole plan as JSON (values, instructions with attributes, constant payloads as hex, shardings, outputs).
+std::string describe_plan(const Plan& plan);
+
 }  // namespace pjrtx

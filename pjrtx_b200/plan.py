@@ -304,6 +304,26 @@ class PlanBuilder:
         self.aliases = sorted((donate or {}).items())
         self.donated = sorted({p for _, p in self.aliases})
 
+    @classmethod
+    def from_description(cls, d: dict) -> "PlanBuilder":
+        """Rebuilds a builder from `pjrtx_b200_plan_describe` JSON."""
+        b = cls(d["num_replicas"], d["num_partitions"])
+        for i, v in enumerate(d["values"]):
+            b.values.append(ValueDesc(i, v["role"], v["dtype"], tuple(v["dims"])))
+            if v["role"] == ROLE_PARAMETER:
+                b.parameter_ids.append(i)
+        for ins in d["instructions"]:
+            kind = ins["kind"]
+            lit = bytes.fromhex(ins["literal"]) if "literal" in ins else None
+            b.instructions.append(Instr(kind, list(ins["inputs"]), list(ins["outputs"]), {k: list(v) for k, v in ins["attrs"].items()},
+                                        lit, ins.get("target")))
+        b.parameter_shardings = [(s["kind"], s["mesh"], s["split_dim"]) for s in d["parameter_shardings"]]
+        b.output_ids = list(d["outputs"])
+        b.output_shardings = [(s["kind"], s["mesh"], s["split_dim"]) for s in d["output_shardings"]]
+        b.donated = list(d["donated"])
+        b.aliases = [tuple(a) for a in d["aliases"]]
+        return b
+
     # ---- lowering to the C ABI --------------------------------------------------
     def build(self, lib) -> "ctypes.c_void_p":
         """Creates the C plan object; the caller owns it (pjrtx_b200_plan_destroy)."""
