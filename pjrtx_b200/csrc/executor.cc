@@ -892,7 +892,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     for (Step& st : kp->steps) {
       Step* prev = merged.empty() ? nullptr : &merged.back();
       bool can = prev && prev->type == Step::kDot && st.type == Step::kDot && prev->dot_scratch.path == 1 &&
-                 st.dot_scratch.path == 1 && prev->inputs[0] == st.inputs[0] && prev->dot.b0 * prev->dot.b1 == 1 &&
+                 st.dot_scratch.path == 1 && prev->dot_scratch.umma == st.dot_scratch.umma && prev->inputs[0] == st.inputs[0] && prev->dot.b0 * prev->dot.b1 == 1 &&
                  st.dot.b0 * st.dot.b1 == 1 && prev->dot.m == st.dot.m && prev->dot.k == st.dot.k &&
                  prev->dot.dtype == st.dot.dtype && prev->dot.lhs_m == st.dot.lhs_m && prev->dot.lhs_k == st.dot.lhs_k &&
                  std::max<size_t>(prev->dot_group.size(), 1) < (size_t)kDotGroupMax;
@@ -1037,8 +1037,8 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
         n_total = 0;
         for (const DotShape& d : st.dot_group) n_total += d.n;
       }
-      s += strfmt(",\"path\":%d,\"tma\":%d,\"grid\":%d,\"ksplit\":%d,\"b0\":%lld,\"b1\":%lld,\"m\":%lld,\"n\":%lld,\"k\":%lld,\"group\":%zu",
-                  st.dot_scratch.path, st.dot_scratch.tma, st.dot_scratch.grid, st.dot_scratch.ksplit, (long long)st.dot.b0, (long long)st.dot.b1, (long long)st.dot.m,
+      s += strfmt(",\"path\":%d,\"tma\":%d,\"umma\":%d,\"grid\":%d,\"ksplit\":%d,\"b0\":%lld,\"b1\":%lld,\"m\":%lld,\"n\":%lld,\"k\":%lld,\"group\":%zu",
+                  st.dot_scratch.path, st.dot_scratch.tma, st.dot_scratch.umma, st.dot_scratch.grid, st.dot_scratch.ksplit, (long long)st.dot.b0, (long long)st.dot.b1, (long long)st.dot.m,
                   n_total, (long long)st.dot.k, std::max<size_t>(st.dot_group.size(), 1));
     } else if (st.type == Step::kSliceUpdate) {
       s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");

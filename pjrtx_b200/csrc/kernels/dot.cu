@@ -14,14 +14,21 @@
 //   3  tile      : shared-memory tiled FFMA contraction with f32 accumulate,
 //                  any strides (f32 matmul at 1e-5 needs real FFMA, not TF32).
 //   0  generic   : one thread per output element, any strides, any m.
+// 16-bit floats without batch axes whose operands a TMA tensor map can describe run on the tensor cores instead
+// (umma_gemm.cuh): rhs[K,N] as a variant of path 1 (so that q/k/v and gate/up still share one launch), rhs[N,K] as
+// path 4. PJRTX_B200_UMMA=0 turns that off; PJRTX_B200_UMMA_MIN_M (default 9) keeps the CUDA-core streaming kernels
+// below that m.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 
 #include "../common.h"
 #include "kernels.h"
 #include "stream_tma.cuh"
+#include "umma_gemm.cuh"
 
 namespace pjrtx {
 
@@ -410,7 +417,12 @@ int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, con
 
 }  // namespace
 
-DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count) {
+namespace {
+int umma_eligible(const DotShape& s);
+DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_major);
+}  // namespace
+
+DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count, bool allow_tensor) {
   DotScratch p;
   p.path = 1;
   const DotShape& s = shapes[0];
@@ -423,6 +435,11 @@ DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count) {
     n_total += shapes[g].n;
   }
   const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
+  if (batch == 1 && allow_tensor) {
+    bool all_umma = true;
+    for (int g = 0; g < count; g++) all_umma &= umma_eligible(shapes[g]) == 1;
+    if (all_umma) return umma_plan(shapes, count, sm_count, false);
+  }
   if (batch == 1) {
     // Persistent TMA kernel: equal shares of (column tile, 64-row chunk) units per CTA.
     p.tma = 1;
@@ -544,12 +561,174 @@ int launch_tma(const DotShape* shapes, int count, const DotScratch& plan, const 
   }
 }
 
+
+// ---- tensor-core stream (umma_gemm.cuh) ---------------------------------------------------------------------------
+
+int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return v && *v ? atoi(v) : fallback;
+}
+
+// 0: not eligible, 1: rhs[K,N] with N contiguous, 2: rhs[N,K] with K contiguous. The tensor maps need 16-byte
+// multiples for every row stride; lhs must be k-contiguous.
+int umma_eligible(const DotShape& s) {
+  static const int enabled = env_int("PJRTX_B200_UMMA", 1);
+  static const int min_m = env_int("PJRTX_B200_UMMA_MIN_M", 9);
+  if (!enabled || (s.dtype != kF16 && s.dtype != kBF16)) return 0;
+  if (s.b0 * s.b1 != 1 || s.m < min_m || s.k < 1 || s.n < 1) return 0;
+  if (s.lhs_k != 1 || (s.m > 1 && s.lhs_m % 8 != 0)) return 0;
+  if (s.m > (1 << 20) || s.n > (1ll << 30) || s.k > (1ll << 30)) return 0;
+  if (s.rhs_n == 1 && s.rhs_k % 8 == 0 && s.rhs_k >= s.n) return 1;
+  if (s.rhs_k == 1 && s.rhs_n % 8 == 0 && s.rhs_n >= s.k) return 2;
+  return 0;
+}
+
+DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_major) {
+  DotScratch p;
+  const DotShape& s = shapes[0];
+  p.path = k_major ? 4 : 1;
+  p.umma = 1;
+  p.m_tile = (int)std::min<int64_t>(256, (s.m + 15) / 16 * 16);
+  const int64_t m_tiles = (s.m + p.m_tile - 1) / p.m_tile;
+  // 256-column tiles (two accumulators per tile) are available behind PJRTX_B200_UMMA_WIDE=1; measured on B200 they
+  // stream no faster than 128-column tiles and leave more partial sums to fold, so they are off by default.
+  int64_t tiles128 = 0;
+  for (int g = 0; g < count; g++) tiles128 += (shapes[g].n + 127) / 128 * m_tiles;
+  static const int wide = env_int("PJRTX_B200_UMMA_WIDE", 0);
+  p.nh = (wide && p.m_tile <= 128 && tiles128 * ((s.k + 63) / 64) >= 16 * (int64_t)sm_count) ? 2 : 1;
+  const int tw = umma::kTileN * p.nh;
+  int64_t tiles = 0;
+  for (int g = 0; g < count; g++) tiles += (shapes[g].n + tw - 1) / tw * m_tiles;
+  const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(tiles * ((s.k + 63) / 64), sm_count));
+  // 128-deep stages once every CTA still gets a long run of them; 64-deep otherwise (finer split, better balance).
+  p.sub = (p.nh == 1 && tiles * ((s.k + 127) / 128) >= 32 * grid) ? 2 : 1;
+  const int64_t kblocks = (s.k + 64 * p.sub - 1) / (64 * p.sub);
+  const int64_t units = tiles * kblocks;
+  p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(units, sm_count));
+  p.per_cta = units / p.grid;
+  p.max_contrib = (int)((kblocks + p.per_cta - 1) / p.per_cta) + 1;
+  const size_t stage = umma::stage_bytes(p.m_tile, p.sub, p.nh);
+  p.stages = (int)std::max<size_t>(2, std::min<size_t>(12, (227 * 1024 - 1536) / stage));
+  p.smem = umma::smem_bytes(p.stages, p.m_tile, p.sub, p.nh);
+  p.ksplit = p.max_contrib;
+  p.partial_bytes = (uint64_t)tiles * p.max_contrib * p.m_tile * tw * sizeof(float);
+  p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+  return p;
+}
+
+template <int SUB, int NH>
+int launch_umma_sub(const umma::Params& prm, const umma::Maps& maps, const DotScratch& plan, bool pdl, cudaStream_t stream) {
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(umma::umma_stream_kernel<SUB, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return 0;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  cfg.blockDim = dim3(umma::kThreads);
+  cfg.dynamicSmemBytes = plan.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, umma::umma_stream_kernel<SUB, NH>, prm, maps) == cudaSuccess ? 1 : 0;
+}
+
+int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs, void* const* out,
+                void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
+  const DotShape& s = shapes[0];
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return 0;
+  const bool k_major = plan.path == 4;
+  const int tw = umma::kTileN * plan.nh;
+  umma::Params p{};
+  umma::Maps maps{};
+  p.m = (int)s.m;
+  p.k = (int)s.k;
+  p.m_tile = plan.m_tile;
+  p.m_tiles = (int)((s.m + plan.m_tile - 1) / plan.m_tile);
+  p.count = count;
+  const CUtensorMapDataType dt = s.dtype == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const cuuint32_t estr[2] = {1, 1};
+  // One 3-d copy per stage when every rhs is made of whole 64-column blocks (a ragged last block would make the
+  // view read past the end of the last row).
+  static const int allow_3d = env_int("PJRTX_B200_UMMA_3D", 1);
+  bool use_3d = allow_3d && !k_major;
+  for (int g = 0; g < count; g++) use_3d &= shapes[g].n % 64 == 0;
+  int tiles = 0;
+  for (int g = 0; g < count; g++) {
+    if ((reinterpret_cast<uintptr_t>(rhs[g]) & 15) != 0) return 0;
+    p.tile_begin[g] = tiles;
+    tiles += (int)((shapes[g].n + tw - 1) / tw) * p.m_tiles;
+    p.out[g] = out[g];
+    p.n[g] = shapes[g].n;
+    p.ldo[g] = shapes[g].out_m;
+  }
+  auto encode_rhs = [&](bool three_d) {
+    for (int g = 0; g < count; g++) {
+      cuuint64_t gdim[3], gstride[2];
+      cuuint32_t box[3];
+      const cuuint32_t estr3[3] = {1, 1, 1};
+      int rank = 2;
+      if (three_d) {
+        rank = 3;
+        gdim[0] = 64; gdim[1] = (cuuint64_t)s.k; gdim[2] = (cuuint64_t)shapes[g].n / 64;
+        gstride[0] = (cuuint64_t)shapes[g].rhs_k * 2; gstride[1] = 128;
+        box[0] = 64; box[1] = (cuuint32_t)(64 * plan.sub); box[2] = (cuuint32_t)(2 * plan.nh);
+      } else if (k_major) {
+        gdim[0] = (cuuint64_t)s.k; gdim[1] = (cuuint64_t)shapes[g].n;
+        gstride[0] = (cuuint64_t)shapes[g].rhs_n * 2;
+        box[0] = 64; box[1] = 128;
+      } else {
+        gdim[0] = (cuuint64_t)shapes[g].n; gdim[1] = (cuuint64_t)s.k;
+        gstride[0] = (cuuint64_t)shapes[g].rhs_k * 2;
+        box[0] = 64; box[1] = (cuuint32_t)(64 * plan.sub);
+      }
+      if (enc(&maps.rhs[g], dt, rank, const_cast<void*>(rhs[g]), gdim, gstride, box, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    }
+    return true;
+  };
+  if (use_3d && !encode_rhs(true)) use_3d = false;  // the driver refused the view: fall back to two boxes per half
+  if (!use_3d && !encode_rhs(false)) return 0;
+  p.rhs_3d = use_3d ? 1 : 0;
+  for (int g = count; g <= umma::kGroupMax; g++) p.tile_begin[g] = tiles;
+  for (int g = count; g < umma::kGroupMax; g++) maps.rhs[g] = maps.rhs[0];
+  {
+    if ((reinterpret_cast<uintptr_t>(lhs) & 15) != 0) return 0;
+    cuuint64_t gdim[2] = {(cuuint64_t)s.k, (cuuint64_t)s.m};
+    // A single row has no stride to honour; any 16-byte multiple that covers the row will do.
+    cuuint64_t gstride[1] = {(cuuint64_t)(s.m > 1 ? s.lhs_m : (s.k + 7) / 8 * 8) * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)plan.m_tile};
+    if (enc(&maps.lhs, dt, 2, const_cast<void*>(lhs), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return 0;
+  }
+  p.kblocks = (int)((s.k + 64 * plan.sub - 1) / (64 * plan.sub));
+  p.units = (long long)tiles * p.kblocks;
+  p.max_contrib = plan.max_contrib;
+  p.partials = static_cast<float*>(partials);
+  p.counters = static_cast<unsigned*>(counters);
+  p.error_flag = error_flag;
+  p.stages = plan.stages;
+  p.is_bf16 = s.dtype == kBF16;
+  p.rhs_k_major = k_major ? 1 : 0;
+  p.early_rhs = early_rhs ? 1 : 0;
+  if (plan.nh == 2)
+    return plan.sub == 2 ? launch_umma_sub<2, 2>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 2>(p, maps, plan, pdl, stream);
+  return plan.sub == 2 ? launch_umma_sub<2, 1>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 1>(p, maps, plan, pdl, stream);
+}
+
 }  // namespace
 
 int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
                      void* const* out, void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl,
                      cudaStream_t stream) {
   if (count < 1 || count > kDotGroupMax) return 0;
+  if (plan.umma) return launch_umma(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
   if (plan.tma) {
     switch (shapes[0].dtype) {
       case kF32: return launch_tma<float>(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
@@ -574,6 +753,9 @@ DotScratch dot_plan(const DotShape& s, int sm_count) {
   const int64_t batch = s.b0 * s.b1;
   auto aligned = [&](int64_t stride) { return stride % V == 0; };
   const bool batches_fit = batch <= 65535;
+  const int tensor = umma_eligible(s);
+  if (tensor == 1) return umma_plan(&s, 1, sm_count, false);
+  if (tensor == 2) return umma_plan(&s, 1, sm_count, true);
   if (s.m <= 8 && s.rhs_n == 1 && s.n % V == 0 && aligned(s.rhs_k) && aligned(s.rhs_b0) && aligned(s.rhs_b1) &&
       batches_fit && s.k >= 1) {
     p.path = 1;
@@ -596,7 +778,7 @@ DotScratch dot_plan(const DotShape& s, int sm_count) {
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
                void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
   if (s.b0 * s.b1 * s.m * s.n == 0) return 1;
-  if (plan.path == 1 && plan.tma) {
+  if (plan.umma || (plan.path == 1 && plan.tma)) {
     const void* rhs_list[1] = {rhs};
     void* out_list[1] = {out};
     return dot_group_launch(&s, 1, plan, lhs, rhs_list, out_list, partials, counters, error_flag, early_rhs, pdl, stream);

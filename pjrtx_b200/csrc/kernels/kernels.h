@@ -47,9 +47,13 @@ struct DotScratch {
   uint64_t partial_bytes = 0;
   uint64_t counter_bytes = 0;
   int ksplit = 1;
-  int path = 0;  // 0 generic, 1 streaming rhs[K,N] (N contiguous), 2 streaming rhs[N,K] (K contiguous), 3 f32 tile
+  // 0 generic, 1 streaming rhs[K,N] (N contiguous), 2 streaming rhs[N,K] (K contiguous), 3 f32 tile,
+  // 4 tensor-core stream with rhs[N,K] (K contiguous)
+  int path = 0;
   // Path 1 without batch axes runs the TMA-fed persistent kernel (stream-K decomposition).
   int tma = 0;
+  // Paths 1 and 4 for 16-bit floats without batch axes can run on the tensor cores (tcgen05, accumulator in TMEM).
+  int umma = 0, m_tile = 0, sub = 1, nh = 1;
   int grid = 0, stages = 0, max_contrib = 0;
   long long per_cta = 0;
   uint64_t smem = 0;
@@ -58,7 +62,8 @@ struct DotScratch {
 constexpr int kDotGroupMax = 4;
 
 // Streaming contractions (path 1) that share lhs, m, k, dtype and have no batch axes can run as one launch.
-DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count);
+// `allow_tensor` = false keeps the CUDA-core streaming kernel even where the tensor-core one would apply.
+DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count, bool allow_tensor = true);
 // `error_flag` (device-visible int) receives a non-zero code if a bounded device-side wait gives up.
 // `early_rhs`: the rhs operands are never written by earlier work of the same stream, so their copies may start
 // before the preceding kernel has finished (programmatic dependent launch).

@@ -167,7 +167,7 @@ int stream_dot_static_scratch(int device, int dtype, const void* lhs, const void
   s.rhs_k = n;
   s.rhs_n = 1;
   s.out_m = n;
-  const DotScratch plan = dot_group_plan(&s, 1, sm_count);
+  const DotScratch plan = dot_group_plan(&s, 1, sm_count, /*allow_tensor=*/false);
   if (!plan.tma || plan.partial_bytes > kStaticPartialBytes || plan.counter_bytes > kStaticCounterBytes) {
     set_last_error("contraction m=%lld k=%lld n=%lld needs %llu bytes of partial sums and %llu bytes of counters; the static "
                    "scratch holds %zu and %zu",

@@ -13,7 +13,7 @@ def _decode_args(cfg, names, weights, caches, tokens, pos):
     return [np.asarray(tokens, np.int32), np.array(pos, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
 
 
-@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("batch", [1, 2, 16, 32])
 def test_tiny_decode_steps_teacher_forced(gpu_backend, batch):
     """Four decode steps; every step the backend gets the oracle's token and caches' history.
 
@@ -27,6 +27,9 @@ def test_tiny_decode_steps_teacher_forced(gpu_backend, batch):
     weights = llama.make_weights(cfg, seed=0)
     caches = llama.make_kv_cache(cfg, batch, max_len, filled)
     exe = be.compile_executable(builder, [0])
+    if batch > 8:  # batched decode projections run on the tensor cores
+        dots = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
+        assert dots and all(s["umma"] == 1 for s in dots), dots
     wbufs = [be.buffer_from_host(weights[n]) for n in names[2:2 + len(weights)]]
     cbufs = [be.buffer_from_host(c) for c in caches]
     tokens = np.arange(3, 3 + batch, dtype=np.int32)

@@ -171,6 +171,41 @@ def test_streaming_dot_paths_against_f64(gpu_backend):
             assert all(np.array_equal(a.view(np.uint8), c.view(np.uint8)) for a, c in zip(got, again))
 
 
+@pytest.mark.parametrize("dtype", [P.BF16_CODE, P.F16])
+def test_tensor_core_dot_shapes_against_f64(gpu_backend, dtype):
+    """16-bit contractions on the tcgen05 path: one row up to several 256-row tiles, ragged k and n, both rhs layouts,
+    three contractions sharing lhs in one launch; error bounded by the summed magnitudes, repeated runs bit-identical."""
+    rng = np.random.default_rng(23)
+    dt = P.np_dtype(dtype)
+    rtol = 2e-2
+    for m, k, n in ((1, 4096, 4096), (16, 64, 128), (32, 4096, 1024), (20, 200, 264), (5, 520, 136), (256, 512, 384),
+                    (300, 1024, 1000), (600, 328, 520)):
+        lhs = rng.standard_normal((m, k), dtype=np.float32).astype(dt)
+        rkn = rng.standard_normal((k, n), dtype=np.float32).astype(dt)
+        rkn2 = rng.standard_normal((k, 256), dtype=np.float32).astype(dt)
+        b = PlanBuilder()
+        pl, pr, pr2 = b.parameter(dtype, lhs.shape), b.parameter(dtype, rkn.shape), b.parameter(dtype, rkn2.shape)
+        prt = b.parameter(dtype, (n, k))
+        b.set_outputs([b.dot_general(pl, pr, [1], [0]), b.dot_general(pl, pr2, [1], [0]), b.dot_general(pl, prt, [1], [1])])
+        exe = gpu_backend.compile_executable(b, [0])
+        steps = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
+        # more than eight rows always take the tensor-core kernel; fewer keep the CUDA-core streaming kernels by default
+        assert steps and (m <= 8 or all(s["umma"] == 1 for s in steps)), steps
+        assert any(s["group"] == 2 for s in steps), steps  # the two rhs[K,N] contractions share a launch
+        rnk = np.ascontiguousarray(rkn.T)
+        got = run_backend(gpu_backend, b, [lhs, rkn, rkn2, rnk], exe=exe)
+        again = run_backend(gpu_backend, b, [lhs, rkn, rkn2, rnk], exe=exe)
+        exe.destroy()
+        l64 = lhs.astype(np.float64)
+        for g, r in zip(got, (rkn, rkn2, rkn)):
+            want = l64 @ r.astype(np.float64)
+            mag = np.abs(l64) @ np.abs(r.astype(np.float64))
+            err = np.abs(g.astype(np.float64) - want)
+            assert g.shape == want.shape
+            assert np.all(err <= rtol * mag * 0.05 + 2.0 ** -8 * np.abs(want)), (dtype, m, k, n, float((err / mag).max()))
+        assert all(np.array_equal(a.view(np.uint8), c.view(np.uint8)) for a, c in zip(got, again))
+
+
 def test_donated_slice_update_is_in_place(gpu_backend):
     be = gpu_backend
     b = PlanBuilder()
