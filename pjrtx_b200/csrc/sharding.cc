@@ -1,6 +1,7 @@
 #include "sharding.h"
 
 #include <algorithm>
+#include <map>
 
 #include "program.h"
 
@@ -30,6 +31,9 @@ class Partitioner {
       out_.device_assignment.push_back((int32_t)out_.device_assignment.size());
     map_.assign(full_.values.size(), UINT32_MAX);
     state_.assign(full_.values.size(), State{});
+    producer_.assign(full_.values.size(), -1);
+    for (size_t i = 0; i < full_.instructions.size(); i++)
+      for (uint32_t o : full_.instructions[i].outputs) producer_[o] = (long)i;
     // Parameters first, in order, so parameter indices are unchanged.
     size_t p = 0;
     for (const Value& v : full_.values) {
@@ -70,6 +74,8 @@ class Partitioner {
   Plan out_;
   std::vector<uint32_t> map_;   // full value -> local value
   std::vector<State> state_;    // of the local value
+  std::vector<long> producer_;  // full value -> full instruction that defines it
+  std::map<std::pair<uint32_t, int64_t>, uint32_t> localized_;
 
   [[noreturn]] void fail(const std::string& why) { throw Fail{why}; }
 
@@ -152,6 +158,56 @@ class Partitioner {
     return emit(Kind::slice, {map_[v]}, lv.dtype, dims, {{"start_indices", start}, {"limit_indices", limit}, {"strides", strides}});
   }
 
+  // Local block of a replicated value along `dim`, rebuilt from its definition where that costs nothing: a broadcast
+  // that is constant along `dim`, an iota along another axis, or elementwise work over such values is emitted at the
+  // local shape (so a causal mask or a splatted scale stays a recognisable splat instead of becoming a slice of a
+  // full-size tensor); everything else is sliced. The full-size definition is left for dead-code elimination.
+  uint32_t localize(uint32_t v, int64_t dim, int depth = 0) {
+    const auto key = std::make_pair(v, dim);
+    auto hit = localized_.find(key);
+    if (hit != localized_.end()) return hit->second;
+    uint32_t result = UINT32_MAX;
+    const long p = producer_[v];
+    const Value& fv = full_.values[v];
+    if (p >= 0 && depth < 12 && fv.dims[dim] % parts_ == 0) {
+      const Instruction& ins = full_.instructions[p];
+      std::vector<int64_t> dims = fv.dims;
+      dims[dim] /= parts_;
+      auto rebuild = [&](const std::vector<uint32_t>& inputs) {
+        Instruction n = ins;
+        n.inputs = inputs;
+        n.outputs = {add_value(ValueRole::instruction_result, fv.dtype, dims)};
+        if (n.has("dims")) n.attrs["dims"] = dims;
+        out_.instructions.push_back(n);
+        return n.outputs[0];
+      };
+      const NodeKind nk = program_node_kind(ins.kind);
+      if (ins.kind == Kind::broadcast_in_dim && state_[ins.inputs[0]].kind == State::kReplicated) {
+        const std::vector<int64_t>& bd = ins.list("broadcast_dimensions");
+        long source = -1;
+        for (size_t k = 0; k < bd.size(); k++)
+          if (bd[k] == dim) source = (long)k;
+        const Value& operand = full_.values[ins.inputs[0]];
+        if (source < 0 || operand.dims[source] == 1) result = rebuild({map_[ins.inputs[0]]});
+        else result = rebuild({localize(ins.inputs[0], source, depth + 1)});
+      } else if (ins.kind == Kind::iota && ins.scalar("iota_dimension", -1) != dim) {
+        result = rebuild({});
+      } else if ((nk == NodeKind::elementwise || ins.kind == Kind::convert) && ins.outputs.size() == 1) {
+        bool ok = true;
+        for (uint32_t in : ins.inputs)
+          ok &= state_[in].kind == State::kReplicated && (full_.values[in].count() == 1 || full_.values[in].dims == fv.dims);
+        if (ok) {
+          std::vector<uint32_t> inputs;
+          for (uint32_t in : ins.inputs) inputs.push_back(full_.values[in].count() == 1 ? map_[in] : localize(in, dim, depth + 1));
+          result = rebuild(inputs);
+        }
+      }
+    }
+    if (result == UINT32_MAX) result = slice_replicated(v, dim);
+    localized_[key] = result;
+    return result;
+  }
+
   void copy_instruction(const Instruction& ins, const std::vector<uint32_t>& inputs, const State& st,
                         const std::map<std::string, std::vector<int64_t>>* attrs = nullptr) {
     Instruction n = ins;
@@ -198,7 +254,7 @@ class Partitioner {
       if (st.kind == State::kSplit)
         for (size_t k = 0; k < ins.inputs.size(); k++)
           if (state_[ins.inputs[k]].kind == State::kReplicated && full_.values[ins.inputs[k]].count() != 1)
-            in[k] = slice_replicated(ins.inputs[k], st.dim);
+            in[k] = localize(ins.inputs[k], st.dim);
       copy_instruction(ins, in, st);
       return;
     }
@@ -267,7 +323,7 @@ class Partitioner {
           if (along == st.dim) fail("concatenate along a split dimension");
           for (size_t k = 0; k < ins.inputs.size(); k++) {
             const State& s = state_[ins.inputs[k]];
-            if (s.kind == State::kReplicated) in[k] = slice_replicated(ins.inputs[k], st.dim);
+            if (s.kind == State::kReplicated) in[k] = localize(ins.inputs[k], st.dim);
             else if (s.dim != st.dim) fail("operands are split along different dimensions");
           }
         }
@@ -280,7 +336,7 @@ class Partitioner {
         auto attrs = ins.attrs;
         if (ins.kind == Kind::dynamic_update_slice) {
           const State& us = state_[ins.inputs[1]];
-          if (st.kind == State::kSplit && us.kind == State::kReplicated) in[1] = slice_replicated(ins.inputs[1], st.dim);
+          if (st.kind == State::kSplit && us.kind == State::kReplicated) in[1] = localize(ins.inputs[1], st.dim);
           else if (st.kind != us.kind || st.dim != us.dim) fail("dynamic_update_slice operand and update are sharded differently");
         } else if (st.kind == State::kSplit) {
           const auto& id = full_.values[ins.inputs[0]].dims;

@@ -230,3 +230,15 @@ def test_execute_requires_gpu_and_fails_loudly(backend):
         backend.compile_executable(b, [0])
     with pytest.raises(be_mod.BackendError):
         backend.buffer_from_host(np.zeros(4, np.float32))
+
+
+def test_partitioned_decode_keeps_attention_recognisable(backend):
+    """Splatted scale / mask operands are rebuilt at the local shape, not sliced out of full-size tensors, so every
+    partition still maps its attention block onto the split-KV kernel and carries no full-size mask."""
+    cfg = llama.TINY
+    b, _ = llama.build_decode_step(cfg, 2, 64, num_partitions=2)
+    for part in range(2):
+        k = backend.describe_kernels(b, partition=part)
+        kinds = [s["type"] for s in k["steps"]]
+        assert kinds.count("attention_decode") == cfg.layers
+        assert kinds.count("all_reduce") == 2 * cfg.layers and kinds.count("all_gather") == 1
