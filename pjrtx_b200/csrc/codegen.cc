@@ -209,8 +209,9 @@ struct VecAccess {
 
 class Gen {
  public:
-  Gen(const Plan& plan, const std::vector<size_t>& nodes, const std::vector<uint32_t>& outputs, int sm_count)
-      : plan_(plan), nodes_(nodes), outputs_(outputs), sm_count_(sm_count > 0 ? sm_count : 148) {
+  Gen(const Plan& plan, const std::vector<size_t>& nodes, const std::vector<uint32_t>& outputs,
+      const std::vector<size_t>& scatters, int sm_count)
+      : plan_(plan), nodes_(nodes), outputs_(outputs), scatters_(scatters), sm_count_(sm_count > 0 ? sm_count : 148) {
     for (size_t n : nodes)
       for (uint32_t o : plan.instructions[n].outputs) producer_[o] = n;
     for (size_t i = 0; i < plan.instructions.size(); i++)
@@ -234,6 +235,12 @@ class Gen {
     for (size_t s = 0; s < outputs_.size(); s++)
       sig += strfmt("%s%s* __restrict__ out%zu", (s || !inputs_.empty()) ? ", " : "",
                     ctype(plan_.values[outputs_[s]].dtype), s);
+    for (size_t q = 0; q < scatters_.size(); q++) {
+      const uint32_t dst = plan_.instructions[scatters_[q]].outputs[0];
+      sig += strfmt("%s%s* __restrict__ dst%zu", (q || !outputs_.empty() || !inputs_.empty()) ? ", " : "",
+                    ctype(plan_.values[dst].dtype), q);
+      k.scatter_dst.push_back(dst);
+    }
     k.name = "pjrtx_fused";
     k.source = std::string(kPreamble) + strfmt("typedef %s idx_t;\n", wide_index_ ? "long long" : "int") +
                strfmt("extern \"C\" __global__ void __launch_bounds__(%d) pjrtx_fused(%s) {\n", k.block,
@@ -252,6 +259,7 @@ class Gen {
   const Plan& plan_;
   std::vector<size_t> nodes_;
   std::vector<uint32_t> outputs_;
+  std::vector<size_t> scatters_;  // in-place dynamic_update_slice instructions performed as offset stores
   int sm_count_;
   std::map<uint32_t, size_t> producer_;     // value -> in-group instruction
   std::map<uint32_t, size_t> constant_of_;  // value -> constant instruction
@@ -352,7 +360,9 @@ class Gen {
       if (!allow_serial_) fail("reduction is not a uniform suffix-axis reduction");
       row_ = false;
     }
-    if (outputs_.empty()) fail("group has no stored value");
+    if (outputs_.empty() && scatters_.empty()) fail("group has no stored value");
+    if (row_ && !scatters_.empty()) fail("slice update inside a row kernel");
+    std::vector<int64_t> counts;  // element counts of everything a map kernel stores (one loop per distinct count)
     for (uint32_t o : outputs_) {
       if (!in_group(o)) fail("stored value is not produced in the group");
       if (!ctype(val(o).dtype)) fail("unsupported element type");
@@ -360,10 +370,20 @@ class Gen {
       if (row_) {
         if (n != N_ && n != R_) fail("stored value does not span the row space");
       } else {
-        if (N_ == 0) N_ = n;
-        if (n != N_) fail("stored values have different element counts");
+        N_ = std::max(N_, n);
+        counts.push_back(n);
       }
       depth_of(o);
+    }
+    for (size_t n : scatters_) {
+      const Instruction& ins = plan_.instructions[n];
+      if (ins.kind != Kind::dynamic_update_slice || ins.inputs.size() != 2 + val(ins.inputs[0]).dims.size())
+        fail("malformed slice update");
+      const Value& update = val(ins.inputs[1]);
+      if (!ctype(update.dtype) || update.dims.size() != val(ins.inputs[0]).dims.size()) fail("unsupported slice update");
+      N_ = std::max(N_, update.count());
+      counts.push_back(update.count());
+      depth_of(ins.inputs[1]);
     }
     if (N_ == 0) fail("empty iteration space");
     // Vector width: 16 bytes of the widest element that is read or written
@@ -373,9 +393,11 @@ class Gen {
     for (size_t n : nodes_)
       for (uint32_t v : plan_.instructions[n].inputs)
         if (!in_group(v) && val(v).count() > 1) widest = std::max(widest, dtype_size(val(v).dtype));
+    for (size_t n : scatters_) widest = std::max(widest, dtype_size(val(plan_.instructions[n].inputs[1]).dtype));
     vec_ = (int)(16 / widest);
-    int64_t extent = row_ ? C_ : N_;
-    while (vec_ > 1 && extent % vec_ != 0) vec_ /= 2;
+    if (row_) counts = {C_};
+    for (int64_t extent : counts)
+      while (vec_ > 1 && extent % vec_ != 0) vec_ /= 2;
   }
 
   // ---- index helpers ----------------------------------------------------
@@ -443,7 +465,7 @@ class Gen {
   Idx broadcast_index(const Idx& out_idx, const std::vector<int64_t>& od, const std::vector<int64_t>& odims,
                       const std::vector<int64_t>& bd) {
     int64_t ocount = element_count(od);
-    if (ocount == 1) return scalar_index();
+    if (ocount == 1) return (row_ && R_ == 1) ? Idx{"r", IdxClass::ROW} : scalar_index();  // one row: the scalar is the row's value
     // Significant operand axes (size > 1) and the output axes they map to.
     std::vector<size_t> sig;
     for (size_t k = 0; k < od.size(); k++)
@@ -789,7 +811,7 @@ class Gen {
       case Kind::reduce_sum: case Kind::reduce_max: case Kind::reduce_min: case Kind::reduce_and: case Kind::reduce_or: {
         auto rv = reduce_var_.find(v);
         if (row_) {
-          if (idx.cls != IdxClass::ROW) fail("reduction result is read at a non-row index");
+          if (idx.cls != IdxClass::ROW && R_ != 1) fail("reduction result is read at a non-row index");
           if (rv == reduce_var_.end()) fail("reduction result is read before its stage");
           return rv->second;
         }
@@ -902,50 +924,112 @@ class Gen {
   }
 
   // ---- kernels ----------------------------------------------------------
+  // Index into the destination of an in-place slice update for element `i` of the update: update coordinates plus
+  // the start indices, each clamped so that the update stays inside the destination (StableHLO semantics).
+  std::string scatter_index(const Instruction& ins, const std::string& i) {
+    const auto& dd = val(ins.inputs[0]).dims;
+    const auto& ud = val(ins.inputs[1]).dims;
+    std::vector<std::string> uc = coords(i, ud), dc(dd.size());
+    for (size_t d = 0; d < dd.size(); d++) {
+      if (ud[d] > dd[d]) fail("slice update larger than its destination");
+      if (ud[d] == dd[d]) {  // the clamp leaves 0
+        dc[d] = uc[d];
+        continue;
+      }
+      std::string start = emit(ins.inputs[2 + d], scalar_index());
+      std::string clamped = index_var(strfmt("min(max((idx_t)%s, (idx_t)0), (idx_t)%lld)", start.c_str(), (long long)(dd[d] - ud[d])));
+      dc[d] = uc[d] == "0" ? clamped : "(" + uc[d] + " + " + clamped + ")";
+    }
+    return index_var(linearize(dc, dd));
+  }
+
+  // Map kernel: one grid-stride loop per distinct element count among the stored values and slice updates.
   std::string emit_map_kernel(FusedKernel* k) {
     k->block = 256;
-    int64_t items = (N_ + vec_ - 1) / vec_;
+    const int64_t n_max = N_;
+    int64_t items = (n_max + vec_ - 1) / vec_;
     k->grid = std::max<int64_t>(1, std::min<int64_t>((items + k->block - 1) / k->block, (int64_t)sm_count_ * 16));
     k->stages = 1;
+    struct Item { bool scatter; size_t index; int64_t count; };
+    std::vector<Item> all;
+    for (size_t s = 0; s < outputs_.size(); s++) all.push_back(Item{false, s, val(outputs_[s]).count()});
+    for (size_t q = 0; q < scatters_.size(); q++)
+      all.push_back(Item{true, q, val(plan_.instructions[scatters_[q]].inputs[1]).count()});
+    std::vector<int64_t> distinct;
+    for (const Item& it : all)
+      if (std::find(distinct.begin(), distinct.end(), it.count) == distinct.end()) distinct.push_back(it.count);
     Scope top;
     scopes_.push_back(&top);
-    Scope body;
-    body.indent = vec_ > 1 ? 6 : 4;
-    scopes_.push_back(&body);
-    in_vec_loop_ = true;
-    vec_loads_.clear();
-    Idx lin{"i", IdxClass::LIN};
-    std::vector<std::string> results;
-    for (uint32_t o : outputs_) results.push_back(emit(o, lin));
-    for (size_t s = 0; s < outputs_.size(); s++) {
-      std::string sv = store_conv(val(outputs_[s]).dtype, results[s]);
-      line(vec_ > 1 ? strfmt("S%zu[v] = %s;", s, sv.c_str()) : strfmt("out%zu[i] = %s;", s, sv.c_str()));
-    }
-    scopes_.pop_back();
-    in_vec_loop_ = false;
-    std::string code = top.code;
-    if (vec_ > 1) {
-      code += strfmt("  for (idx_t i0 = ((idx_t)blockIdx.x * %d + threadIdx.x) * %d; i0 < %lld; i0 += (idx_t)gridDim.x * %d) {\n",
-                     k->block, vec_, (long long)N_, k->block * vec_);
-      for (const VecAccess& a : vec_loads_) {
-        const char* t = ctype(val(a.value).dtype);
-        code += strfmt("    __align__(16) %s %s[%d]; ldvec<%s, %d>(%s, in%d + i0);\n", t, a.array.c_str(), vec_, t, vec_,
-                       a.array.c_str(), input_slot_[a.value]);
+    std::string loops;
+    for (size_t g = 0; g < distinct.size(); g++) {
+      N_ = distinct[g];  // contiguity of loads is judged against this loop's extent
+      Scope body;
+      body.indent = vec_ > 1 ? 6 : 4;
+      scopes_.push_back(&body);
+      in_vec_loop_ = true;
+      vec_loads_.clear();
+      Idx lin{"i", IdxClass::LIN};
+      std::vector<std::string> decl, after;
+      for (const Item& it : all) {
+        if (it.count != N_) continue;
+        if (!it.scatter) {
+          const size_t s = it.index;
+          const char* t = ctype(val(outputs_[s]).dtype);
+          std::string sv = store_conv(val(outputs_[s]).dtype, emit(outputs_[s], lin));
+          line(vec_ > 1 ? strfmt("S%zu[v] = %s;", s, sv.c_str()) : strfmt("out%zu[i] = %s;", s, sv.c_str()));
+          if (vec_ > 1) {
+            decl.push_back(strfmt("    __align__(16) %s S%zu[%d];\n", t, s, vec_));
+            after.push_back(strfmt("    stvec<%s, %d>(out%zu + i0, S%zu);\n", t, vec_, s, s));
+          }
+        } else {
+          const size_t q = it.index;
+          const Instruction& ins = plan_.instructions[scatters_[q]];
+          const int dt = val(ins.inputs[1]).dtype;
+          const char* t = ctype(dt);
+          // Vector stores need the trailing full-extent axes of the update to hold whole vectors.
+          const auto& dd = val(ins.inputs[0]).dims;
+          const auto& ud = val(ins.inputs[1]).dims;
+          // (a window inside an axis starts at a run-time offset, so only full axes guarantee alignment)
+          int64_t run = 1;
+          for (size_t d = ud.size(); d-- > 0 && ud[d] == dd[d];) run *= ud[d];
+          std::string sv = store_conv(dt, emit(ins.inputs[1], lin));
+          if (vec_ > 1 && run % vec_ == 0) {
+            line(strfmt("D%zu[v] = %s;", q, sv.c_str()));
+            line(strfmt("if (v == 0) D%zu_at = %s;", q, scatter_index(ins, "i").c_str()));
+            decl.push_back(strfmt("    __align__(16) %s D%zu[%d]; idx_t D%zu_at = 0;\n", t, q, vec_, q));
+            after.push_back(strfmt("    stvec<%s, %d>(dst%zu + D%zu_at, D%zu);\n", t, vec_, q, q, q));
+          } else {
+            line(strfmt("dst%zu[%s] = %s;", q, scatter_index(ins, "i").c_str(), sv.c_str()));
+          }
+        }
       }
-      for (size_t s = 0; s < outputs_.size(); s++)
-        code += strfmt("    __align__(16) %s S%zu[%d];\n", ctype(val(outputs_[s]).dtype), s, vec_);
-      code += strfmt("#pragma unroll\n    for (int v = 0; v < %d; v++) {\n      const idx_t i = i0 + v;\n", vec_);
-      code += body.code;
-      code += "    }\n";
-      for (size_t s = 0; s < outputs_.size(); s++)
-        code += strfmt("    stvec<%s, %d>(out%zu + i0, S%zu);\n", ctype(val(outputs_[s]).dtype), vec_, s, s);
-      code += "  }\n";
-    } else {
-      code += strfmt("  for (idx_t i = (idx_t)blockIdx.x * %d + threadIdx.x; i < %lld; i += (idx_t)gridDim.x * %d) {\n",
-                     k->block, (long long)N_, k->block);
-      code += body.code;
-      code += "  }\n";
+      scopes_.pop_back();
+      in_vec_loop_ = false;
+      // Later loops start at a rotated block so that small loops do not all land on block 0.
+      std::string bx = g == 0 ? "blockIdx.x" : strfmt("((blockIdx.x + %zuu) %% gridDim.x)", g);
+      if (vec_ > 1) {
+        loops += strfmt("  for (idx_t i0 = ((idx_t)%s * %d + threadIdx.x) * %d; i0 < %lld; i0 += (idx_t)gridDim.x * %d) {\n",
+                        bx.c_str(), k->block, vec_, (long long)N_, k->block * vec_);
+        for (const VecAccess& a : vec_loads_) {
+          const char* t = ctype(val(a.value).dtype);
+          loops += strfmt("    __align__(16) %s %s[%d]; ldvec<%s, %d>(%s, in%d + i0);\n", t, a.array.c_str(), vec_, t, vec_,
+                          a.array.c_str(), input_slot_[a.value]);
+        }
+        for (const std::string& d : decl) loops += d;
+        loops += strfmt("#pragma unroll\n    for (int v = 0; v < %d; v++) {\n      const idx_t i = i0 + v;\n", vec_);
+        loops += body.code;
+        loops += "    }\n";
+        for (const std::string& d : after) loops += d;
+        loops += "  }\n";
+      } else {
+        loops += strfmt("  for (idx_t i = (idx_t)%s * %d + threadIdx.x; i < %lld; i += (idx_t)gridDim.x * %d) {\n", bx.c_str(),
+                        k->block, (long long)N_, k->block);
+        loops += body.code;
+        loops += "  }\n";
+      }
     }
+    N_ = n_max;
+    std::string code = top.code + loops;
     scopes_.pop_back();
     return code;
   }
@@ -1156,12 +1240,12 @@ bool codegen_fusible(const Plan& plan, const Instruction& ins) {
 }
 
 bool generate_fused_kernel(const Plan& plan, const std::vector<size_t>& nodes, const std::vector<uint32_t>& outputs,
-                           int sm_count, FusedKernel* out, std::string* why) {
+                           const std::vector<size_t>& scatters, int sm_count, FusedKernel* out, std::string* why) {
   for (int serial = 0; serial < 2; serial++) {
     // The one-thread-per-output reduction form is tried only for a lone reduction.
     if (serial == 1 && nodes.size() != 1) break;
     try {
-      Gen gen(plan, nodes, outputs, sm_count);
+      Gen gen(plan, nodes, outputs, scatters, sm_count);
       *out = gen.run(serial == 1);
       return true;
     } catch (const Fail& f) {

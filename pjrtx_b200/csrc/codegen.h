@@ -30,6 +30,7 @@ struct FusedKernel {
   std::string source;             // complete translation unit
   std::vector<uint32_t> inputs;   // external values, kernel pointer params in this order
   std::vector<uint32_t> outputs;  // stored values, pointer params after the inputs
+  std::vector<uint32_t> scatter_dst;  // results of in-place slice updates done by the kernel, pointer params after the outputs
   bool row = false;               // true: one CTA per row with reduce stages
   int64_t rows = 1, cols = 1;     // row kernel iteration space
   int64_t n = 0;                  // map kernel element count
@@ -44,10 +45,13 @@ struct FusedKernel {
 bool codegen_fusible(const Plan& plan, const Instruction& ins);
 
 // Generates the kernel for `nodes` (ascending instruction indices). `outputs`
-// are the values that must be stored. Returns false with a reason when the run
-// cannot be expressed as one kernel (the planner then shortens the run).
+// are the values that must be stored. `scatters` are dynamic_update_slice
+// instructions among the nodes whose operand storage is updated in place: the
+// kernel computes the update and stores it at the (clamped) start indices.
+// Returns false with a reason when the run cannot be expressed as one kernel
+// (the planner then shortens the run).
 bool generate_fused_kernel(const Plan& plan, const std::vector<size_t>& nodes,
-                           const std::vector<uint32_t>& outputs, int sm_count, FusedKernel* out,
-                           std::string* why);
+                           const std::vector<uint32_t>& outputs, const std::vector<size_t>& scatters, int sm_count,
+                           FusedKernel* out, std::string* why);
 
 }  // namespace pjrtx

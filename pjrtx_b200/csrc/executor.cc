@@ -735,11 +735,39 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     return stored;
   };
   auto skipped = [&](size_t i) { return plan.instructions[i].kind == Kind::constant || dead[i] != 0; };
+  // An in-place slice update can be the tail of a generated kernel: the kernel computes the update and stores it at
+  // the start indices (a KV-cache row written by the kernel that rotated it).
+  const bool fuse_dus = env_flag_local("PJRTX_B200_FUSE_SLICE_UPDATE", true);
+  auto scatter_at = [&](size_t i) {
+    return fuse_dus && plan.instructions[i].kind == Kind::dynamic_update_slice && dus_in_place[i] != 0 && !dead[i];
+  };
   auto fusible_at = [&](size_t i) {
     const Instruction& ins = plan.instructions[i];
-    return skipped(i) || codegen_fusible(plan, ins);
+    return skipped(i) || scatter_at(i) || codegen_fusible(plan, ins);
+  };
+  // The slice updates of [a, b) can run inside one kernel when nothing else in the range touches their storage
+  // (another thread of the same kernel could read a row before or after it is overwritten) and no two of them share it.
+  auto scatters_of = [&](size_t a, size_t b, std::vector<size_t>* out) {
+    out->clear();
+    for (size_t n = a; n < b; n++)
+      if (scatter_at(n)) out->push_back(n);
+    for (size_t q = 0; q < out->size(); q++) {
+      const Instruction& d = plan.instructions[(*out)[q]];
+      const uint32_t r = kp->root[d.outputs[0]];
+      for (size_t q2 = q + 1; q2 < out->size(); q2++)
+        if (kp->root[plan.instructions[(*out)[q2]].outputs[0]] == r) return false;
+      for (size_t n = a; n < b; n++) {
+        if (n == (*out)[q] || skipped(n)) continue;
+        for (uint32_t v : plan.instructions[n].inputs)
+          if (kp->root[v] == r) return false;
+      }
+      for (size_t k = 1; k < d.inputs.size(); k++)
+        if (kp->root[d.inputs[k]] == r) return false;
+    }
+    return true;
   };
 
+  const bool fusion_debug = env_flag_local("PJRTX_B200_FUSION_DEBUG", false);
   size_t i = 0;
   while (i < ni) {
     const Instruction& ins = plan.instructions[i];
@@ -758,7 +786,13 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
         for (; b > a; b--) {
           if (skipped(b - 1) && b - 1 > a) continue;  // never end a kernel on a skipped instruction
           std::vector<uint32_t> stored = stored_roots(a, b);
-          if (stored.empty()) {
+          std::vector<size_t> scatters;
+          if (!scatters_of(a, b, &scatters)) {
+            why = "a slice update's storage is used elsewhere in the run";
+            if (fusion_debug) fprintf(stderr, "pjrtx_b200 fusion: nodes [%zu, %zu) not one kernel: %s\n", a, b, why.c_str());
+            continue;
+          }
+          if (stored.empty() && scatters.empty()) {
             placed = true;  // pure aliases: nothing to launch
             break;
           }
@@ -767,17 +801,19 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
             if (!skipped(n)) nodes.push_back(n);
           Step st;
           st.type = Step::kFused;
-          if (generate_fused_kernel(plan, nodes, stored, sm_count, &st.fused, &why)) {
+          if (generate_fused_kernel(plan, nodes, stored, scatters, sm_count, &st.fused, &why)) {
             st.nodes = nodes;
             for (uint32_t v : st.fused.inputs) {
               uint32_t r = kp->root[v];
               if (std::find(st.inputs.begin(), st.inputs.end(), r) == st.inputs.end()) st.inputs.push_back(r);
             }
             st.outputs = stored;
+            for (uint32_t v : st.fused.scatter_dst) st.outputs.push_back(kp->root[v]);
             kp->steps.push_back(std::move(st));
             placed = true;
             break;
           }
+          if (fusion_debug) fprintf(stderr, "pjrtx_b200 fusion: nodes [%zu, %zu) not one kernel: %s\n", a, b, why.c_str());
         }
         if (!placed) {
           Issue is{(long)a, plan.instructions[a].outputs.empty() ? -1 : (long)plan.instructions[a].outputs[0],
@@ -1145,6 +1181,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         std::vector<void*> addr;
         for (uint32_t v : st.fused.inputs) addr.push_back(ptr.of(v));
         for (uint32_t v : st.fused.outputs) addr.push_back(ptr.of(v));
+        for (uint32_t v : st.fused.scatter_dst) addr.push_back(ptr.of(v));
         std::vector<void*> args(addr.size());
         for (size_t k = 0; k < addr.size(); k++) args[k] = &addr[k];
         cudaLaunchConfig_t cfg = {};

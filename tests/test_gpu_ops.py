@@ -234,6 +234,49 @@ def test_donated_slice_update_is_in_place(gpu_backend):
     assert np.array_equal(got[:, 15].view(np.uint16), u[:, 0].view(np.uint16))
 
 
+def test_slice_updates_ride_in_the_producing_kernel(gpu_backend):
+    """Two in-place updates of different donated buffers computed and stored by one generated kernel: one writes whole
+    trailing rows (vector stores), the other a window inside the innermost axis (scalar stores); start indices clamp."""
+    be = gpu_backend
+    b = PlanBuilder()
+    cache = b.parameter(P.BF16_CODE, [2, 16, 2, 8])
+    table = b.parameter(P.F32, [6, 40])
+    x = b.parameter(P.BF16_CODE, [2, 2, 8])
+    y = b.parameter(P.F32, [2, 16])
+    pos = b.parameter(P.S32, [])
+    col = b.parameter(P.S32, [])
+    zero = b.constant(np.int32(0))
+    upd = b.reshape(x * x + x, [2, 1, 2, 8])
+    out0 = b.dynamic_update_slice(cache, upd, [zero, pos, zero, zero])
+    win = b.unary("tanh", y) * y
+    out1 = b.dynamic_update_slice(table, win, [pos, col])
+    b.set_outputs([out0, out1], donate={0: 0, 1: 1})
+    exe = be.compile_executable(b, [0])
+    steps = be.describe_kernels(b)["steps"]
+    assert [s["type"] for s in steps] == ["fused"] and "dst1" in steps[0]["source"], [s["type"] for s in steps]
+    rng = np.random.default_rng(31)
+    c0 = rng.standard_normal((2, 16, 2, 8), dtype=np.float32).astype(P.np_dtype(P.BF16_CODE))
+    t0 = rng.standard_normal((6, 40), dtype=np.float32)
+    xs = rng.standard_normal((2, 2, 8), dtype=np.float32).astype(P.np_dtype(P.BF16_CODE))
+    ys = rng.standard_normal((2, 16), dtype=np.float32)
+    for p_, c_ in ((3, 7), (0, 0), (99, 99), (-4, -1), (15, 24)):
+        args = [c0, t0, xs, ys, np.array(p_, np.int32), np.array(c_, np.int32)]
+        want = run_oracle(b, args)
+        outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
+        got0, got1 = outs[0].to_numpy(), outs[1].to_numpy()
+        assert_close(got0, want[0], 2e-2, what=f"cache pos={p_}")
+        assert_close(got1, want[1], 1e-5, what=f"table pos={p_} col={c_}")
+        # everything outside the windows is untouched, bit for bit
+        r = min(max(p_, 0), 15)
+        mask = np.ones(c0.shape, bool)
+        mask[:, r] = False
+        assert np.array_equal(got0.view(np.uint16)[mask], c0.view(np.uint16)[mask])
+        r1, c1 = min(max(p_, 0), 4), min(max(c_, 0), 24)
+        mask1 = np.ones(t0.shape, bool)
+        mask1[r1:r1 + 2, c1:c1 + 16] = False
+        assert np.array_equal(got1[mask1], t0[mask1])
+
+
 def test_buffer_round_trip_and_errors(gpu_backend):
     be = gpu_backend
     for dt in (np.float32, np.int32, np.uint8, np.int8, np.uint16, np.uint32, np.uint64, np.int64, np.float16, np.bool_):
