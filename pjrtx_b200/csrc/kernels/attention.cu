@@ -8,10 +8,12 @@
 //
 // The cache is the only large operand (2 * (limit+1) * kv_heads * head_dim elements per sequence), so the kernel is
 // HBM-bound and organised around reading each K/V row exactly once with 16-byte loads: all `rep` query heads that
-// share a KV head are processed by the same CTA; a group of head_dim*esize/16 lanes owns one key row at a time, keeps
-// its slice of every query head and of every output accumulator in registers and needs only log2(group) shuffles per
-// key for the score. The key range is split across CTAs (grid.x) to fill the GPU at batch 1; partial (max, sum, out)
-// triples go to an f32 workspace and the CTA that arrives last merges them in split order (deterministic).
+// share a KV head are processed by the same CTA; a group of head_dim*esize/16 lanes owns a key row, keeps its slice
+// of every query head and of every output accumulator in registers and needs only log2(group) shuffles per key for
+// the score. At batch 1 the kernel is bound by latency, not bytes, so the work per CTA is short and flat: a chunk of
+// keys is loaded at once, one block-wide maximum per chunk replaces per-key rescaling, and partial sums of different
+// threads are simply added. The key range is split across CTAs (grid.x); partial (max, sum, out) triples go to an f32
+// workspace and the CTA that arrives last merges them in split order (deterministic).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -68,7 +70,6 @@ __device__ __forceinline__ long long load_scalar(const void* p, int dtype) {
 }
 
 constexpr int kWarps = 8;
-constexpr int kKeysPerStep = 4;  // keys a lane group handles per loop iteration (loads issued together)
 
 struct DecodeArgs {
   long long batch, heads, kv_heads, kv_len;
@@ -82,40 +83,41 @@ struct DecodeArgs {
   unsigned* counters;  // [batch * kv_heads]
 };
 
-// Merge (m2, l2, o2) into (m1, l1, o1); -inf maxima stand for "no keys seen".
-template <int N>
-__device__ __forceinline__ void merge_state(float& m1, float& l1, float* o1, float m2, float l2, const float* o2) {
-  const float m = fmaxf(m1, m2);
-  const float a = m1 == -INFINITY ? 0.f : __expf(m1 - m);
-  const float b = m2 == -INFINITY ? 0.f : __expf(m2 - m);
-  l1 = l1 * a + l2 * b;
-#pragma unroll
-  for (int i = 0; i < N; i++) o1[i] = o1[i] * a + o2[i] * b;
-  m1 = m;
-}
-
-template <typename T, int REP, int HD>
+// One CTA = one (sequence, KV head, key split). The split is walked in chunks of GROUPS * KPG keys; per chunk every
+// lane group (HD * esize / 16 lanes, one 16-byte slice of a row per lane) takes KPG keys:
+//   1. all K and V rows of the chunk are requested at once (2 * KPG 16-byte loads in flight per lane),
+//   2. scores = q . k for the `REP` query heads that share the KV head (log2(lanes per group) shuffles per score),
+//   3. one block-wide maximum per head (shuffles + one shared-memory round), so that
+//   4. p = exp(score - max) needs no per-key rescaling and the per-thread (sum, out) accumulators of different
+//      threads are plain partial sums; they are rescaled once per chunk when the running maximum moves.
+// After the last chunk the partial sums are added across the CTA, and (max, sum, out) goes to the workspace; the CTA
+// that arrives last for the (sequence, KV head) merges the splits in split order.
+template <typename T, int REP, int HD, int KPG>
 __global__ void __launch_bounds__(kWarps * 32)
 attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                    const void* __restrict__ token, T* __restrict__ out) {
   PJRTX_PDL_PROLOGUE();
   constexpr int V = Elem<T>::V;
-  constexpr int LPK = HD / V;        // lanes per key row
-  constexpr int KPW = 32 / LPK;      // key rows per warp per step
+  constexpr int LPK = HD / V;                  // lanes per key row
+  constexpr int GPW = 32 / LPK;                // lane groups per warp
+  constexpr int GROUPS = kWarps * GPW;         // lane groups per CTA
+  constexpr int CHUNK = GROUPS * KPG;          // keys per chunk
   static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "head_dim must give a power-of-two lane group");
-  __shared__ float sm_m[kWarps][REP], sm_l[kWarps][REP];
+  __shared__ float sm_max[2][kWarps][REP];     // double-buffered: one barrier per chunk
+  __shared__ float sm_l[kWarps][REP];
   __shared__ float sm_o[kWarps][REP][HD];
   __shared__ int is_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane / LPK, gl = lane % LPK;  // which key of the step, which slice of the row
+  const int sub = lane / LPK, gl = lane % LPK;  // lane group within the warp, slice of the row
+  const int group = warp * GPW + sub;
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   long long limit = load_scalar(token, a.token_dtype);  // keys 0..limit are visible
   if (limit >= a.kv_len) limit = a.kv_len - 1;
   const long long count = limit + 1;
-  const long long chunk = (count + a.splits - 1) / a.splits;
-  const long long j_begin = (long long)split * chunk;
-  const long long j_end = min(j_begin + chunk, count);
+  const long long per_split = (count + a.splits - 1) / a.splits;
+  const long long j_begin = (long long)split * per_split;
+  const long long j_end = min(j_begin + per_split, count);
 
   // Query slices of the `rep` heads that share this KV head.
   float qf[REP][V];
@@ -125,10 +127,10 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(qp));
     Elem<T>::unpack(raw, qf[r]);
   }
-  float m[REP], l[REP], o[REP][V];
+  float m_run[REP], l[REP], o[REP][V];
 #pragma unroll
   for (int r = 0; r < REP; r++) {
-    m[r] = -INFINITY;
+    m_run[r] = -INFINITY;
     l[r] = 0.f;
 #pragma unroll
     for (int i = 0; i < V; i++) o[r][i] = 0.f;
@@ -136,23 +138,24 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
   const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
   const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
 
-  // Each lane group walks keys j_begin + warp*KPW + sub + t*(kWarps*KPW). The loop bound is the same for every
-  // lane of the warp (the shuffles below need all 32 lanes); keys past the end are masked per lane.
-  constexpr int STRIDE = kWarps * KPW;
-  for (long long base = j_begin + warp * KPW; base < j_end; base += (long long)STRIDE * kKeysPerStep) {
-    uint4 kr[kKeysPerStep], vr[kKeysPerStep];
-    bool ok[kKeysPerStep];
+  int parity = 0;
+  for (long long c0 = j_begin; c0 < j_end; c0 += CHUNK, parity ^= 1) {  // same trip count for every thread of the CTA
+    uint4 kr[KPG], vr[KPG];
+    bool ok[KPG];
 #pragma unroll
-    for (int u = 0; u < kKeysPerStep; u++) {
-      const long long j = base + sub + (long long)u * STRIDE;
+    for (int u = 0; u < KPG; u++) {
+      const long long j = c0 + group + (long long)u * GROUPS;  // consecutive groups read consecutive rows
       ok[u] = j < j_end;
       const long long jj = ok[u] ? j : j_begin;  // a valid row; its contribution is masked below
       kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + jj * a.kv_row_stride));
       vr[u] = __ldg(reinterpret_cast<const uint4*>(vb + jj * a.kv_row_stride));
     }
-    float s[kKeysPerStep][REP];
+    float s[KPG][REP];
+    float mx[REP];
 #pragma unroll
-    for (int u = 0; u < kKeysPerStep; u++) {
+    for (int r = 0; r < REP; r++) mx[r] = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < KPG; u++) {
       float kf[V];
       Elem<T>::unpack(kr[u], kf);
 #pragma unroll
@@ -164,122 +167,152 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
         for (int off = LPK >> 1; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
         if (a.round_scores) d = Elem<T>::round(d);
         s[u][r] = ok[u] ? d * a.scale : -INFINITY;
+        mx[r] = fmaxf(mx[r], s[u][r]);
+      }
+    }
+    // Block-wide maximum per head.
+#pragma unroll
+    for (int r = 0; r < REP; r++) {
+#pragma unroll
+      for (int off = LPK; off < 32; off <<= 1) mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], off));
+      if (lane == 0) sm_max[parity][warp][r] = mx[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < REP; r++) {
+      float m_new = m_run[r];
+#pragma unroll
+      for (int w = 0; w < kWarps; w++) m_new = fmaxf(m_new, sm_max[parity][w][r]);
+      if (m_new != m_run[r]) {  // uniform over the CTA
+        const float corr = m_run[r] == -INFINITY ? 0.f : __expf(m_run[r] - m_new);
+        l[r] *= corr;
+#pragma unroll
+        for (int i = 0; i < V; i++) o[r][i] *= corr;
+        m_run[r] = m_new;
       }
     }
 #pragma unroll
-    for (int r = 0; r < REP; r++) {
-      float mx = m[r];
-#pragma unroll
-      for (int u = 0; u < kKeysPerStep; u++) mx = fmaxf(mx, s[u][r]);
-      if (mx == -INFINITY) continue;
-      const float corr = m[r] == -INFINITY ? 0.f : __expf(m[r] - mx);
-      l[r] *= corr;
-#pragma unroll
-      for (int i = 0; i < V; i++) o[r][i] *= corr;
-      m[r] = mx;
-    }
-#pragma unroll
-    for (int u = 0; u < kKeysPerStep; u++) {
+    for (int u = 0; u < KPG; u++) {
       float vf[V];
       Elem<T>::unpack(vr[u], vf);
 #pragma unroll
       for (int r = 0; r < REP; r++) {
-        const float p = s[u][r] == -INFINITY ? 0.f : __expf(s[u][r] - m[r]);
+        const float p = s[u][r] == -INFINITY ? 0.f : __expf(s[u][r] - m_run[r]);
         l[r] += p;
 #pragma unroll
         for (int i = 0; i < V; i++) o[r][i] = fmaf(p, vf[i], o[r][i]);
       }
     }
   }
-  // Merge the KPW lane groups of the warp.
+  // Sum the partial (l, o) of the lane groups: inside the warp with shuffles, across warps through shared memory.
 #pragma unroll
-  for (int off = LPK; off < 32; off <<= 1) {
+  for (int r = 0; r < REP; r++) {
 #pragma unroll
-    for (int r = 0; r < REP; r++) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m[r], off);
-      const float l2 = __shfl_xor_sync(0xffffffffu, l[r], off);
-      float o2[V];
+    for (int off = LPK; off < 32; off <<= 1) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], off);
 #pragma unroll
-      for (int i = 0; i < V; i++) o2[i] = __shfl_xor_sync(0xffffffffu, o[r][i], off);
-      merge_state<V>(m[r], l[r], o[r], m2, l2, o2);
+      for (int i = 0; i < V; i++) o[r][i] += __shfl_xor_sync(0xffffffffu, o[r][i], off);
     }
-  }
-  if (sub == 0) {
-#pragma unroll
-    for (int r = 0; r < REP; r++) {
-      if (gl == 0) {
-        sm_m[warp][r] = m[r];
-        sm_l[warp][r] = l[r];
-      }
+    if (sub == 0) {
+      if (gl == 0) sm_l[warp][r] = l[r];
 #pragma unroll
       for (int i = 0; i < V; i++) sm_o[warp][r][gl * V + i] = o[r][i];
     }
   }
   __syncthreads();
-  // Merge the warps (fixed order) and publish this split's partial.
   const long long tile = (long long)b * a.kv_heads + g;
   float* ws = a.workspace + (tile * a.splits + split) * (long long)REP * (HD + 2);
   for (int idx = threadIdx.x; idx < REP * HD; idx += kWarps * 32) {
     const int r = idx / HD, d = idx % HD;
-    float mm = sm_m[0][r], ll = sm_l[0][r], oo = sm_o[0][r][d];
+    float oo = 0.f, ll = 0.f;
 #pragma unroll
-    for (int w = 1; w < kWarps; w++) {
-      float o2 = sm_o[w][r][d];
-      merge_state<1>(mm, ll, &oo, sm_m[w][r], sm_l[w][r], &o2);
+    for (int w = 0; w < kWarps; w++) {
+      oo += sm_o[w][r][d];
+      ll += sm_l[w][r];
+    }
+    if (a.splits == 1) {  // nothing to merge: this CTA saw every key
+      out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(ll > 0.f ? oo / ll : 0.f);
+      continue;
     }
     ws[r * (HD + 2) + d] = oo;
     if (d == 0) {
-      ws[r * (HD + 2) + HD] = mm;
+      ws[r * (HD + 2) + HD] = m_run[r];
       ws[r * (HD + 2) + HD + 1] = ll;
     }
   }
+  if (a.splits == 1) return;
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) is_last = atomicAdd(&a.counters[tile], 1u) == (unsigned)a.splits - 1;
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // Two passes over the splits with independent loads (issued in batches) instead of one dependent chain: first the
-  // overall maximum, then the weighted sums in split order.
+  // Merge of the splits in two rounds of loads: (max, sum) of every split and head into shared memory, then all the
+  // `out` values a thread needs at once; the weights exp(max_split - max) are applied in split order.
   const float* base = a.workspace + tile * a.splits * (long long)REP * (HD + 2);
   const long long split_stride = (long long)REP * (HD + 2);
-  for (int idx = threadIdx.x; idx < REP * HD; idx += kWarps * 32) {
-    const int r = idx / HD, d = idx % HD;
-    const float* p = base + r * (HD + 2);
+  float* sm_ml = &sm_o[0][0][0];  // the partial sums are consumed: reuse as [splits][REP][2] (splits <= 64)
+  for (int idx = threadIdx.x; idx < a.splits * REP * 2; idx += kWarps * 32) {
+    const int sp = idx / (REP * 2), r = (idx / 2) % REP, which = idx & 1;
+    sm_ml[idx] = __ldcg(base + sp * split_stride + r * (HD + 2) + HD + which);
+  }
+  __syncthreads();
+  constexpr int PER_THREAD = (REP * HD + kWarps * 32 - 1) / (kWarps * 32);
+  constexpr int BATCH = 16;
+  float acc[PER_THREAD], lsum[PER_THREAD], mmax[PER_THREAD];
+#pragma unroll
+  for (int e = 0; e < PER_THREAD; e++) {
+    const int idx = threadIdx.x + e * kWarps * 32;
+    const int r = idx < REP * HD ? idx / HD : 0;
     float mm = -INFINITY;
-    for (int sp = 0; sp < a.splits; sp += 8) {
-      float mv[8];
+    for (int sp = 0; sp < a.splits; sp++) mm = fmaxf(mm, sm_ml[(sp * REP + r) * 2]);
+    mmax[e] = mm;
+    acc[e] = 0.f;
+    lsum[e] = 0.f;
+  }
+  for (int sp0 = 0; sp0 < a.splits; sp0 += BATCH) {
+    float ov[PER_THREAD][BATCH];
 #pragma unroll
-      for (int e = 0; e < 8; e++) mv[e] = sp + e < a.splits ? __ldcg(p + (sp + e) * split_stride + HD) : -INFINITY;
+    for (int e = 0; e < PER_THREAD; e++) {
+      const int idx = threadIdx.x + e * kWarps * 32;
+      const int r = idx < REP * HD ? idx / HD : 0, d = idx < REP * HD ? idx % HD : 0;
 #pragma unroll
-      for (int e = 0; e < 8; e++) mm = fmaxf(mm, mv[e]);
+      for (int u = 0; u < BATCH; u++)
+        ov[e][u] = sp0 + u < a.splits ? __ldcg(base + (sp0 + u) * split_stride + r * (HD + 2) + d) : 0.f;
     }
-    float ll = 0.f, oo = 0.f;
-    for (int sp = 0; sp < a.splits; sp += 4) {
-      float mv[4], lv[4], ov[4];
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const bool in = sp + e < a.splits;
-        mv[e] = in ? __ldcg(p + (sp + e) * split_stride + HD) : -INFINITY;
-        lv[e] = in ? __ldcg(p + (sp + e) * split_stride + HD + 1) : 0.f;
-        ov[e] = in ? __ldcg(p + (sp + e) * split_stride + d) : 0.f;
-      }
+    for (int e = 0; e < PER_THREAD; e++) {
+      const int idx = threadIdx.x + e * kWarps * 32;
+      const int r = idx < REP * HD ? idx / HD : 0;
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const float w = mv[e] == -INFINITY ? 0.f : __expf(mv[e] - mm);
-        ll = fmaf(lv[e], w, ll);
-        oo = fmaf(ov[e], w, oo);
+      for (int u = 0; u < BATCH; u++) {
+        if (sp0 + u < a.splits) {
+          const float ms = sm_ml[((sp0 + u) * REP + r) * 2];
+          const float w = ms == -INFINITY ? 0.f : __expf(ms - mmax[e]);
+          lsum[e] = fmaf(sm_ml[((sp0 + u) * REP + r) * 2 + 1], w, lsum[e]);
+          acc[e] = fmaf(ov[e][u], w, acc[e]);
+        }
       }
     }
-    out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(ll > 0.f ? oo / ll : 0.f);
+  }
+#pragma unroll
+  for (int e = 0; e < PER_THREAD; e++) {
+    const int idx = threadIdx.x + e * kWarps * 32;
+    if (idx < REP * HD) {
+      const int r = idx / HD, d = idx % HD;
+      out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(lsum[e] > 0.f ? acc[e] / lsum[e] : 0.f);
+    }
   }
   if (threadIdx.x == 0) a.counters[tile] = 0;
 }
 
+// Keys per lane group and chunk: eight while the scores of all heads still fit in registers, four beyond.
+template <int REP> struct KeysPerGroup { static constexpr int value = REP <= 4 ? 8 : 4; };
+
 template <typename T, int REP, int HD>
 int launch_decode(const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out, bool pdl,
                   cudaStream_t stream) {
-  return launch_kernel(attn_decode_kernel<T, REP, HD>, grid, dim3(kWarps * 32), 0, stream, pdl, a, (const T*)q, (const T*)k,
+  return launch_kernel(attn_decode_kernel<T, REP, HD, KeysPerGroup<REP>::value>, grid, dim3(kWarps * 32), 0, stream, pdl, a, (const T*)q, (const T*)k,
                        (const T*)v, token, (T*)out) == cudaSuccess
              ? 1
              : 0;
@@ -313,11 +346,14 @@ bool attn_decode_supported(const AttnDecodeShape& s) {
 AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   AttnDecodePlan p;
   const long long tiles = s.batch * s.kv_heads;
-  // About one CTA per SM; every split should still cover a few hundred keys' worth of rows.
-  long long want = ((long long)sm_count + tiles - 1) / tiles;
-  long long max_splits = std::max<long long>(1, s.kv_len / 64);
-  p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
   const long long rep = s.heads / s.kv_heads;
+  // Keys one CTA handles per chunk (see the kernel): no split should be shorter than that.
+  const long long lanes_per_key = s.head_dim * (long long)dtype_size(s.dtype) / 16;
+  const long long chunk = kWarps * (32 / lanes_per_key) * (rep <= 4 ? 8 : 4);
+  // About four CTAs per SM in total, so that the tail of the last wave is short next to the whole.
+  long long want = (4ll * sm_count + tiles - 1) / tiles;
+  long long max_splits = std::max<long long>(1, s.kv_len / chunk);
+  p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
   p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
   p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
   return p;
