@@ -1079,8 +1079,8 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
     } else if (st.type == Step::kSliceUpdate) {
       s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");
     } else if (st.type == Step::kAttnDecode) {
-      s += strfmt(",\"splits\":%d,\"batch\":%lld,\"heads\":%lld,\"kv_heads\":%lld,\"kv_len\":%lld,\"head_dim\":%lld",
-                  st.attn_plan.splits, st.attn.batch, st.attn.heads, st.attn.kv_heads, st.attn.kv_len, st.attn.head_dim);
+      s += strfmt(",\"mma\":%d,\"splits\":%d,\"batch\":%lld,\"heads\":%lld,\"kv_heads\":%lld,\"kv_len\":%lld,\"head_dim\":%lld",
+                  st.attn_plan.mma, st.attn_plan.splits, st.attn.batch, st.attn.heads, st.attn.kv_heads, st.attn.kv_len, st.attn.head_dim);
     }
     s += "}";
   }

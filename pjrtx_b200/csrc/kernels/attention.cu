@@ -17,6 +17,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "../common.h"
 #include "kernels.h"
 
@@ -82,6 +85,77 @@ struct DecodeArgs {
   float* workspace;   // [batch * kv_heads][splits][REP][HD + 2]
   unsigned* counters;  // [batch * kv_heads]
 };
+
+// Second half of a split: after every thread has written its part of this split's (max, sum, out) triple to the
+// workspace, the CTA that arrives last for the (sequence, KV head) merges all splits in split order and writes `out`.
+// `scratch` is shared memory for 64 * REP * 2 floats that nothing else uses any more.
+template <typename T, int REP, int HD, int THREADS>
+__device__ __forceinline__ void merge_splits(const DecodeArgs& a, long long tile, int b, int g, float* scratch, int* is_last,
+                                             T* __restrict__ out) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) *is_last = atomicAdd(&a.counters[tile], 1u) == (unsigned)a.splits - 1;
+  __syncthreads();
+  if (!*is_last) return;
+  __threadfence();
+  // Merge of the splits in two rounds of loads: (max, sum) of every split and head into shared memory, then all the
+  // `out` values a thread needs at once; the weights exp(max_split - max) are applied in split order.
+  const float* base = a.workspace + tile * a.splits * (long long)REP * (HD + 2);
+  const long long split_stride = (long long)REP * (HD + 2);
+  float* sm_ml = scratch;  // [splits][REP][2], splits <= 64
+  for (int idx = threadIdx.x; idx < a.splits * REP * 2; idx += THREADS) {
+    const int sp = idx / (REP * 2), r = (idx / 2) % REP, which = idx & 1;
+    sm_ml[idx] = __ldcg(base + sp * split_stride + r * (HD + 2) + HD + which);
+  }
+  __syncthreads();
+  constexpr int PER_THREAD = (REP * HD + THREADS - 1) / (THREADS);
+  constexpr int BATCH = 16;
+  float acc[PER_THREAD], lsum[PER_THREAD], mmax[PER_THREAD];
+#pragma unroll
+  for (int e = 0; e < PER_THREAD; e++) {
+    const int idx = threadIdx.x + e * THREADS;
+    const int r = idx < REP * HD ? idx / HD : 0;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < a.splits; sp++) mm = fmaxf(mm, sm_ml[(sp * REP + r) * 2]);
+    mmax[e] = mm;
+    acc[e] = 0.f;
+    lsum[e] = 0.f;
+  }
+  for (int sp0 = 0; sp0 < a.splits; sp0 += BATCH) {
+    float ov[PER_THREAD][BATCH];
+#pragma unroll
+    for (int e = 0; e < PER_THREAD; e++) {
+      const int idx = threadIdx.x + e * THREADS;
+      const int r = idx < REP * HD ? idx / HD : 0, d = idx < REP * HD ? idx % HD : 0;
+#pragma unroll
+      for (int u = 0; u < BATCH; u++)
+        ov[e][u] = sp0 + u < a.splits ? __ldcg(base + (sp0 + u) * split_stride + r * (HD + 2) + d) : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < PER_THREAD; e++) {
+      const int idx = threadIdx.x + e * THREADS;
+      const int r = idx < REP * HD ? idx / HD : 0;
+#pragma unroll
+      for (int u = 0; u < BATCH; u++) {
+        if (sp0 + u < a.splits) {
+          const float ms = sm_ml[((sp0 + u) * REP + r) * 2];
+          const float w = ms == -INFINITY ? 0.f : __expf(ms - mmax[e]);
+          lsum[e] = fmaf(sm_ml[((sp0 + u) * REP + r) * 2 + 1], w, lsum[e]);
+          acc[e] = fmaf(ov[e][u], w, acc[e]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < PER_THREAD; e++) {
+    const int idx = threadIdx.x + e * THREADS;
+    if (idx < REP * HD) {
+      const int r = idx / HD, d = idx % HD;
+      out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(lsum[e] > 0.f ? acc[e] / lsum[e] : 0.f);
+    }
+  }
+  if (threadIdx.x == 0) a.counters[tile] = 0;
+}
 
 // One CTA = one (sequence, KV head, key split). The split is walked in chunks of GROUPS * KPG keys; per chunk every
 // lane group (HD * esize / 16 lanes, one 16-byte slice of a row per lane) takes KPG keys:
@@ -241,69 +315,303 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
     }
   }
   if (a.splits == 1) return;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) is_last = atomicAdd(&a.counters[tile], 1u) == (unsigned)a.splits - 1;
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  // Merge of the splits in two rounds of loads: (max, sum) of every split and head into shared memory, then all the
-  // `out` values a thread needs at once; the weights exp(max_split - max) are applied in split order.
-  const float* base = a.workspace + tile * a.splits * (long long)REP * (HD + 2);
-  const long long split_stride = (long long)REP * (HD + 2);
-  float* sm_ml = &sm_o[0][0][0];  // the partial sums are consumed: reuse as [splits][REP][2] (splits <= 64)
-  for (int idx = threadIdx.x; idx < a.splits * REP * 2; idx += kWarps * 32) {
-    const int sp = idx / (REP * 2), r = (idx / 2) % REP, which = idx & 1;
-    sm_ml[idx] = __ldcg(base + sp * split_stride + r * (HD + 2) + HD + which);
+  merge_splits<T, REP, HD, kWarps * 32>(a, tile, b, g, &sm_o[0][0][0], &is_last, out);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core variant for 16-bit caches with many query heads per KV head or many sequences: with eight heads per KV
+// head the CUDA cores need ~4000 lane-instructions per K/V row pair and become the limit long before HBM does, while
+// the same work is 32 warp-level MMAs per 16 keys.
+//
+// One CTA (4 warps) = one (sequence, KV head, key split). K and V rows stream through a ring of shared-memory stages
+// of 64 keys (cp.async, 16 bytes per request, rows XOR-swizzled in 16-byte units so that ldmatrix reads are
+// conflict-free); rows past the end of the split are zero-filled. Each warp owns 16 keys of a stage:
+//   S[16 x 16 keys] = Q[16 x HD] . K^T      mma.m16n8k16, Q fragments held in registers (rows >= REP are zero),
+//                                           K fragments by ldmatrix
+//   online softmax on the accumulator fragments (row statistics are shared by the four lanes of a quad)
+//   O[16 x HD]     += P[16 x 16 keys] . V   the S accumulators, rounded to the element type, are the A fragments;
+//                                           V fragments by ldmatrix.trans
+// After the last stage the four warps' (max, sum, out) are merged through shared memory and the split is published
+// like in the CUDA-core kernel.
+constexpr int kMmaWarps = 4;
+constexpr int kMmaStageKeys = 16 * kMmaWarps;
+constexpr int kMmaStages = 3;
+
+template <typename T> struct MmaOps;
+template <> struct MmaOps<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
-  __syncthreads();
-  constexpr int PER_THREAD = (REP * HD + kWarps * 32 - 1) / (kWarps * 32);
-  constexpr int BATCH = 16;
-  float acc[PER_THREAD], lsum[PER_THREAD], mmax[PER_THREAD];
-#pragma unroll
-  for (int e = 0; e < PER_THREAD; e++) {
-    const int idx = threadIdx.x + e * kWarps * 32;
-    const int r = idx < REP * HD ? idx / HD : 0;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < a.splits; sp++) mm = fmaxf(mm, sm_ml[(sp * REP + r) * 2]);
-    mmax[e] = mm;
-    acc[e] = 0.f;
-    lsum[e] = 0.f;
+  static __device__ __forceinline__ unsigned pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
   }
-  for (int sp0 = 0; sp0 < a.splits; sp0 += BATCH) {
-    float ov[PER_THREAD][BATCH];
-#pragma unroll
-    for (int e = 0; e < PER_THREAD; e++) {
-      const int idx = threadIdx.x + e * kWarps * 32;
-      const int r = idx < REP * HD ? idx / HD : 0, d = idx < REP * HD ? idx % HD : 0;
-#pragma unroll
-      for (int u = 0; u < BATCH; u++)
-        ov[e][u] = sp0 + u < a.splits ? __ldcg(base + (sp0 + u) * split_stride + r * (HD + 2) + d) : 0.f;
+};
+template <> struct MmaOps<__half> {
+  static __device__ __forceinline__ void mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ unsigned pack(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+  }
+};
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned* r, unsigned smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned* r, unsigned smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+// 16-byte asynchronous copy; `bytes` = 0 writes zeros without reading the source.
+__device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
+}
+
+template <typename T, int REP, int HD>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                       const void* __restrict__ token, T* __restrict__ out) {
+  static_assert(sizeof(T) == 2 && (HD == 64 || HD == 128) && REP <= 16, "16-bit elements, head_dim 64 or 128");
+  constexpr int THREADS = kMmaWarps * 32;
+  constexpr int CPR = HD / 8;                        // 16-byte chunks per row
+  constexpr int HALVES = HD / 64;                    // 128-byte column blocks per row
+  constexpr int TILE_BYTES = kMmaStageKeys * HD * 2;  // one of K or V for one stage
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  extern __shared__ __align__(1024) unsigned char smem_attn[];
+  __shared__ int is_last;
+  PJRTX_PDL_PROLOGUE();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  long long limit = load_scalar(token, a.token_dtype);  // keys 0..limit are visible
+  if (limit >= a.kv_len) limit = a.kv_len - 1;
+  const long long count = limit + 1;
+  const long long per_split = (count + a.splits - 1) / a.splits;
+  const long long j_begin = (long long)split * per_split;
+  const long long j_end = min(j_begin + per_split, count);
+  const int stages_total = j_end > j_begin ? (int)((j_end - j_begin + kMmaStageKeys - 1) / kMmaStageKeys) : 0;
+
+  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride;
+  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride;
+  const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_attn);
+
+  // Row `row` (0..63) of a stage tile, 16-byte chunk `c` of the row: column block c / 8 holds [64 rows][128 bytes],
+  // chunk position XORed with the row's low three bits.
+  auto tile_offset = [](int row, int c) { return (unsigned)((c >> 3) * (kMmaStageKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)); };
+  auto issue_stage = [&](int st) {
+    const unsigned dst = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
+    const long long j0 = j_begin + (long long)st * kMmaStageKeys;
+    for (int idx = threadIdx.x; idx < kMmaStageKeys * CPR; idx += THREADS) {
+      const int row = idx / CPR, c = idx % CPR;
+      const long long j = j0 + row;
+      const bool in = j < j_end;
+      const long long jj = in ? j : j_begin;
+      cp_async16(dst + tile_offset(row, c), kb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
+      cp_async16(dst + TILE_BYTES + tile_offset(row, c), vb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
     }
+  };
+  for (int st = 0; st < kMmaStages - 1; st++) {
+    if (st < stages_total) issue_stage(st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  // Q fragments: row r = lane / 4 (and r + 8), columns ks * 16 + (lane % 4) * 2 (+ 8).
+  unsigned qa[HD / 16][4];
+  {
+    const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+    const T* qrow0 = q + b * a.q_batch_stride + (g * REP + r0) * a.q_head_stride;
+    const T* qrow1 = q + b * a.q_batch_stride + (g * REP + r0 + 8) * a.q_head_stride;
 #pragma unroll
-    for (int e = 0; e < PER_THREAD; e++) {
-      const int idx = threadIdx.x + e * kWarps * 32;
-      const int r = idx < REP * HD ? idx / HD : 0;
+    for (int ks = 0; ks < HD / 16; ks++) {
+      qa[ks][0] = r0 < REP ? __ldg(reinterpret_cast<const unsigned*>(qrow0 + ks * 16 + c0)) : 0u;
+      qa[ks][1] = r0 + 8 < REP ? __ldg(reinterpret_cast<const unsigned*>(qrow1 + ks * 16 + c0)) : 0u;
+      qa[ks][2] = r0 < REP ? __ldg(reinterpret_cast<const unsigned*>(qrow0 + ks * 16 + c0 + 8)) : 0u;
+      qa[ks][3] = r0 + 8 < REP ? __ldg(reinterpret_cast<const unsigned*>(qrow1 + ks * 16 + c0 + 8)) : 0u;
+    }
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};
+  float o[HD / 8][4];
 #pragma unroll
-      for (int u = 0; u < BATCH; u++) {
-        if (sp0 + u < a.splits) {
-          const float ms = sm_ml[((sp0 + u) * REP + r) * 2];
-          const float w = ms == -INFINITY ? 0.f : __expf(ms - mmax[e]);
-          lsum[e] = fmaf(sm_ml[((sp0 + u) * REP + r) * 2 + 1], w, lsum[e]);
-          acc[e] = fmaf(ov[e][u], w, acc[e]);
+  for (int nt = 0; nt < HD / 8; nt++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
+
+  for (int st = 0; st < stages_total; st++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kMmaStages - 2) : "memory");
+    __syncthreads();  // stage st is complete for everyone, and everyone is done with stage st - 1
+    if (st + kMmaStages - 1 < stages_total) issue_stage(st + kMmaStages - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    const unsigned ktile = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
+    const unsigned vtile = ktile + TILE_BYTES;
+    const int row0 = warp * 16;  // this warp's keys inside the stage
+    // S = Q . K^T for 16 keys: two accumulator tiles of 8 keys.
+    float sc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) sc[nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) {
+      // Matrices: (keys 0-7, hd 0-7), (keys 0-7, hd 8-15), (keys 8-15, hd 0-7), (keys 8-15, hd 8-15) of this k step.
+      unsigned bk[4];
+      const int key = row0 + ((lane >> 4) << 3) + (lane & 7);
+      const int chunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(bk, ktile + tile_offset(key, chunk));
+      MmaOps<T>::mma(sc[0], qa[ks], bk[0], bk[1]);
+      MmaOps<T>::mma(sc[1], qa[ks], bk[2], bk[3]);
+    }
+    // Scale, mask and online softmax. Accumulator element e of tile nt: row (lane / 4) + 8 * (e / 2),
+    // key row0 + nt * 8 + (lane % 4) * 2 + (e % 2).
+    const long long key_base = j_begin + (long long)st * kMmaStageKeys + row0 + (lane & 3) * 2;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float d = sc[nt][e];
+        if (a.round_scores) d = Elem<T>::round(d);
+        const bool ok = key_base + nt * 8 + (e & 1) < j_end;
+        d = ok ? d * a.scale : -INFINITY;
+        sc[nt][e] = d;
+        mx[e >> 1] = fmaxf(mx[e >> 1], d);
+      }
+    unsigned pa[4];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {  // row lane / 4 (h = 0) and row lane / 4 + 8 (h = 1)
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      const float corr = (m_run[h] == -INFINITY || m_new == m_run[h]) ? (m_run[h] == -INFINITY ? 0.f : 1.f) : __expf(m_run[h] - m_new);
+      if (corr != 1.f) {
+        l_part[h] *= corr;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; nt++) {
+          o[nt][2 * h] *= corr;
+          o[nt][2 * h + 1] *= corr;
+        }
+      }
+      m_run[h] = m_new;
+      float p[4];
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const float sv = sc[nt][2 * h + e];
+          p[nt * 2 + e] = sv == -INFINITY ? 0.f : __expf(sv - m_new);
+        }
+      // The probabilities enter the second contraction in the element type; the row sum uses the same rounded values.
+      pa[h] = MmaOps<T>::pack(p[0], p[1]);       // keys 0-7 block
+      pa[2 + h] = MmaOps<T>::pack(p[2], p[3]);   // keys 8-15 block
+      l_part[h] += Elem<T>::round(p[0]) + Elem<T>::round(p[1]) + Elem<T>::round(p[2]) + Elem<T>::round(p[3]);
+    }
+    // O += P . V: B fragments from V[key][hd] by transposing loads, two 8-column tiles per ldmatrix.
+#pragma unroll
+    for (int np = 0; np < HD / 16; np++) {
+      // Matrices: (keys 0-7, hd tile 2np), (keys 8-15, hd tile 2np), (keys 0-7, hd tile 2np+1), (keys 8-15, hd tile 2np+1).
+      unsigned bv[4];
+      const int key = row0 + (((lane >> 3) & 1) << 3) + (lane & 7);
+      const int chunk = np * 2 + (lane >> 4);
+      ldmatrix_x4_trans(bv, vtile + tile_offset(key, chunk));
+      MmaOps<T>::mma(o[2 * np], pa, bv[0], bv[1]);
+      MmaOps<T>::mma(o[2 * np + 1], pa, bv[2], bv[3]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // the stage memory is free: reuse it for the merge of the four warps
+
+  // Row sums over the quad, then per-warp (max, sum, out) to shared memory.
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    l_part[h] += __shfl_xor_sync(0xffffffffu, l_part[h], 1);
+    l_part[h] += __shfl_xor_sync(0xffffffffu, l_part[h], 2);
+  }
+  float* sm_m = reinterpret_cast<float*>(smem_attn);                 // [warps][16]
+  float* sm_l = sm_m + kMmaWarps * 16;                               // [warps][16]
+  float* sm_o = sm_l + kMmaWarps * 16;                               // [warps][REP][HD]
+  {
+    const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int r = r0 + 8 * h;
+      if (r < REP) {
+        if ((lane & 3) == 0) {
+          sm_m[warp * 16 + r] = m_run[h];
+          sm_l[warp * 16 + r] = l_part[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; nt++) {
+          sm_o[(warp * REP + r) * HD + nt * 8 + c0] = o[nt][2 * h];
+          sm_o[(warp * REP + r) * HD + nt * 8 + c0 + 1] = o[nt][2 * h + 1];
         }
       }
     }
   }
+  __syncthreads();
+  const long long tile = (long long)b * a.kv_heads + g;
+  float* ws = a.workspace + (tile * a.splits + split) * (long long)REP * (HD + 2);
+  for (int idx = threadIdx.x; idx < REP * HD; idx += THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
 #pragma unroll
-  for (int e = 0; e < PER_THREAD; e++) {
-    const int idx = threadIdx.x + e * kWarps * 32;
-    if (idx < REP * HD) {
-      const int r = idx / HD, d = idx % HD;
-      out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(lsum[e] > 0.f ? acc[e] / lsum[e] : 0.f);
+    for (int w = 0; w < kMmaWarps; w++) mm = fmaxf(mm, sm_m[w * 16 + r]);
+    float oo = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; w++) {
+      const float mw = sm_m[w * 16 + r];
+      const float wgt = mw == -INFINITY ? 0.f : __expf(mw - mm);
+      oo = fmaf(sm_o[(w * REP + r) * HD + d], wgt, oo);
+      ll = fmaf(sm_l[w * 16 + r], wgt, ll);
+    }
+    if (a.splits == 1) {
+      out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(ll > 0.f ? oo / ll : 0.f);
+      continue;
+    }
+    ws[r * (HD + 2) + d] = oo;
+    if (d == 0) {
+      ws[r * (HD + 2) + HD] = mm;
+      ws[r * (HD + 2) + HD + 1] = ll;
     }
   }
-  if (threadIdx.x == 0) a.counters[tile] = 0;
+  if (a.splits == 1) return;
+  __syncthreads();  // the merge scratch below overlaps sm_m / sm_l / sm_o
+  merge_splits<T, REP, HD, THREADS>(a, tile, b, g, reinterpret_cast<float*>(smem_attn), &is_last, out);
+}
+
+template <typename T, int REP, int HD>
+int launch_decode_mma(const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out,
+                      bool pdl, cudaStream_t stream) {
+  constexpr size_t stage_smem = (size_t)kMmaStages * 2 * kMmaStageKeys * HD * 2;
+  constexpr size_t merge_smem = (size_t)(2 * kMmaWarps * 16 + kMmaWarps * REP * HD) * sizeof(float);
+  constexpr size_t scratch_smem = (size_t)64 * REP * 2 * sizeof(float);
+  constexpr size_t smem = stage_smem > merge_smem ? (stage_smem > scratch_smem ? stage_smem : scratch_smem)
+                                                  : (merge_smem > scratch_smem ? merge_smem : scratch_smem);
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<T, REP, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    configured = true;
+  }
+  return launch_kernel(attn_decode_mma_kernel<T, REP, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q,
+                       (const T*)k, (const T*)v, token, (T*)out) == cudaSuccess
+             ? 1
+             : 0;
+}
+
+template <typename T>
+int dispatch_decode_mma(int rep, int hd, const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v,
+                        const void* token, void* out, bool pdl, cudaStream_t stream) {
+#define CASE(R, H) \
+  if (rep == R && hd == H) return launch_decode_mma<T, R, H>(a, grid, q, k, v, token, out, pdl, stream);
+  CASE(4, 128) CASE(8, 128) CASE(4, 64) CASE(8, 64)
+#undef CASE
+  return 0;
 }
 
 // Keys per lane group and chunk: eight while the scores of all heads still fit in registers, four beyond.
@@ -347,6 +655,22 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   AttnDecodePlan p;
   const long long tiles = s.batch * s.kv_heads;
   const long long rep = s.heads / s.kv_heads;
+  // Tensor-core kernel: 16-bit caches where the CUDA cores would be the limit (eight heads per KV head) or where the
+  // cache is large enough for throughput to matter more than the latency of one short CTA.
+  // PJRTX_B200_ATTENTION_MMA=0 / 1 forces the choice wherever the kernel applies.
+  const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8);
+  const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
+  const bool large = tiles * s.kv_len >= (long long)sm_count * 2048;
+  p.mma = mma_ok && (force && *force ? atoi(force) != 0 : (rep == 8 || large)) ? 1 : 0;
+  if (p.mma) {
+    // Two CTAs per SM are resident; aim for two waves of them, with splits no shorter than two stages of keys.
+    long long want = (4ll * sm_count + tiles - 1) / tiles;
+    long long max_splits = std::max<long long>(1, s.kv_len / (2 * kMmaStageKeys));
+    p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
+    p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
+    p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+    return p;
+  }
   // Keys one CTA handles per chunk (see the kernel): no split should be shorter than that.
   const long long lanes_per_key = s.head_dim * (long long)dtype_size(s.dtype) / 16;
   const long long chunk = kWarps * (32 / lanes_per_key) * (rep <= 4 ? 8 : 4);
@@ -379,6 +703,10 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
   a.counters = static_cast<unsigned*>(counters);
   dim3 grid((unsigned)plan.splits, (unsigned)s.kv_heads, (unsigned)s.batch);
   const int rep = (int)(s.heads / s.kv_heads);
+  if (plan.mma) {
+    if (s.dtype == kF16) return dispatch_decode_mma<__half>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
+    return dispatch_decode_mma<__nv_bfloat16>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
+  }
   if (s.dtype == kF32) {
     // f32 rows are twice as wide: only head_dim 64 and 128 with 16 / 32 lanes per key.
     return dispatch_decode<float>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);

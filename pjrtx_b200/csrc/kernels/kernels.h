@@ -117,6 +117,7 @@ struct AttnDecodeShape {
 };
 struct AttnDecodePlan {
   int splits = 1;
+  int mma = 0;  // 1: warp-level tensor-core kernel (16-bit caches), 0: CUDA-core kernel
   uint64_t workspace_bytes = 0, counter_bytes = 0;
 };
 bool attn_decode_supported(const AttnDecodeShape& s);
