@@ -27,6 +27,7 @@ from pjrtx_b200.programs import llama, random_init  # noqa: E402
 
 
 TRAFFIC_RATIO = 1.021  # (dram read + write) / algorithmic bytes, byte-weighted over the captured launches
+UMMA_TRAFFIC_RATIO = 1.02  # same ratio for the tensor-core kernel (profiles/umma_stream_kernel_llama8b_batch32.md)
 
 
 def measured_peaks():
@@ -204,7 +205,8 @@ def run_ours(args):
     device = local_rank
     be.enumerate_devices()
     if world == 1:
-        cfg, batch, filled, workload = llama.LLAMA3_8B, 1, 2048, "llama3-8b-shape bf16 decode batch 1, KV prefilled 2048"
+        cfg, batch, filled = llama.LLAMA3_8B, max(1, args.batch), 2048
+        workload = f"llama3-8b-shape bf16 decode batch {batch}, KV prefilled 2048"
     else:
         cfg, batch, filled = llama.LLAMA3_70B, 32, 4096
         workload = f"llama3-70b-shape bf16 decode batch 32, KV 4096, TP={world}"
@@ -314,6 +316,7 @@ def run_ours(args):
     acc /= reps
     esize = 2
     stream_bytes = stream_ms = 0.0
+    tensor_core = False
     for st, t in zip(desc, acc):
         label = st["type"] + (f"/path{st['path']}" if st["type"] == "dot" else ("/row" if st.get("row") else ""))
         per_type.setdefault(label, [0, 0.0])
@@ -322,6 +325,7 @@ def run_ours(args):
         if st["type"] == "dot" and st["path"] == 1 and st["b0"] * st["b1"] == 1:
             stream_bytes += st["k"] * st["n"] * esize + st["m"] * (st["k"] + st["n"]) * esize
             stream_ms += float(t)
+            tensor_core |= bool(st.get("umma"))
     peak, peak_kind = measured_peaks()
     step_ms = ms / args.steps
     kv_mid = filled + args.warmup + args.steps // 2
@@ -342,8 +346,11 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram read+write bytes per step over all launches of this kernel: algorithmic bytes x the ratio an
                      # ncu capture of one layer's launches gave (profiles/stream_tma_kernel_llama8b_layer.md)
-                     "traffic": stream_bytes * TRAFFIC_RATIO, "algorithmic_bytes": stream_bytes,
-                     "kernel": "tma::stream_tma_kernel (weight-streaming contraction)", "peak_kind": f"of {peak_kind}",
+                     "traffic": stream_bytes * (UMMA_TRAFFIC_RATIO if tensor_core else TRAFFIC_RATIO),
+                     "algorithmic_bytes": stream_bytes,
+                     "kernel": ("umma::umma_stream_kernel (tcgen05 weight-streaming contraction)" if tensor_core
+                                else "tma::stream_tma_kernel (weight-streaming contraction)"),
+                     "peak_kind": f"of {peak_kind}",
                      "launches_per_step": sum(1 for s in desc if s["type"] == "dot" and s["path"] == 1),
                      "whole_step": {"algorithmic_bytes": alg, "achieved": alg / (step_ms * 1e-3) / 1e9,
                                     "frac": alg / (step_ms * 1e-3) / 1e9 / peak, "frac_of_8tbs": alg / (step_ms * 1e-3) / 8e12}},
@@ -351,7 +358,7 @@ def run_ours(args):
         "kernel_time_ms_per_step": {k: {"launches": v[0], "ms": round(v[1], 4)} for k, v in sorted(per_type.items())},
         "compile_s": round(compile_s, 2), "setup_s": round(setup_s, 2),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and batch == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(llama.LLAMA3_8B, 1, filled, budget_layers=args.cpu_layers)
     if rank == 0:
         print(json.dumps(result))
@@ -429,6 +436,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="truncate the decoder (debugging only; changes the workload)")
     ap.add_argument("--cpu-layers", type=int, default=2, help="decoder layers in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="sequences decoded together on one GPU (1 = the headline workload; 16 and 32 are the batched-decode configs)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

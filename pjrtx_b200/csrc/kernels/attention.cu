@@ -660,7 +660,7 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   // PJRTX_B200_ATTENTION_MMA=0 / 1 forces the choice wherever the kernel applies.
   const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8);
   const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
-  const bool large = tiles * s.kv_len >= (long long)sm_count * 2048;
+  const bool large = tiles * s.kv_len >= (long long)sm_count * 256;  // measured: ahead from batch 4 at 2K keys, 8 KV heads
   p.mma = mma_ok && (force && *force ? atoi(force) != 0 : (rep == 8 || large)) ? 1 : 0;
   if (p.mma) {
     // Two CTAs per SM are resident; aim for two waves of them, with splits no shorter than two stages of keys.

@@ -16,8 +16,8 @@
 //   0  generic   : one thread per output element, any strides, any m.
 // 16-bit floats without batch axes whose operands a TMA tensor map can describe run on the tensor cores instead
 // (umma_gemm.cuh): rhs[K,N] as a variant of path 1 (so that q/k/v and gate/up still share one launch), rhs[N,K] as
-// path 4. PJRTX_B200_UMMA=0 turns that off; PJRTX_B200_UMMA_MIN_M (default 9) keeps the CUDA-core streaming kernels
-// below that m.
+// path 4. PJRTX_B200_UMMA=0 turns that off; PJRTX_B200_UMMA_MIN_M (default 3: measured on the
+// 8B decode shapes the CUDA-core kernel is ahead for one and two rows only) keeps the CUDA-core streaming kernels below that m.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -573,7 +573,7 @@ int env_int(const char* name, int fallback) {
 // multiples for every row stride; lhs must be k-contiguous.
 int umma_eligible(const DotShape& s) {
   static const int enabled = env_int("PJRTX_B200_UMMA", 1);
-  static const int min_m = env_int("PJRTX_B200_UMMA_MIN_M", 9);
+  static const int min_m = env_int("PJRTX_B200_UMMA_MIN_M", 3);
   if (!enabled || (s.dtype != kF16 && s.dtype != kBF16)) return 0;
   if (s.b0 * s.b1 != 1 || s.m < min_m || s.k < 1 || s.n < 1) return 0;
   if (s.lhs_k != 1 || (s.m > 1 && s.lhs_m % 8 != 0)) return 0;

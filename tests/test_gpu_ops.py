@@ -189,8 +189,8 @@ def test_tensor_core_dot_shapes_against_f64(gpu_backend, dtype):
         b.set_outputs([b.dot_general(pl, pr, [1], [0]), b.dot_general(pl, pr2, [1], [0]), b.dot_general(pl, prt, [1], [1])])
         exe = gpu_backend.compile_executable(b, [0])
         steps = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
-        # more than eight rows always take the tensor-core kernel; fewer keep the CUDA-core streaming kernels by default
-        assert steps and (m <= 8 or all(s["umma"] == 1 for s in steps)), steps
+        # three rows and more take the tensor-core kernel; one and two keep the CUDA-core streaming kernels by default
+        assert steps and (m <= 2 or all(s["umma"] == 1 for s in steps)), steps
         assert any(s["group"] == 2 for s in steps), steps  # the two rhs[K,N] contractions share a launch
         rnk = np.ascontiguousarray(rkn.T)
         got = run_backend(gpu_backend, b, [lhs, rkn, rkn2, rnk], exe=exe)
