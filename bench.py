@@ -221,6 +221,8 @@ def run_ours(args):
         uid = [be.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         be.comm_init(device, uid[0], rank, world)
+        if os.environ.get("PJRTX_B200_PEER_ALLREDUCE", "1") != "0":
+            be.enable_peer_all_reduce(device, rank, world, dist.all_gather_object)
     t0 = time.time()
     _progress("compiling")
     exe = be.compile_executable(builder, [device], partition=rank if world > 1 else None)

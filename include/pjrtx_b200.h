@@ -298,6 +298,14 @@ uint64_t pjrtx_b200_custom_call_registry_version(void);
 int pjrtx_b200_comm_unique_id(uint8_t out_id[128]);
 int pjrtx_b200_comm_init(int device_ordinal, const uint8_t id[128], int rank, int world_size);
 void pjrtx_b200_comm_destroy(int device_ordinal);
+/* Peer-memory all-reduce (no counterpart in the reference). Optional, after comm_init: every rank calls
+ * comm_peer_export (allocates this rank's region and returns its 64-byte CUDA IPC handle), the host ships all handles
+ * to all ranks in rank order, every rank calls comm_peer_import with the world_size x 64 bytes; from then on sums of up
+ * to world_size x 512 KiB inside executables run as one kernel per rank (reduce-scatter and all-gather through the
+ * peers' regions over NVLink) instead of a library collective. All ranks must have exported before any of them executes (the exchange of the handles is that
+ * barrier). Ranks are processes on one node, one GPU each, 2..8 of them. 1 on success, 0 with last_error set. */
+int pjrtx_b200_comm_peer_export(int device_ordinal, uint8_t out_handle[64]);
+int pjrtx_b200_comm_peer_import(int device_ordinal, const uint8_t *handles, int rank, int world_size);
 
 /* ---- contraction without allocation ---------------------------------------- */
 /* No counterpart in the reference. out[m, n] = lhs[m, k] . rhs[k, n] for dense row-major device pointers, 1 <= m <= 8,

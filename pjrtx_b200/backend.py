@@ -136,6 +136,8 @@ SYMBOLS = {
     "pjrtx_b200_comm_unique_id": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint8)]),
     "pjrtx_b200_comm_init": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint8), ctypes.c_int, ctypes.c_int]),
     "pjrtx_b200_comm_destroy": (None, [ctypes.c_int]),
+    "pjrtx_b200_comm_peer_export": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint8)]),
+    "pjrtx_b200_comm_peer_import": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint8), ctypes.c_int, ctypes.c_int]),
     "pjrtx_b200_dot_static_scratch": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _P, _P, _P, ctypes.c_int64, ctypes.c_int64,
                                                       ctypes.c_int64, _P]),
     "pjrtx_b200_compile_check": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint64]),
@@ -462,6 +464,27 @@ class Backend:
         buf = (ctypes.c_uint8 * 128)(*unique_id)
         if not self.lib.pjrtx_b200_comm_init(device, buf, rank, world):
             raise BackendError("CommandSubmissionFailed", self._err())
+
+    def comm_peer_export(self, device: int) -> bytes:
+        """Allocates this rank's peer region and returns its 64-byte IPC handle (ship it to every other rank)."""
+        buf = (ctypes.c_uint8 * 64)()
+        if not self.lib.pjrtx_b200_comm_peer_export(device, buf):
+            raise BackendError("CommandSubmissionFailed", self._err())
+        return bytes(buf)
+
+    def comm_peer_import(self, device: int, handles: Sequence[bytes], rank: int, world: int) -> None:
+        """Maps every rank's region (handles in rank order); small all-reduces then run over peer memory."""
+        flat = b"".join(handles)
+        buf = (ctypes.c_uint8 * len(flat))(*flat)
+        if not self.lib.pjrtx_b200_comm_peer_import(device, buf, rank, world):
+            raise BackendError("CommandSubmissionFailed", self._err())
+
+    def enable_peer_all_reduce(self, device: int, rank: int, world: int, all_gather_object) -> None:
+        """Export, exchange through `all_gather_object(list_out, obj)` (torch.distributed's signature), import."""
+        mine = self.comm_peer_export(device)
+        handles = [None] * world
+        all_gather_object(handles, mine)
+        self.comm_peer_import(device, handles, rank, world)
 
     def dot_static_scratch(self, dtype: int, lhs_ptr: int, rhs_ptr: int, out_ptr: int, m: int, k: int, n: int, device: int = 0,
                            stream: int = 0) -> None:

@@ -495,10 +495,21 @@ int pjrtx_b200_comm_init(int device_ordinal, const uint8_t id[128], int rank, in
   GUARD_INT(Device* d = get_device(device_ordinal); if (!d || !id) return 0; return comm_init(d, id, rank, world_size) ? 1 : 0;)
 }
 
+int pjrtx_b200_comm_peer_export(int device_ordinal, uint8_t out_handle[64]) {
+  GUARD_INT(Device* d = get_device(device_ordinal); if (!d || !out_handle) return 0; return comm_peer_export(d, out_handle) ? 1 : 0;)
+}
+
+int pjrtx_b200_comm_peer_import(int device_ordinal, const uint8_t* handles, int rank, int world_size) {
+  GUARD_INT(Device* d = get_device(device_ordinal); if (!d || !handles) return 0; return comm_peer_import(d, handles, rank, world_size) ? 1 : 0;)
+}
+
 void pjrtx_b200_comm_destroy(int device_ordinal) {
   try {
     Device* d = get_device(device_ordinal);
-    if (d) comm_destroy(d);
+    if (d) {
+      comm_peer_close(d);
+      comm_destroy(d);
+    }
   } catch (...) {
   }
 }

@@ -1,5 +1,7 @@
 #include "device.h"
 
+#include "kernels/kernels.h"
+
 #include <dlfcn.h>
 #include <nccl.h>
 #include <nvrtc.h>
@@ -402,7 +404,93 @@ bool comm_init(Device* dev, const uint8_t id_bytes[128], int rank, int world) {
   return true;
 }
 
-bool comm_all_reduce_sum(Device* dev, const void* src, void* dst, uint64_t count, int dtype) {
+namespace {
+constexpr uint64_t kPeerSlotBytes = 1ull << 20;  // one part in wire format: sums of up to world x 512 KiB
+bool peer_enabled() {
+  const char* v = getenv("PJRTX_B200_PEER_ALLREDUCE");
+  return !(v && *v == '0');
+}
+}  // namespace
+
+bool comm_peer_export(Device* dev, uint8_t handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaSetDevice(dev->ordinal);
+  if (!dev->peer_regions[0] || dev->peer_ready) {
+    // (re)create the local region; it is parked in slot 0 until the import knows this rank's number
+    comm_peer_close(dev);
+    void* region = nullptr;
+    const uint64_t bytes = peer_region_bytes(kPeerSlotBytes);
+    if (!check_cuda(cudaMalloc(&region, bytes), "cudaMalloc(peer region)")) return false;
+    if (!check_cuda(cudaMemset(region, 0, bytes), "cudaMemset(peer region)") ||
+        !check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) {
+      cudaFree(region);
+      return false;
+    }
+    dev->peer_regions[0] = region;
+    dev->peer_slot_bytes = kPeerSlotBytes;
+    dev->peer_world = 0;
+  }
+  cudaIpcMemHandle_t h;
+  if (!check_cuda(cudaIpcGetMemHandle(&h, dev->peer_regions[0]), "cudaIpcGetMemHandle")) return false;
+  memcpy(handle, &h, 64);
+  return true;
+}
+
+bool comm_peer_import(Device* dev, const uint8_t* handles, int rank, int world) {
+  if (world < 2 || world > 8 || rank < 0 || rank >= world) {
+    set_last_error("peer regions support 2..8 ranks (got rank %d of %d)", rank, world);
+    return false;
+  }
+  if (!dev->peer_regions[0] || dev->peer_world != 0) {
+    set_last_error("export this rank's peer region before importing the others");
+    return false;
+  }
+  cudaSetDevice(dev->ordinal);
+  void* local = dev->peer_regions[0];
+  dev->peer_regions[0] = nullptr;
+  for (int r = 0; r < world; r++) {
+    if (r == rank) {
+      dev->peer_regions[r] = local;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + (size_t)r * 64, 64);
+    void* mapped = nullptr;
+    if (!check_cuda(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) {
+      dev->peer_rank = rank;
+      dev->peer_world = world;
+      comm_peer_close(dev);
+      return false;
+    }
+    dev->peer_regions[r] = mapped;
+  }
+  dev->peer_rank = rank;
+  dev->peer_world = world;
+  dev->peer_ready = true;
+  return true;
+}
+
+void comm_peer_close(Device* dev) {
+  cudaSetDevice(dev->ordinal);
+  if (dev->peer_world == 0) {  // exported only
+    if (dev->peer_regions[0]) cudaFree(dev->peer_regions[0]);
+  } else {
+    for (int r = 0; r < dev->peer_world; r++) {
+      if (!dev->peer_regions[r]) continue;
+      if (r == dev->peer_rank) cudaFree(dev->peer_regions[r]);
+      else cudaIpcCloseMemHandle(dev->peer_regions[r]);
+    }
+  }
+  for (void*& p : dev->peer_regions) p = nullptr;
+  dev->peer_ready = false;
+  dev->peer_world = 0;
+}
+
+bool comm_all_reduce_sum(Device* dev, const void* src, void* dst, uint64_t count, int dtype, bool pdl) {
+  if (dev->peer_ready && peer_enabled() && dev->peer_world == dev->comm_world &&
+      peer_all_reduce_launch(dev->peer_regions, dev->peer_rank, dev->peer_world, dev->peer_slot_bytes, dtype, src, dst, count,
+                             dev->error_flag_dev, pdl, dev->stream))
+    return true;
   Nccl* api = nccl();
   ncclDataType_t t;
   if (!api || !dev->comm) {

@@ -34,6 +34,12 @@ struct Device {
   // Tensor-parallel communicator (void* = ncclComm_t), set by comm_init.
   void* comm = nullptr;
   int comm_rank = 0, comm_world = 1;
+  // Peer-mapped regions for the one-shot all-reduce (kernels/peer_reduce.cu): peer_regions[r] is rank r's region as
+  // mapped into this process, peer_regions[peer_rank] the local allocation.
+  void* peer_regions[8] = {nullptr};
+  uint64_t peer_slot_bytes = 0;
+  int peer_rank = 0, peer_world = 0;
+  bool peer_ready = false;
   std::mutex mu;
   // Transfer counters (src/runtime/device_memory.zig:258-304).
   uint64_t h2d_bytes = 0, d2h_bytes = 0, live_bytes = 0, peak_bytes = 0;
@@ -77,7 +83,13 @@ JitKernel* jit_get_kernel(const std::string& source, const char* entry, std::str
 // NCCL, loaded with dlopen so the library also loads where NCCL is absent.
 bool comm_unique_id(uint8_t out[128]);
 bool comm_init(Device* dev, const uint8_t id[128], int rank, int world);
-bool comm_all_reduce_sum(Device* dev, const void* src, void* dst, uint64_t count, int dtype);
+// Small sums go through the peer-memory kernel when the regions are set up (and PJRTX_B200_PEER_ALLREDUCE is not 0).
+bool comm_all_reduce_sum(Device* dev, const void* src, void* dst, uint64_t count, int dtype, bool pdl = false);
+// Peer regions: every rank exports a handle of its own region, the host ships all handles to all ranks, every rank
+// imports them. All ranks must have exported before any rank executes.
+bool comm_peer_export(Device* dev, uint8_t handle[64]);
+bool comm_peer_import(Device* dev, const uint8_t* handles, int rank, int world);
+void comm_peer_close(Device* dev);
 bool comm_all_gather(Device* dev, const void* src, void* dst, uint64_t send_count, int dtype);
 void comm_destroy(Device* dev);
 

@@ -1261,7 +1261,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         (*launches)++;
         break;
       case Step::kAllReduce:
-        if (!comm_all_reduce_sum(dev, ptr.of(st.inputs[0]), ptr.of(st.outputs[0]), st.count, st.dtype)) {
+        if (!comm_all_reduce_sum(dev, ptr.of(st.inputs[0]), ptr.of(st.outputs[0]), st.count, st.dtype, exe->pdl)) {
           *error = last_error();
           return false;
         }

@@ -125,4 +125,12 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count);
 int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, const void* q, const void* k, const void* v,
                        const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream);
 
+// All-reduce (sum) over peer-mapped regions, one launch per rank (kernels/peer_reduce.cu). `regions[r]` is rank r's
+// region as mapped into this process (regions[rank] is the local one), `peer_region_bytes(slot_bytes)` long.
+// Returns 0 when the call does not fit (more than 8 ranks, size not a multiple of 8 x ranks bytes, or a part of it
+// larger than half a slot).
+uint64_t peer_region_bytes(uint64_t slot_bytes);
+int peer_all_reduce_launch(void* const* regions, int rank, int world, uint64_t slot_bytes, int dtype, const void* in, void* out,
+                           uint64_t count, int* error_flag, bool pdl, cudaStream_t stream);
+
 }  // namespace pjrtx

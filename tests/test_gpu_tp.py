@@ -1,7 +1,8 @@
 """Tensor parallelism on real GPUs: one process per GPU, NCCL all_reduce / all_gather inside the executable.
 
 Each rank compiles its partition of the tiny Llama-shaped decode step, feeds its own weight and cache shards, and must
-reproduce the CPU oracle's logits of the unpartitioned program. Skipped when fewer than two GPUs are visible.
+reproduce the CPU oracle's logits of the unpartitioned program; once with NCCL's all-reduce, once with the one-kernel
+all-reduce over peer-mapped memory. Skipped when fewer than two GPUs are visible.
 NVLS is switched off so that a rank that dies mid-test leaves nothing bound inside the switch.
 """
 import os
@@ -29,7 +30,7 @@ def _shard(arr, split_dim, rank, world):
     return np.ascontiguousarray(np.take(arr, range(rank * n, (rank + 1) * n), axis=split_dim))
 
 
-def _worker(rank, world, port, batch, queue):
+def _worker(rank, world, port, batch, peer, queue):
     import torch.distributed as dist
 
     import pjrtx_b200
@@ -39,7 +40,7 @@ def _worker(rank, world, port, batch, queue):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        _run_rank(rank, world, batch, queue, dist, pjrtx_b200)
+        _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200)
     except Exception:  # report instead of leaving the parent to wait for its timeout
         import traceback
 
@@ -49,7 +50,7 @@ def _worker(rank, world, port, batch, queue):
         dist.destroy_process_group()
 
 
-def _run_rank(rank, world, batch, queue, dist, pjrtx_b200):
+def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
     if True:
         be = pjrtx_b200.Backend()
         cfg = llama.TINY
@@ -63,6 +64,8 @@ def _run_rank(rank, world, batch, queue, dist, pjrtx_b200):
         uid = [be.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         be.comm_init(rank, uid[0], rank, world)
+        if peer:  # all-reduce as one kernel per rank over peer-mapped memory instead of the library collective
+            be.enable_peer_all_reduce(rank, rank, world, dist.all_gather_object)
         exe = be.compile_executable(full, [rank], partition=rank)
         kinds = [s["type"] for s in exe.describe()["kernel_plan"]["steps"]]
         results = []
@@ -77,8 +80,8 @@ def _run_rank(rank, world, batch, queue, dist, pjrtx_b200):
                                  for r in results]))
 
 
-@pytest.mark.parametrize("batch", [2, 16])
-def test_two_gpu_tensor_parallel_decode_matches_oracle(batch):
+@pytest.mark.parametrize("batch,peer", [(2, False), (16, False), (2, True), (16, True)])
+def test_two_gpu_tensor_parallel_decode_matches_oracle(batch, peer):
     import torch
     import torch.multiprocessing as mp
 
@@ -90,7 +93,7 @@ def test_two_gpu_tensor_parallel_decode_matches_oracle(batch):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, batch, queue)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, batch, peer, queue)) for r in range(world)]
     for p in procs:
         p.start()
     got = {}
