@@ -287,6 +287,15 @@ uint64_t pjrtx_b200_executable_step_times(PjrtxB200Executable *executable, float
 /* Backend.destroyExecutable (backend.zig:148). */
 void pjrtx_b200_executable_destroy(PjrtxB200Executable *executable);
 
+/* ---- StableHLO text ------------------------------------------------------- */
+/* Reads `func.func @main` of a textual StableHLO module into a plan (the subset of operations the backend executes;
+ * static shapes; pretty or generic operation syntax). Replaces, for text, the MLIR-based importer
+ * (src/compiler/stablehlo_module_import.zig:241-264, stablehlo_operation_import.zig:22-456). NULL on failure with
+ * last_error holding one line in the reference's format (src/compiler/stablehlo_decode.zig:117-140):
+ *   unsupported op: op=<name> loc=L:C dtype=<t> rank=<r|unknown> sharding=<...> feature=stablehlo-op
+ * or, for malformed text, `invalid module: loc=L:C detail="..." feature=stablehlo-text`. */
+PjrtxB200Plan *pjrtx_b200_plan_from_stablehlo_text(const char *text, uint64_t length);
+
 /* ---- custom calls -------------------------------------------------------- */
 /* Backend.register{Identity,Unary,Binary}CustomCall / unregisterCustomCall / customCallRegistryVersion
  * (backend.zig:150-175). `op_name` is "identity" or an elementwise kind name; arity 1 or 2. */

@@ -406,6 +406,8 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
                 r = x[0]
             else:
                 raise NotImplementedError(f"custom call {ins.target}")
+        elif k == "optimization_barrier":
+            r = x[0]
         elif k == "all_reduce":
             r = all_reduce(x[0], code) if all_reduce is not None else x[0]
         elif k == "all_gather":

@@ -111,6 +111,7 @@ SYMBOLS = {
     "pjrtx_b200_plan_set_parameter_sharding": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_int, ctypes.c_char_p, ctypes.c_int64]),
     "pjrtx_b200_plan_set_output_sharding": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_int, ctypes.c_char_p, ctypes.c_int64]),
     "pjrtx_b200_plan_set_donation": (ctypes.c_int, [_P, _U32P, ctypes.c_uint64, _U32P, _U32P, ctypes.c_uint64]),
+    "pjrtx_b200_plan_from_stablehlo_text": (_P, [ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_verify": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_program": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
@@ -354,6 +355,21 @@ class Backend:
             buf = ctypes.create_string_buffer(4096)
             ok = self.lib.pjrtx_b200_plan_verify(plan, buf, 4096)
             return "" if ok else buf.value.decode()
+        finally:
+            self.lib.pjrtx_b200_plan_destroy(plan)
+
+    def import_stablehlo_text(self, text: str) -> plan_mod.PlanBuilder:
+        """`func.func @main` of a textual StableHLO module as a PlanBuilder (compile it like any other plan).
+
+        Raises BackendError("Unimplemented") with the reference-format diagnostic for operations outside the subset and
+        BackendError("InvalidProgram") for malformed text."""
+        raw = text.encode()
+        plan = self.lib.pjrtx_b200_plan_from_stablehlo_text(raw, len(raw))
+        if not plan:
+            err = self._err()
+            raise BackendError("Unimplemented" if err.startswith("unsupported op") else "InvalidProgram", err)
+        try:
+            return plan_mod.PlanBuilder.from_description(json.loads(_text(self.lib, self.lib.pjrtx_b200_plan_describe, plan)))
         finally:
             self.lib.pjrtx_b200_plan_destroy(plan)
 

@@ -11,6 +11,7 @@
 #include "plan.h"
 #include "program.h"
 #include "sharding.h"
+#include "stablehlo_text.h"
 
 using namespace pjrtx;
 
@@ -244,6 +245,14 @@ PjrtxB200Plan* pjrtx_b200_plan_create(int32_t num_replicas, int32_t num_partitio
 }
 
 void pjrtx_b200_plan_destroy(PjrtxB200Plan* plan) { delete plan; }
+
+PjrtxB200Plan* pjrtx_b200_plan_from_stablehlo_text(const char* text, uint64_t length) {
+  GUARD_PTR(if (!text) return nullptr; auto p = std::make_unique<PjrtxB200Plan>(); std::string error;
+            if (!import_stablehlo_text(std::string(text, length), &p->plan, &error)) {
+              set_last_error("%s", error.c_str());
+              return nullptr;
+            } return p.release();)
+}
 
 uint32_t pjrtx_b200_plan_add_value(PjrtxB200Plan* plan, int role, int dtype, const int64_t* dims, uint64_t rank) {
   try {

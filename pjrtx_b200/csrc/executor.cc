@@ -1160,8 +1160,19 @@ struct Pointers {
   }
 };
 
+// Waits for the last step event and fills step_ms from consecutive event pairs.
+void collect_step_times(Executable* exe) {
+  const size_t n = exe->kp.steps.size();
+  cudaEventSynchronize(exe->step_events[n]);
+  exe->step_ms.assign(n, 0.f);
+  for (size_t k = 0; k < n; k++) cudaEventElapsedTime(&exe->step_ms[k], exe->step_events[k], exe->step_events[k + 1]);
+}
+
+// `timed`: an event is recorded before every step and after the last one. Outside a stream capture the call then
+// waits and fills step_ms; inside a capture (`capturing`) the records become graph nodes and the caller reads the
+// times after it has launched the graph (collect_step_times).
 bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* launches, std::string* error,
-               bool timed = false) {
+               bool timed = false, bool capturing = false) {
   Device* dev = ds.dev;
   const KernelPlan& kp = exe->kp;
   if (timed) {
@@ -1285,9 +1296,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
   }
   if (timed) {
     cudaEventRecord(exe->step_events[kp.steps.size()], dev->stream);
-    cudaEventSynchronize(exe->step_events[kp.steps.size()]);
-    exe->step_ms.assign(kp.steps.size(), 0.f);
-    for (size_t k = 0; k < kp.steps.size(); k++) cudaEventElapsedTime(&exe->step_ms[k], exe->step_events[k], exe->step_events[k + 1]);
+    if (!capturing) collect_step_times(exe);
   }
   return true;
 }
@@ -1446,7 +1455,7 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
       if (b) buffer_free(b);
   };
 
-  if (exe->use_graph && !exe->profiling) {
+  if (exe->use_graph) {
     // Small parameters are staged into fixed slots; the graph reads the slots.
     std::vector<void*> graph_ptrs = param_ptrs;
     uint64_t dynamic_inputs = 0;
@@ -1461,6 +1470,35 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
         graph_ptrs[p] = slot;
         dynamic_inputs++;
       }
+    if (exe->profiling) {
+      // Profiled replay: the same steps captured with an event record between them, so the step times are those of
+      // graph nodes (no host launch gap) running one after the other; instantiated for this call only.
+      Pointers gp{&kp, &ds, &graph_ptrs, {}};
+      cudaGraph_t graph = nullptr;
+      cudaGraphExec_t timed_exec = nullptr;
+      if (!check_cuda(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) {
+        *error = last_error();
+        return false;
+      }
+      uint64_t captured = 0;
+      std::string run_error;
+      bool ok = run_steps(exe, ds, gp, &captured, &run_error, true, true);
+      cudaError_t ce = cudaStreamEndCapture(dev->stream, &graph);
+      if (ok && ce == cudaSuccess && graph) ce = cudaGraphInstantiate(&timed_exec, graph, 0);
+      if (graph) cudaGraphDestroy(graph);
+      if (!ok || ce != cudaSuccess || !timed_exec) {
+        *error = ok ? std::string("profiled graph capture failed: ") + cudaGetErrorString(ce) : run_error;
+        cudaGetLastError();
+        return false;
+      }
+      ce = cudaGraphLaunch(timed_exec, dev->stream);
+      if (ce == cudaSuccess) collect_step_times(exe);
+      cudaGraphExecDestroy(timed_exec);
+      if (ce != cudaSuccess) {
+        *error = std::string("profiled graph launch failed: ") + cudaGetErrorString(ce);
+        return false;
+      }
+    } else {
     if (!ds.graph || ds.graph_param_ptrs != graph_ptrs) {
       if (ds.graph) {
         cudaGraphExecDestroy(ds.graph);
@@ -1495,6 +1533,7 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
     if (!check_cuda(cudaGraphLaunch(ds.graph, dev->stream), "graph launch")) {
       *error = last_error();
       return false;
+    }
     }
     launches = kp.steps.size();
     exe->stats.graph_launch_count++;
