@@ -1160,6 +1160,13 @@ struct Pointers {
   }
 };
 
+// Inside a stream capture an ordinary event record only marks a dependency; the external flag makes it a graph node
+// that takes a timestamp every time the graph runs.
+void record_step_event(cudaEvent_t event, cudaStream_t stream, bool capturing) {
+  if (capturing) cudaEventRecordWithFlags(event, stream, cudaEventRecordExternal);
+  else cudaEventRecord(event, stream);
+}
+
 // Waits for the last step event and fills step_ms from consecutive event pairs.
 void collect_step_times(Executable* exe) {
   const size_t n = exe->kp.steps.size();
@@ -1181,11 +1188,11 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
       cudaEventCreate(&e);
       exe->step_events.push_back(e);
     }
-    cudaEventRecord(exe->step_events[0], dev->stream);
+    record_step_event(exe->step_events[0], dev->stream, capturing);
   }
   size_t step_index = 0;
   for (const Step& st : kp.steps) {
-    if (timed && step_index > 0) cudaEventRecord(exe->step_events[step_index], dev->stream);
+    if (timed && step_index > 0) record_step_event(exe->step_events[step_index], dev->stream, capturing);
     step_index++;
     switch (st.type) {
       case Step::kFused: {
@@ -1295,7 +1302,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
     return false;
   }
   if (timed) {
-    cudaEventRecord(exe->step_events[kp.steps.size()], dev->stream);
+    record_step_event(exe->step_events[kp.steps.size()], dev->stream, capturing);
     if (!capturing) collect_step_times(exe);
   }
   return true;
@@ -1482,7 +1489,12 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
       }
       uint64_t captured = 0;
       std::string run_error;
+      // An event record between two kernels leaves no kernel-to-kernel edge to make programmatic, and the launch
+      // attribute is refused there: the timed capture launches without it.
+      const bool pdl = exe->pdl;
+      exe->pdl = false;
       bool ok = run_steps(exe, ds, gp, &captured, &run_error, true, true);
+      exe->pdl = pdl;
       cudaError_t ce = cudaStreamEndCapture(dev->stream, &graph);
       if (ok && ce == cudaSuccess && graph) ce = cudaGraphInstantiate(&timed_exec, graph, 0);
       if (graph) cudaGraphDestroy(graph);

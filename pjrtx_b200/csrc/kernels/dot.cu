@@ -605,8 +605,14 @@ DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_maj
   const int64_t kblocks = (s.k + 64 * p.sub - 1) / (64 * p.sub);
   const int64_t units = tiles * kblocks;
   p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(units, sm_count));
+  // A split tile costs its f32 partial twice (written, read back): m_tile x 128 x 8 bytes per contributor, against
+  // 128 x k x 2 bytes of weights per tile. Split only while the partials of a tile stay below about half its weights,
+  // or when whole tiles would leave most of the machine idle.
+  const int64_t split_ok = s.k / (8 * (int64_t)p.m_tile);
+  p.whole_tiles = (split_ok < 2 || (p.m_tile >= 128 && 2 * tiles >= sm_count)) ? 1 : 0;
+  if (p.whole_tiles) p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count));
   p.per_cta = units / p.grid;
-  p.max_contrib = (int)((kblocks + p.per_cta - 1) / p.per_cta) + 1;
+  p.max_contrib = p.whole_tiles ? 1 : (int)((kblocks + p.per_cta - 1) / p.per_cta) + 1;
   const size_t stage = umma::stage_bytes(p.m_tile, p.sub, p.nh);
   p.stages = (int)std::max<size_t>(2, std::min<size_t>(12, (227 * 1024 - 1536) / stage));
   p.smem = umma::smem_bytes(p.stages, p.m_tile, p.sub, p.nh);
@@ -717,6 +723,7 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
   p.is_bf16 = s.dtype == kBF16;
   p.rhs_k_major = k_major ? 1 : 0;
   p.early_rhs = early_rhs ? 1 : 0;
+  p.whole_tiles = plan.whole_tiles;
   if (plan.nh == 2)
     return plan.sub == 2 ? launch_umma_sub<2, 2>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 2>(p, maps, plan, pdl, stream);
   return plan.sub == 2 ? launch_umma_sub<2, 1>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 1>(p, maps, plan, pdl, stream);

@@ -53,7 +53,7 @@ struct DotScratch {
   // Path 1 without batch axes runs the TMA-fed persistent kernel (stream-K decomposition).
   int tma = 0;
   // Paths 1 and 4 for 16-bit floats without batch axes can run on the tensor cores (tcgen05, accumulator in TMEM).
-  int umma = 0, m_tile = 0, sub = 1, nh = 1;
+  int umma = 0, m_tile = 0, sub = 1, nh = 1, whole_tiles = 0;
   int grid = 0, stages = 0, max_contrib = 0;
   long long per_cta = 0;
   uint64_t smem = 0;

@@ -19,6 +19,8 @@
 // Work decomposition (stream-K): units are ordered tile-major and CTA b of G takes the b-th equal share, so every SM
 // streams the same number of bytes whatever the shape. A CTA that covers only part of a tile's k range writes a
 // partial; the CTA that arrives last for the tile folds the partials in CTA order (run-to-run identical results).
+// For tall tiles (many rows of m) the f32 partials would outweigh the weights they save from idling, so the host
+// then asks for whole tiles per CTA (`whole_tiles`) and nothing is folded.
 //
 // Programmatic dependent launch: weights are never written by earlier work of the stream (`early_rhs`), so their
 // copies for the first ring of stages are issued before griddepcontrol.wait; activation copies and all stores wait.
@@ -62,6 +64,7 @@ struct Params {
   int rhs_k_major;       // 1: rhs is [n, k] with k contiguous
   int rhs_3d;            // rhs [k, n] with n % 64 == 0: one copy per stage through a 3-d view {64 n, k, n / 64}
   int early_rhs;         // rhs copies may start before the preceding kernel of the stream has finished
+  int whole_tiles;       // 1: CTA b owns tiles [b*T/G, (b+1)*T/G) completely instead of an equal share of units
 };
 
 struct Maps {
@@ -225,8 +228,12 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long u_begin = (long long)blockIdx.x * p.units / gridDim.x;
-  const long long u_end = (long long)(blockIdx.x + 1) * p.units / gridDim.x;
+  // Equal shares of units; with `whole_tiles` equal shares of tiles (no tile is split, nothing to fold).
+  const long long tiles_total = p.units / p.kblocks;
+  const long long u_begin = p.whole_tiles ? ((long long)blockIdx.x * tiles_total / gridDim.x) * p.kblocks
+                                          : (long long)blockIdx.x * p.units / gridDim.x;
+  const long long u_end = p.whole_tiles ? ((long long)(blockIdx.x + 1) * tiles_total / gridDim.x) * p.kblocks
+                                        : (long long)(blockIdx.x + 1) * p.units / gridDim.x;
   const int count = (int)(u_end - u_begin);
   // Two accumulator sets of NH x m_tile f32 columns; the allocation is a power of two >= 32 columns.
   uint32_t tmem_cols = 32;
@@ -408,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
         const long long tile_units_begin = (long long)tile * p.kblocks;
         const long long first_cta = ((tile_units_begin + 1) * gridDim.x + p.units - 1) / p.units - 1;
         const long long last_cta = ((tile_units_begin + p.kblocks) * gridDim.x + p.units - 1) / p.units - 1;
-        const int contributors = (int)(last_cta - first_cta + 1);
+        const int contributors = p.whole_tiles ? 1 : (int)(last_cta - first_cta + 1);
         const long long n_total = p.n[c.group];
         const long long n_first = (long long)c.n_tile * TW + n_local;  // this thread's column in half 0
         const int m0 = c.m_idx * p.m_tile;
