@@ -247,6 +247,11 @@ int pjrtx_b200_plan_verify(PjrtxB200Plan *plan, char *out, uint64_t capacity);
 /* The plan itself as JSON (values, instructions, attributes, constant payloads in hex, shardings, outputs): the
  * inverse of the builder calls above, used to inspect what pjrtx_b200_plan_partition produced. Returns the full length. */
 uint64_t pjrtx_b200_plan_describe(PjrtxB200Plan *plan, char *out, uint64_t capacity);
+/* Stable cache key of the plan under the current backend state ("pjrtx-<16 hex digits>"): the fields the reference's
+ * executable cache hashes (src/runtime/executable_fingerprint.zig:9-140: capabilities name, custom-call registry
+ * version, compile options, shardings, donation, values, instructions with attributes, constants, call targets). A host
+ * keeps compiled executables under this key. Same text-out convention as plan_describe. */
+uint64_t pjrtx_b200_plan_fingerprint(PjrtxB200Plan *plan, char *out, uint64_t capacity);
 /* Backend program graph (nodes, edges, fusion groups, schedule, liveness) as JSON; needs no device.
  * Returns the full length; writes at most capacity-1 bytes. program_build.build (program_build.zig:10-207). */
 uint64_t pjrtx_b200_plan_describe_program(PjrtxB200Plan *plan, char *out, uint64_t capacity);

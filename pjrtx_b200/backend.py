@@ -114,6 +114,7 @@ SYMBOLS = {
     "pjrtx_b200_plan_from_stablehlo_text": (_P, [ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_verify": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
+    "pjrtx_b200_plan_fingerprint": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_program": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_kernels": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_partition": (_P, [_P, ctypes.c_int32, ctypes.c_int32]),
@@ -384,6 +385,14 @@ class Backend:
                 return plan_mod.PlanBuilder.from_description(json.loads(_text(self.lib, self.lib.pjrtx_b200_plan_describe, part)))
             finally:
                 self.lib.pjrtx_b200_plan_destroy(part)
+        finally:
+            self.lib.pjrtx_b200_plan_destroy(plan)
+
+    def plan_fingerprint(self, builder: plan_mod.PlanBuilder) -> str:
+        """Cache key of the plan under the current backend state (custom-call registry version included)."""
+        plan = builder.build(self.lib)
+        try:
+            return _text(self.lib, self.lib.pjrtx_b200_plan_fingerprint, plan)
         finally:
             self.lib.pjrtx_b200_plan_destroy(plan)
 

@@ -335,6 +335,10 @@ uint64_t pjrtx_b200_plan_describe(PjrtxB200Plan* plan, char* out, uint64_t capac
   GUARD_INT(if (!plan) return 0; return write_text(describe_plan(plan->plan), out, capacity);)
 }
 
+uint64_t pjrtx_b200_plan_fingerprint(PjrtxB200Plan* plan, char* out, uint64_t capacity) {
+  GUARD_INT(if (!plan) return 0; return write_text(plan_fingerprint(plan->plan, "b200_cuda", custom_call_registry_version()), out, capacity);)
+}
+
 uint64_t pjrtx_b200_plan_describe_program(PjrtxB200Plan* plan, char* out, uint64_t capacity) {
   GUARD_INT(if (!plan) return 0; std::string msg = verify_plan(plan->plan); if (!msg.empty()) {
     set_last_error("%s", msg.c_str());

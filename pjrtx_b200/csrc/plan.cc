@@ -325,4 +325,76 @@ std::string describe_plan(const Plan& plan) {
   return s + "]}";
 }
 
+namespace {
+struct Fnv {
+  uint64_t h = 1469598103934665603ull;
+  void bytes(const void* p, size_t n) {
+    const uint8_t* b = static_cast<const uint8_t*>(p);
+    for (size_t i = 0; i < n; i++) {
+      h ^= b[i];
+      h *= 1099511628211ull;
+    }
+  }
+  template <typename T> void pod(const T& v) { bytes(&v, sizeof(T)); }
+  void str(const std::string& s) {
+    pod((uint64_t)s.size());
+    bytes(s.data(), s.size());
+  }
+  template <typename T> void list(const std::vector<T>& v) {
+    pod((uint64_t)v.size());
+    if (!v.empty()) bytes(v.data(), v.size() * sizeof(T));
+  }
+};
+}  // namespace
+
+std::string plan_fingerprint(const Plan& plan, const char* backend_name, uint64_t custom_call_registry_version) {
+  Fnv f;
+  f.str("pjrtx-b200-executable-cache-v1");
+  f.str(backend_name ? backend_name : "");
+  f.pod(custom_call_registry_version);
+  f.pod(plan.num_replicas);
+  f.pod(plan.num_partitions);
+  f.pod(plan.use_shardy);
+  f.list(plan.device_assignment);
+  auto shardings = [&](const std::vector<Sharding>& v) {
+    f.pod((uint64_t)v.size());
+    for (const Sharding& s : v) {
+      f.pod((int)s.kind);
+      f.str(s.mesh_name);
+      f.list(s.device_assignment);
+      f.pod(s.split_dim);
+    }
+  };
+  shardings(plan.parameter_shardings);
+  shardings(plan.output_shardings);
+  f.list(plan.output_ids);
+  f.list(plan.donated_parameter_indices);
+  f.pod((uint64_t)plan.output_aliases.size());
+  for (const OutputAlias& a : plan.output_aliases) {
+    f.pod(a.output_index);
+    f.pod(a.parameter_index);
+    f.pod(a.kind);
+  }
+  f.pod((uint64_t)plan.values.size());
+  for (const Value& v : plan.values) {
+    f.pod((int)v.role);
+    f.pod(v.dtype);
+    f.list(v.dims);
+  }
+  f.pod((uint64_t)plan.instructions.size());
+  for (const Instruction& ins : plan.instructions) {
+    f.pod((int)ins.kind);
+    f.list(ins.inputs);
+    f.list(ins.outputs);
+    f.pod((uint64_t)ins.attrs.size());
+    for (const auto& kv : ins.attrs) {
+      f.str(kv.first);
+      f.list(kv.second);
+    }
+    f.list(ins.literal);
+    f.str(ins.custom_call_target);
+  }
+  return strfmt("pjrtx-%016llx", (unsigned long long)f.h);
+}
+
 }  // namespace pjrtx

@@ -251,3 +251,32 @@ def test_partitioned_decode_keeps_attention_recognisable(backend):
         kinds = [s["type"] for s in k["steps"]]
         assert kinds.count("attention_decode") == cfg.layers
         assert kinds.count("all_reduce") == 2 * cfg.layers and kinds.count("all_gather") == 1
+
+
+def test_plan_fingerprint_is_stable_and_sensitive(backend):
+    """Cache key: equal for equal plans, different when an attribute, a constant, a donation or the custom-call
+    registry changes (the fields of src/runtime/executable_fingerprint.zig:9-140)."""
+    import re
+
+    def build(scale=0.5, perm=(1, 0), donate=None):
+        b = PlanBuilder()
+        x = b.parameter(P.F32, [4, 8])
+        y = b.transpose(x * np.float32(scale), list(perm))
+        b.set_outputs([y], donate=donate)
+        return b
+
+    a = backend.plan_fingerprint(build())
+    assert re.fullmatch(r"pjrtx-[0-9a-f]{16}", a)
+    assert backend.plan_fingerprint(build()) == a
+    assert backend.plan_fingerprint(build(scale=0.25)) != a
+    c = PlanBuilder()
+    x = c.parameter(P.F32, [4, 8])
+    c.set_outputs([c.reshape(x * np.float32(0.5), [8, 4])])
+    assert backend.plan_fingerprint(c) != a
+    version = backend.lib.pjrtx_b200_custom_call_registry_version()
+    assert backend.lib.pjrtx_b200_register_custom_call(b"tests.fingerprint.identity", b"identity", 1)
+    try:
+        assert backend.lib.pjrtx_b200_custom_call_registry_version() != version
+        assert backend.plan_fingerprint(build()) != a
+    finally:
+        backend.lib.pjrtx_b200_unregister_custom_call(b"tests.fingerprint.identity")
