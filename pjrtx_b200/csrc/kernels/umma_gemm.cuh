@@ -43,6 +43,11 @@ constexpr int kTileN = 128;          // weight columns per tile (MMA M)
 constexpr int kSubK = 64;            // k elements per swizzle row (128 bytes of 16-bit data)
 constexpr int kThreads = 192;        // warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer
 constexpr unsigned kSpinLimit = 1u << 22;
+#ifndef PJRTX_UMMA_SHARED_FOLD_MIN
+#define PJRTX_UMMA_SHARED_FOLD_MIN 384
+#endif
+// rows x contributors of a split tile from which all contributors fold it together (below: the last arriver alone)
+constexpr int kSharedFoldMin = PJRTX_UMMA_SHARED_FOLD_MIN;
 
 struct Params {
   int m, k;
@@ -500,9 +505,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (threadIdx.x == 0) flags[0] = arrive_acq_rel(&p.counters[tile]) == (unsigned)contributors - 1;
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          // Few rows or few contributors: whoever arrives last folds everything. Otherwise the fold is shared: every
+          // Few rows or few contributors: whoever arrives last folds everything (measured faster up to ~7 contributors
+          // of 32 rows: the shared form pays a second counter round trip). Otherwise the fold is shared: every
           // contributor takes a slice of the rows once all have arrived, which this CTA checks after its last segment.
-          const bool shared_fold = m_rows * contributors >= 128;
+          const bool shared_fold = m_rows * contributors >= kSharedFoldMin;
           if (!shared_fold) {
             if (flags[0]) {
               fold_rows(tile, c, m0, 0, m_rows, contributors);
