@@ -1,10 +1,10 @@
 """Generates tests/golden/llama_like_*.npz from the reference's own NumPy reference.
 
-Run in a container that has the reference checkout:
-    python tests/golden/make_llama_like_golden.py /root/reference
+Run where a checkout of the reference is available, giving its root:
+    python tests/golden/make_llama_like_golden.py <reference checkout>
 It imports src/plugin/jax/jax_llama_like_inference.py (its `make_fixture` and `np_reference`, :206-252), evaluates
 the two fixtures the reference's test uses (seed default_rng(7); shapes (2,4,8) and (4,16,32), :439-441) and stores
-inputs and expected outputs. The GPU box has no reference checkout, so the vectors are committed.
+inputs and expected outputs. Machines that run the tests have no reference checkout, so the vectors are committed.
 """
 import importlib.util
 import os
@@ -30,4 +30,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_llama_like_golden.py <reference checkout>")
+    main(sys.argv[1])
