@@ -43,11 +43,6 @@ constexpr int kTileN = 128;          // weight columns per tile (MMA M)
 constexpr int kSubK = 64;            // k elements per swizzle row (128 bytes of 16-bit data)
 constexpr int kThreads = 192;        // warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer
 constexpr unsigned kSpinLimit = 1u << 22;
-#ifndef PJRTX_UMMA_SHARED_FOLD_MIN
-#define PJRTX_UMMA_SHARED_FOLD_MIN 384
-#endif
-// rows x contributors of a split tile from which all contributors fold it together (below: the last arriver alone)
-constexpr int kSharedFoldMin = PJRTX_UMMA_SHARED_FOLD_MIN;
 
 struct Params {
   int m, k;
@@ -402,47 +397,6 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
       const int first_tile = (int)(u_begin / p.kblocks);
       const int last_tile = (int)((u_end - 1) / p.kblocks);
       const int n_local = warp * 32 + lane;
-      struct Pending {
-        int tile, contributors, index, m0, m_rows;
-      };
-      Pending pending[2];
-      int pending_count = 0;
-      // Adds rows [r_begin, r_end) of a tile's partials over its contributors (in CTA order, sixteen rows at a time
-      // with all their loads issued before the adds) and writes the outputs; this thread owns column n_local.
-      auto fold_rows = [&](int tile, const Cursor& c, int m0, int r_begin, int r_end, int contributors) {
-        const float* first_slot = p.partials + ((long long)tile * p.max_contrib * p.m_tile) * TW;
-        const long long slot_stride = (long long)p.m_tile * TW;
-        const long long n_total = p.n[c.group];
-        const long long ldo = p.ldo[c.group];
-#pragma unroll
-        for (int h = 0; h < NH; h++) {
-          const long long n = (long long)c.n_tile * TW + n_local + h * kTileN;
-          for (int r0 = r_begin; r0 < r_end; r0 += 16) {
-            float t[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) t[j] = 0.f;
-#pragma unroll 2
-            for (int q = 0; q < contributors; q++) {
-              const float* src = first_slot + (long long)q * slot_stride + r0 * TW + h * kTileN + n_local;
-              float v[16];
-#pragma unroll
-              for (int j = 0; j < 16; j++) v[j] = (r0 + j < r_end) ? __ldcg(src + j * TW) : 0.f;
-#pragma unroll
-              for (int j = 0; j < 16; j++) t[j] += v[j];
-            }
-            if (n < n_total) {
-#pragma unroll
-              for (int j = 0; j < 16; j++) {
-                if (r0 + j < r_end) {
-                  const long long at = (long long)(m0 + r0 + j) * ldo + n;
-                  if (p.is_bf16) static_cast<__nv_bfloat16*>(p.out[c.group])[at] = __float2bfloat16_rn(t[j]);
-                  else static_cast<__half*>(p.out[c.group])[at] = __float2half_rn(t[j]);
-                }
-              }
-            }
-          }
-        }
-      };
       int seg = 0;
       for (int tile = first_tile; tile <= last_tile; tile++, seg++) {
         Cursor c;
@@ -505,52 +459,42 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (threadIdx.x == 0) flags[0] = arrive_acq_rel(&p.counters[tile]) == (unsigned)contributors - 1;
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          // Few rows or few contributors: whoever arrives last folds everything (measured faster up to ~7 contributors
-          // of 32 rows: the shared form pays a second counter round trip). Otherwise the fold is shared: every
-          // contributor takes a slice of the rows once all have arrived, which this CTA checks after its last segment.
-          const bool shared_fold = m_rows * contributors >= kSharedFoldMin;
-          if (!shared_fold) {
-            if (flags[0]) {
-              fold_rows(tile, c, m0, 0, m_rows, contributors);
-              if (threadIdx.x == 0) p.counters[tile] = 0;
+          if (flags[0]) {
+            const float* first_slot = p.partials + ((long long)tile * p.max_contrib * p.m_tile) * TW;
+            const long long slot_stride = (long long)p.m_tile * TW;
+            // Sixteen rows at a time, all their loads issued before the adds; contributors are added in CTA order.
+#pragma unroll
+            for (int h = 0; h < NH; h++) {
+              const long long n = n_first + h * kTileN;
+              for (int r0 = 0; r0 < m_rows; r0 += 16) {
+                float t[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) t[j] = 0.f;
+#pragma unroll 2
+                for (int q = 0; q < contributors; q++) {
+                  const float* src = first_slot + (long long)q * slot_stride + r0 * TW + h * kTileN + n_local;
+                  float v[16];
+#pragma unroll
+                  for (int j = 0; j < 16; j++) v[j] = (r0 + j < m_rows) ? __ldcg(src + j * TW) : 0.f;
+#pragma unroll
+                  for (int j = 0; j < 16; j++) t[j] += v[j];
+                }
+                if (n < n_total) {
+#pragma unroll
+                  for (int j = 0; j < 16; j++) {
+                    if (r0 + j < m_rows) {
+                      const long long at = (long long)(m0 + r0 + j) * ldo + n;
+                      if (p.is_bf16) static_cast<__nv_bfloat16*>(p.out[c.group])[at] = __float2bfloat16_rn(t[j]);
+                      else static_cast<__half*>(p.out[c.group])[at] = __float2half_rn(t[j]);
+                    }
+                  }
+                }
+              }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-          } else if (pending_count < 2) {
-            pending[pending_count++] = Pending{tile, contributors, (int)(blockIdx.x - first_cta), m0, m_rows};
+            if (threadIdx.x == 0) p.counters[tile] = 0;
           }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-      }
-      // Shared folds of the (at most two) split tiles this CTA contributed to.
-      for (int k = 0; k < pending_count; k++) {
-        const Pending pd = pending[k];
-        if (threadIdx.x == 0) {
-          bool arrived = false;
-          for (unsigned spin = 0; spin < kSpinLimit; spin++) {
-            unsigned v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.counters + pd.tile) : "memory");
-            if (v >= (unsigned)pd.contributors) {
-              arrived = true;
-              break;
-            }
-          }
-          if (!arrived) atomicExch(p.error_flag, 15);
-          flags[0] = arrived;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (flags[0]) {
-          Cursor c;
-          c.tile = pd.tile;
-          c.kb = 0;
-          locate_tile(p, &c);
-          const int r_begin = (int)((long long)pd.index * pd.m_rows / pd.contributors);
-          const int r_end = (int)((long long)(pd.index + 1) * pd.m_rows / pd.contributors);
-          fold_rows(pd.tile, c, pd.m0, r_begin, r_end, pd.contributors);
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        // Second count: the contributor that finishes last leaves the counter at zero for the next launch. Nobody can
-        // still be waiting then, because finishing comes after waiting.
-        if (threadIdx.x == 0 && flags[0] && arrive_acq_rel(&p.counters[pd.tile]) == 2u * pd.contributors - 1) p.counters[pd.tile] = 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
