@@ -1037,7 +1037,13 @@ class Gen {
   std::string emit_row_kernel(FusedKernel* k) {
     int64_t items = C_ / vec_;
     int block = 32;
-    while (block < 512 && block * 4 < items) block *= 2;
+    // Many rows: a few items per thread keep the SMs full with small CTAs. Fewer rows than SMs: latency is what
+    // counts, so one item per thread (every loop over the row is then a single round of loads).
+    if (R_ >= sm_count_) {
+      while (block < 512 && block * 4 < items) block *= 2;
+    } else {
+      while (block < 1024 && block < items) block *= 2;
+    }
     k->block = block;
     k->grid = std::max<int64_t>(1, std::min<int64_t>(R_, (int64_t)sm_count_ * std::max(1, 2048 / block)));
     // Reductions by stage (a reduction of depth d runs in stage d-1).

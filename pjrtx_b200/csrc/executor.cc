@@ -786,6 +786,9 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
         for (; b > a; b--) {
           if (skipped(b - 1) && b - 1 > a) continue;  // never end a kernel on a skipped instruction
           std::vector<uint32_t> stored = stored_roots(a, b);
+          // Values without elements need no kernel (their storage has no bytes either).
+          stored.erase(std::remove_if(stored.begin(), stored.end(), [&](uint32_t r) { return plan.values[r].count() == 0; }),
+                       stored.end());
           std::vector<size_t> scatters;
           if (!scatters_of(a, b, &scatters)) {
             why = "a slice update's storage is used elsewhere in the run";

@@ -277,6 +277,22 @@ def test_slice_updates_ride_in_the_producing_kernel(gpu_backend):
         assert np.array_equal(got1[mask1], t0[mask1])
 
 
+def test_values_without_elements(gpu_backend):
+    """Empty operands and results: no kernel is launched for them, the other outputs are unaffected, and a contraction
+    with no rows returns an empty result."""
+    be = gpu_backend
+    b = PlanBuilder()
+    x, y, z = b.parameter(P.F32, [0, 4]), b.parameter(P.F32, [0, 4]), b.parameter(P.F32, [3])
+    w = b.parameter(P.F32, [4, 5])
+    b.set_outputs([x + y, z * z, b.dot_general(x, w, [1], [0])])
+    args = [np.zeros((0, 4), np.float32), np.zeros((0, 4), np.float32), np.array([1, 2, 3], np.float32),
+            np.ones((4, 5), np.float32)]
+    got = run_backend(be, b, args)
+    want = run_oracle(b, args)
+    assert got[0].shape == (0, 4) and got[2].shape == (0, 5)
+    assert np.array_equal(got[1], want[1]) and np.array_equal(got[1], np.array([1, 4, 9], np.float32))
+
+
 def test_buffer_round_trip_and_errors(gpu_backend):
     be = gpu_backend
     for dt in (np.float32, np.int32, np.uint8, np.int8, np.uint16, np.uint32, np.uint64, np.int64, np.float16, np.bool_):
