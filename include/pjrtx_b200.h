@@ -292,6 +292,88 @@ uint64_t pjrtx_b200_executable_step_times(PjrtxB200Executable *executable, float
 /* Backend.destroyExecutable (backend.zig:148). */
 void pjrtx_b200_executable_destroy(PjrtxB200Executable *executable);
 
+/* ---- resident-executable cache ----------------------------------------------- */
+/* Replaces the runtime's executable residency (src/runtime/executable_cache.zig): compile requests are keyed by
+ * fingerprint (pjrtx_b200_plan_fingerprint), a compiled executable stays resident while leased and afterwards until
+ * the byte budget or a memory-pressure trim needs its device memory. Victim order among idle entries: most resident
+ * bytes, then cheapest to compile, then least recently used, then smaller fingerprint (:284-313). An executable's
+ * resident bytes are the device memory it owns (resident constants + arena + contraction scratch). */
+typedef struct PjrtxB200ExecutableCache PjrtxB200ExecutableCache;
+
+/* executable_cache.Stats (src/runtime/executable_cache.zig:10-25). */
+typedef struct PjrtxB200ExecutableCacheStats {
+  uint64_t hits;
+  uint64_t misses;
+  uint64_t evictions;
+  uint64_t evicted_resident_bytes;
+  uint64_t resident_entries;
+  uint64_t resident_bytes;
+  uint64_t peak_resident_bytes;
+  uint64_t largest_resident_bytes;
+  uint64_t compile_latency_samples;
+  uint64_t compile_latency_us_total;
+  uint64_t compile_latency_us_peak;
+  uint64_t pressure_trim_requests;
+  uint64_t pressure_trimmed_bytes;
+  uint64_t pressure_trim_failures;
+} PjrtxB200ExecutableCacheStats;
+
+/* executable_cache.Trim (:66-73). */
+typedef struct PjrtxB200ExecutableCacheTrim {
+  uint64_t requested_bytes;
+  uint64_t target_resident_bytes;
+  uint64_t freed_bytes;
+  uint64_t evicted_entries;
+  uint64_t remaining_resident_bytes;
+  int32_t still_over_capacity;
+} PjrtxB200ExecutableCacheTrim;
+
+/* executable_cache.EntrySnapshot (:58-63). */
+typedef struct PjrtxB200ExecutableCacheEntry {
+  int32_t resident;
+  uint64_t resident_bytes;
+  uint64_t reference_count;
+  uint64_t compile_latency_us;
+} PjrtxB200ExecutableCacheEntry;
+
+/* Residency.init / deinit (:333-343). `capacity_bytes` is the device memory that buffers and resident executables
+ * share (0 = untracked: no pressure trims). Destroying the cache destroys every resident executable. */
+PjrtxB200ExecutableCache *pjrtx_b200_executable_cache_create(uint64_t capacity_bytes);
+void pjrtx_b200_executable_cache_destroy(PjrtxB200ExecutableCache *cache);
+/* Residency.recordCompile (:346-352): 1 = seen before (hit), 0 = new (miss), -1 = error. */
+int pjrtx_b200_executable_cache_record_compile(PjrtxB200ExecutableCache *cache, const char *fingerprint);
+/* Residency.acquireBackendExecutable (:379-391, 429-470): leases the resident executable of a recorded fingerprint, or
+ * compiles `plan` for the devices, trims idle entries to make room for its device bytes (`out_compile_trim`), and makes
+ * it resident with one lease. `*out_reused` = 1 when no compile ran. The executable belongs to the cache: give the lease
+ * back with pjrtx_b200_executable_cache_release, never pjrtx_b200_executable_destroy. NULL on failure or for a
+ * fingerprint that was never recorded. */
+PjrtxB200Executable *pjrtx_b200_executable_cache_acquire(PjrtxB200ExecutableCache *cache, const char *fingerprint,
+                                                         PjrtxB200Plan *plan, const int32_t *device_ordinals,
+                                                         uint64_t device_count, int *out_reused,
+                                                         PjrtxB200ExecutableCacheTrim *out_compile_trim);
+/* Residency.release (:394-399): returns one lease; idle entries beyond the byte budget are evicted. */
+void pjrtx_b200_executable_cache_release(PjrtxB200ExecutableCache *cache, const char *fingerprint);
+/* Residency.setMaxResidentBytes (:366-371). */
+void pjrtx_b200_executable_cache_set_max_resident_bytes(PjrtxB200ExecutableCache *cache, uint64_t max_resident_bytes);
+/* Residency.trimForAllocation (:374-376, 404-426): `bytes_in_use` = buffer bytes outside the cache. */
+int pjrtx_b200_executable_cache_trim_for_allocation(PjrtxB200ExecutableCache *cache, uint64_t bytes_in_use,
+                                                    uint64_t allocation_bytes, PjrtxB200ExecutableCacheTrim *out);
+/* The capacity that pressure trims work against (the reference's tests set memory.stats.capacity_bytes directly). */
+void pjrtx_b200_executable_cache_set_capacity(PjrtxB200ExecutableCache *cache, uint64_t capacity_bytes);
+/* Residency.statsSnapshot / entrySnapshot (:355-362). entry returns 0 for an unknown fingerprint. */
+int pjrtx_b200_executable_cache_stats(PjrtxB200ExecutableCache *cache, PjrtxB200ExecutableCacheStats *out);
+int pjrtx_b200_executable_cache_entry(PjrtxB200ExecutableCache *cache, const char *fingerprint,
+                                      PjrtxB200ExecutableCacheEntry *out);
+/* Policy-test hooks (the reference's Testing namespaces: setCompileLatencyForTest :167-170, initBorrowedResident):
+ * install_placeholder makes a recorded fingerprint resident with one lease and `resident_bytes` of accounted memory
+ * but no executable behind it, so the eviction policy runs without a device; it returns 1 when the placeholder became
+ * resident, 2 when the fingerprint was resident already (the lease is taken on that entry), 0 on error. */
+int pjrtx_b200_executable_cache_install_placeholder(PjrtxB200ExecutableCache *cache, const char *fingerprint,
+                                                    uint64_t resident_bytes, uint64_t bytes_in_use,
+                                                    PjrtxB200ExecutableCacheTrim *out_compile_trim);
+void pjrtx_b200_executable_cache_set_compile_latency(PjrtxB200ExecutableCache *cache, const char *fingerprint,
+                                                     uint64_t latency_us);
+
 /* ---- StableHLO text ------------------------------------------------------- */
 /* Reads `func.func @main` of a textual StableHLO module into a plan (the subset of operations the backend executes;
  * static shapes; pretty or generic operation syntax). Replaces, for text, the MLIR-based importer

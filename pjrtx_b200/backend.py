@@ -69,6 +69,32 @@ class MemoryStats(ctypes.Structure):
                 ("host_to_device_bytes", ctypes.c_uint64), ("device_to_host_bytes", ctypes.c_uint64)]
 
 
+_CACHE_STATS_FIELDS = ["hits", "misses", "evictions", "evicted_resident_bytes", "resident_entries", "resident_bytes",
+                       "peak_resident_bytes", "largest_resident_bytes", "compile_latency_samples",
+                       "compile_latency_us_total", "compile_latency_us_peak", "pressure_trim_requests",
+                       "pressure_trimmed_bytes", "pressure_trim_failures"]
+
+
+class ExecutableCacheStats(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint64) for n in _CACHE_STATS_FIELDS]
+
+
+class ExecutableCacheTrim(ctypes.Structure):
+    _fields_ = [("requested_bytes", ctypes.c_uint64), ("target_resident_bytes", ctypes.c_uint64),
+                ("freed_bytes", ctypes.c_uint64), ("evicted_entries", ctypes.c_uint64),
+                ("remaining_resident_bytes", ctypes.c_uint64), ("still_over_capacity", ctypes.c_int32)]
+
+    def as_dict(self) -> dict:
+        d = {n: getattr(self, n) for n, _ in self._fields_}
+        d["still_over_capacity"] = bool(d["still_over_capacity"])
+        return d
+
+
+class ExecutableCacheEntry(ctypes.Structure):
+    _fields_ = [("resident", ctypes.c_int32), ("resident_bytes", ctypes.c_uint64), ("reference_count", ctypes.c_uint64),
+                ("compile_latency_us", ctypes.c_uint64)]
+
+
 # Every symbol include/pjrtx_b200.h declares: name -> (restype, argtypes).
 _P = ctypes.c_void_p
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -143,6 +169,21 @@ SYMBOLS = {
     "pjrtx_b200_dot_static_scratch": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _P, _P, _P, ctypes.c_int64, ctypes.c_int64,
                                                       ctypes.c_int64, _P]),
     "pjrtx_b200_compile_check": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint64]),
+    "pjrtx_b200_executable_cache_create": (_P, [ctypes.c_uint64]),
+    "pjrtx_b200_executable_cache_destroy": (None, [_P]),
+    "pjrtx_b200_executable_cache_record_compile": (ctypes.c_int, [_P, ctypes.c_char_p]),
+    "pjrtx_b200_executable_cache_acquire": (_P, [_P, ctypes.c_char_p, _P, ctypes.POINTER(ctypes.c_int32), ctypes.c_uint64,
+                                                 ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ExecutableCacheTrim)]),
+    "pjrtx_b200_executable_cache_release": (None, [_P, ctypes.c_char_p]),
+    "pjrtx_b200_executable_cache_set_max_resident_bytes": (None, [_P, ctypes.c_uint64]),
+    "pjrtx_b200_executable_cache_set_capacity": (None, [_P, ctypes.c_uint64]),
+    "pjrtx_b200_executable_cache_trim_for_allocation": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_uint64,
+                                                                       ctypes.POINTER(ExecutableCacheTrim)]),
+    "pjrtx_b200_executable_cache_stats": (ctypes.c_int, [_P, ctypes.POINTER(ExecutableCacheStats)]),
+    "pjrtx_b200_executable_cache_entry": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.POINTER(ExecutableCacheEntry)]),
+    "pjrtx_b200_executable_cache_install_placeholder": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_uint64, ctypes.c_uint64,
+                                                                        ctypes.POINTER(ExecutableCacheTrim)]),
+    "pjrtx_b200_executable_cache_set_compile_latency": (None, [_P, ctypes.c_char_p, ctypes.c_uint64]),
 }
 
 _lib = None
@@ -249,6 +290,111 @@ class Executable:
     def destroy(self):
         if self.handle:
             self._lib.pjrtx_b200_executable_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class CachedExecutable(Executable):
+    """A lease on a resident executable: `destroy` gives the lease back to the cache instead of freeing the executable."""
+
+    def __init__(self, lib, handle, builder, cache: "ExecutableCache", fingerprint: str, reused: bool, compile_trim: dict):
+        super().__init__(lib, handle, builder)
+        self.cache = cache
+        self.fingerprint = fingerprint
+        self.reused = reused
+        self.compile_trim = compile_trim
+
+    def destroy(self):
+        if self.handle:
+            self.handle = None
+            self.cache.release(self.fingerprint)
+
+
+class ExecutableCache:
+    """Resident executables keyed by plan fingerprint (the reference's `Residency`, src/runtime/executable_cache.zig:
+    333-400, driven the way src/runtime/client_residency_tests.zig drives it)."""
+
+    def __init__(self, backend: "Backend", capacity_bytes: int = 0):
+        self.backend = backend
+        self.lib = backend.lib
+        self.handle = self.lib.pjrtx_b200_executable_cache_create(capacity_bytes)
+        if not self.handle:
+            raise BackendError("OutOfMemory", backend._err())
+
+    def record_compile(self, fingerprint: str) -> bool:
+        r = self.lib.pjrtx_b200_executable_cache_record_compile(self.handle, fingerprint.encode())
+        if r < 0:
+            raise BackendError("InvalidProgram", self.backend._err())
+        return r == 1
+
+    def compile(self, builder: plan_mod.PlanBuilder, devices: Sequence[int] = (0,),
+                fingerprint: Optional[str] = None) -> CachedExecutable:
+        """`recordCompile` + `acquireBackendExecutable`: a resident executable is leased again, otherwise the plan compiles."""
+        plan = builder.build(self.lib)
+        try:
+            fp = fingerprint or _text(self.lib, self.lib.pjrtx_b200_plan_fingerprint, plan)
+            self.record_compile(fp)
+            devs = (ctypes.c_int32 * len(devices))(*devices)
+            reused = ctypes.c_int(0)
+            trim = ExecutableCacheTrim()
+            h = self.lib.pjrtx_b200_executable_cache_acquire(self.handle, fp.encode(), plan, devs, len(devices),
+                                                             ctypes.byref(reused), ctypes.byref(trim))
+            if not h:
+                raise BackendError("InvalidProgram", self.backend._err())
+            return CachedExecutable(self.lib, h, builder, self, fp, bool(reused.value), trim.as_dict())
+        finally:
+            self.lib.pjrtx_b200_plan_destroy(plan)
+
+    def install_placeholder(self, fingerprint: str, resident_bytes: int, bytes_in_use: int = 0):
+        """Policy-test hook: a resident entry with accounted bytes and no executable. Returns (reused, compile trim)."""
+        trim = ExecutableCacheTrim()
+        r = self.lib.pjrtx_b200_executable_cache_install_placeholder(self.handle, fingerprint.encode(), resident_bytes,
+                                                                     bytes_in_use, ctypes.byref(trim))
+        if r == 0:
+            raise BackendError("InvalidProgram", self.backend._err())
+        return r == 2, trim.as_dict()
+
+    def release(self, fingerprint: str) -> None:
+        if self.handle:
+            self.lib.pjrtx_b200_executable_cache_release(self.handle, fingerprint.encode())
+
+    def set_max_resident_bytes(self, max_resident_bytes: int) -> None:
+        self.lib.pjrtx_b200_executable_cache_set_max_resident_bytes(self.handle, max_resident_bytes)
+
+    def set_capacity(self, capacity_bytes: int) -> None:
+        self.lib.pjrtx_b200_executable_cache_set_capacity(self.handle, capacity_bytes)
+
+    def set_compile_latency(self, fingerprint: str, latency_us: int) -> None:
+        self.lib.pjrtx_b200_executable_cache_set_compile_latency(self.handle, fingerprint.encode(), latency_us)
+
+    def trim_for_allocation(self, bytes_in_use: int, allocation_bytes: int) -> dict:
+        trim = ExecutableCacheTrim()
+        if not self.lib.pjrtx_b200_executable_cache_trim_for_allocation(self.handle, bytes_in_use, allocation_bytes,
+                                                                        ctypes.byref(trim)):
+            raise BackendError("InvalidProgram", self.backend._err())
+        return trim.as_dict()
+
+    def stats(self) -> dict:
+        s = ExecutableCacheStats()
+        if not self.lib.pjrtx_b200_executable_cache_stats(self.handle, ctypes.byref(s)):
+            raise BackendError("InvalidProgram", self.backend._err())
+        return {n: getattr(s, n) for n in _CACHE_STATS_FIELDS}
+
+    def entry(self, fingerprint: str) -> Optional[dict]:
+        e = ExecutableCacheEntry()
+        if not self.lib.pjrtx_b200_executable_cache_entry(self.handle, fingerprint.encode(), ctypes.byref(e)):
+            return None
+        return {"resident": bool(e.resident), "resident_bytes": e.resident_bytes, "reference_count": e.reference_count,
+                "compile_latency_us": e.compile_latency_us}
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.lib.pjrtx_b200_executable_cache_destroy(self.handle)
             self.handle = None
 
     def __del__(self):

@@ -6,7 +6,10 @@
 #include <cstring>
 #include <new>
 
+#include <chrono>
+
 #include "device.h"
+#include "executable_cache.h"
 #include "executor.h"
 #include "plan.h"
 #include "program.h"
@@ -23,6 +26,18 @@ struct PjrtxB200Plan {
 };
 struct PjrtxB200Executable {
   Executable* exe;
+};
+struct PjrtxB200ExecutableCache {
+  ExecutableCache cache;
+  uint64_t capacity_bytes;
+  explicit PjrtxB200ExecutableCache(uint64_t capacity)
+      : cache([](void* h) {
+          // Placeholders carry no executable.
+          PjrtxB200Executable* w = static_cast<PjrtxB200Executable*>(h);
+          if (w->exe) destroy_executable(w->exe);
+          delete w;
+        }),
+        capacity_bytes(capacity) {}
 };
 struct PjrtxB200ExecutionEvent {
   int device;
@@ -482,6 +497,154 @@ void pjrtx_b200_executable_destroy(PjrtxB200Executable* executable) {
     if (!executable) return;
     destroy_executable(executable->exe);
     delete executable;
+  } catch (...) {
+  }
+}
+
+// ---- resident-executable cache -------------------------------------------------
+
+namespace {
+
+void fill_trim(const CacheTrim& t, PjrtxB200ExecutableCacheTrim* out) {
+  if (!out) return;
+  out->requested_bytes = t.requested_bytes;
+  out->target_resident_bytes = t.target_resident_bytes;
+  out->freed_bytes = t.freed_bytes;
+  out->evicted_entries = t.evicted_entries;
+  out->remaining_resident_bytes = t.remaining_resident_bytes;
+  out->still_over_capacity = t.still_over_capacity ? 1 : 0;
+}
+
+}  // namespace
+
+PjrtxB200ExecutableCache* pjrtx_b200_executable_cache_create(uint64_t capacity_bytes) {
+  GUARD_PTR(return new PjrtxB200ExecutableCache(capacity_bytes);)
+}
+
+void pjrtx_b200_executable_cache_destroy(PjrtxB200ExecutableCache* cache) {
+  try {
+    delete cache;
+  } catch (...) {
+  }
+}
+
+int pjrtx_b200_executable_cache_record_compile(PjrtxB200ExecutableCache* cache, const char* fingerprint) {
+  try {
+    if (!cache || !fingerprint) {
+      set_last_error("null cache or fingerprint");
+      return -1;
+    }
+    return cache->cache.record_compile(fingerprint) ? 1 : 0;
+  } catch (const std::exception& e) {
+    set_last_error("%s", e.what());
+    return -1;
+  } catch (...) {
+    set_last_error("unknown error");
+    return -1;
+  }
+}
+
+PjrtxB200Executable* pjrtx_b200_executable_cache_acquire(PjrtxB200ExecutableCache* cache, const char* fingerprint,
+                                                         PjrtxB200Plan* plan, const int32_t* device_ordinals,
+                                                         uint64_t device_count, int* out_reused,
+                                                         PjrtxB200ExecutableCacheTrim* out_compile_trim) {
+  GUARD_PTR(
+      if (out_reused) *out_reused = 0; fill_trim(CacheTrim{}, out_compile_trim);
+      if (!cache || !fingerprint || !plan || (device_count && !device_ordinals)) {
+        set_last_error("null cache, fingerprint, plan or device list");
+        return nullptr;
+      } CacheEntrySnapshot snap;
+      if (!cache->cache.entry(fingerprint, &snap)) {
+        set_last_error("fingerprint %s was not recorded", fingerprint);
+        return nullptr;
+      } if (void* h = cache->cache.retain_resident(fingerprint)) {
+        if (out_reused) *out_reused = 1;
+        return static_cast<PjrtxB200Executable*>(h);
+      } std::vector<int> devs(device_ordinals, device_ordinals + device_count);
+      std::string err; auto t0 = std::chrono::steady_clock::now(); Executable* exe = compile_executable(plan->plan, devs, &err);
+      if (!exe) {
+        set_last_error("%s", err.c_str());
+        return nullptr;
+      } const uint64_t latency_us =
+          (uint64_t)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+      ExecutableStats st = executable_stats(exe);
+      const uint64_t resident = st.resident_constant_bytes + st.arena_bytes + st.scratch_bytes;
+      // Buffer bytes outside the cache: the device counts every allocation, the executables' included.
+      uint64_t in_use = 0; if (Device* d = devs.empty() ? nullptr : get_device(devs[0])) {
+        std::lock_guard<std::mutex> lock(d->mu);
+        const uint64_t held = cache->cache.stats().resident_bytes + resident;
+        in_use = d->live_bytes > held ? d->live_bytes - held : 0;
+      } bool reused = false;
+      CacheTrim trim; void* h = cache->cache.install(fingerprint, new PjrtxB200Executable{exe}, resident, latency_us,
+                                                     cache->capacity_bytes, in_use, &reused, &trim);
+      if (out_reused) *out_reused = reused ? 1 : 0; fill_trim(trim, out_compile_trim);
+      return static_cast<PjrtxB200Executable*>(h);)
+}
+
+void pjrtx_b200_executable_cache_release(PjrtxB200ExecutableCache* cache, const char* fingerprint) {
+  try {
+    if (cache && fingerprint) cache->cache.release(fingerprint);
+  } catch (...) {
+  }
+}
+
+void pjrtx_b200_executable_cache_set_max_resident_bytes(PjrtxB200ExecutableCache* cache, uint64_t max_resident_bytes) {
+  try {
+    if (cache) cache->cache.set_max_resident_bytes(max_resident_bytes);
+  } catch (...) {
+  }
+}
+
+void pjrtx_b200_executable_cache_set_capacity(PjrtxB200ExecutableCache* cache, uint64_t capacity_bytes) {
+  if (cache) cache->capacity_bytes = capacity_bytes;
+}
+
+int pjrtx_b200_executable_cache_trim_for_allocation(PjrtxB200ExecutableCache* cache, uint64_t bytes_in_use,
+                                                    uint64_t allocation_bytes, PjrtxB200ExecutableCacheTrim* out) {
+  GUARD_INT(if (!cache) return 0;
+            fill_trim(cache->cache.trim_for_allocation(cache->capacity_bytes, bytes_in_use, allocation_bytes), out); return 1;)
+}
+
+int pjrtx_b200_executable_cache_stats(PjrtxB200ExecutableCache* cache, PjrtxB200ExecutableCacheStats* out) {
+  GUARD_INT(if (!cache || !out) return 0; CacheStats s = cache->cache.stats(); out->hits = s.hits; out->misses = s.misses;
+            out->evictions = s.evictions; out->evicted_resident_bytes = s.evicted_resident_bytes;
+            out->resident_entries = s.resident_entries; out->resident_bytes = s.resident_bytes;
+            out->peak_resident_bytes = s.peak_resident_bytes; out->largest_resident_bytes = s.largest_resident_bytes;
+            out->compile_latency_samples = s.compile_latency_samples; out->compile_latency_us_total = s.compile_latency_us_total;
+            out->compile_latency_us_peak = s.compile_latency_us_peak; out->pressure_trim_requests = s.pressure_trim_requests;
+            out->pressure_trimmed_bytes = s.pressure_trimmed_bytes; out->pressure_trim_failures = s.pressure_trim_failures;
+            return 1;)
+}
+
+int pjrtx_b200_executable_cache_entry(PjrtxB200ExecutableCache* cache, const char* fingerprint,
+                                      PjrtxB200ExecutableCacheEntry* out) {
+  GUARD_INT(if (!cache || !fingerprint) return 0; CacheEntrySnapshot s; if (!cache->cache.entry(fingerprint, &s)) return 0;
+            if (out) {
+              out->resident = s.resident ? 1 : 0;
+              out->resident_bytes = s.resident_bytes;
+              out->reference_count = s.reference_count;
+              out->compile_latency_us = s.compile_latency_us;
+            } return 1;)
+}
+
+int pjrtx_b200_executable_cache_install_placeholder(PjrtxB200ExecutableCache* cache, const char* fingerprint,
+                                                    uint64_t resident_bytes, uint64_t bytes_in_use,
+                                                    PjrtxB200ExecutableCacheTrim* out_compile_trim) {
+  GUARD_INT(fill_trim(CacheTrim{}, out_compile_trim); if (!cache || !fingerprint) return 0;
+            if (cache->cache.retain_resident(fingerprint)) return 2;
+            bool reused = false; CacheTrim trim;
+            void* h = cache->cache.install(fingerprint, new PjrtxB200Executable{nullptr}, resident_bytes, 0,
+                                           cache->capacity_bytes, bytes_in_use, &reused, &trim);
+            fill_trim(trim, out_compile_trim); if (!h) {
+              set_last_error("fingerprint %s was not recorded", fingerprint);
+              return 0;
+            } return reused ? 2 : 1;)
+}
+
+void pjrtx_b200_executable_cache_set_compile_latency(PjrtxB200ExecutableCache* cache, const char* fingerprint,
+                                                     uint64_t latency_us) {
+  try {
+    if (cache && fingerprint) cache->cache.set_compile_latency(fingerprint, latency_us);
   } catch (...) {
   }
 }

@@ -166,20 +166,20 @@ __device__ __forceinline__ void merge_splits(const DecodeArgs& a, long long tile
 //      threads are plain partial sums; they are rescaled once per chunk when the running maximum moves.
 // After the last chunk the partial sums are added across the CTA, and (max, sum, out) goes to the workspace; the CTA
 // that arrives last for the (sequence, KV head) merges the splits in split order.
-template <typename T, int REP, int HD, int KPG>
-__global__ void __launch_bounds__(kWarps * 32)
+template <typename T, int REP, int HD, int KPG, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                    const void* __restrict__ token, T* __restrict__ out) {
   PJRTX_PDL_PROLOGUE();
   constexpr int V = Elem<T>::V;
   constexpr int LPK = HD / V;                  // lanes per key row
   constexpr int GPW = 32 / LPK;                // lane groups per warp
-  constexpr int GROUPS = kWarps * GPW;         // lane groups per CTA
+  constexpr int GROUPS = WARPS * GPW;         // lane groups per CTA
   constexpr int CHUNK = GROUPS * KPG;          // keys per chunk
   static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "head_dim must give a power-of-two lane group");
-  __shared__ float sm_max[2][kWarps][REP];     // double-buffered: one barrier per chunk
-  __shared__ float sm_l[kWarps][REP];
-  __shared__ float sm_o[kWarps][REP][HD];
+  __shared__ float sm_max[2][WARPS][REP];     // double-buffered: one barrier per chunk
+  __shared__ float sm_l[WARPS][REP];
+  __shared__ float sm_o[WARPS][REP][HD];
   __shared__ int is_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -256,7 +256,7 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
     for (int r = 0; r < REP; r++) {
       float m_new = m_run[r];
 #pragma unroll
-      for (int w = 0; w < kWarps; w++) m_new = fmaxf(m_new, sm_max[parity][w][r]);
+      for (int w = 0; w < WARPS; w++) m_new = fmaxf(m_new, sm_max[parity][w][r]);
       if (m_new != m_run[r]) {  // uniform over the CTA
         const float corr = m_run[r] == -INFINITY ? 0.f : __expf(m_run[r] - m_new);
         l[r] *= corr;
@@ -296,11 +296,11 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
   __syncthreads();
   const long long tile = (long long)b * a.kv_heads + g;
   float* ws = a.workspace + (tile * a.splits + split) * (long long)REP * (HD + 2);
-  for (int idx = threadIdx.x; idx < REP * HD; idx += kWarps * 32) {
+  for (int idx = threadIdx.x; idx < REP * HD; idx += WARPS * 32) {
     const int r = idx / HD, d = idx % HD;
     float oo = 0.f, ll = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWarps; w++) {
+    for (int w = 0; w < WARPS; w++) {
       oo += sm_o[w][r][d];
       ll += sm_l[w][r];
     }
@@ -315,7 +315,7 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
     }
   }
   if (a.splits == 1) return;
-  merge_splits<T, REP, HD, kWarps * 32>(a, tile, b, g, &sm_o[0][0][0], &is_last, out);
+  merge_splits<T, REP, HD, WARPS * 32>(a, tile, b, g, &sm_o[0][0][0], &is_last, out);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -614,13 +614,18 @@ int dispatch_decode_mma(int rep, int hd, const DecodeArgs& a, dim3 grid, const v
   return 0;
 }
 
-// Keys per lane group and chunk: eight while the scores of all heads still fit in registers, four beyond.
-template <int REP> struct KeysPerGroup { static constexpr int value = REP <= 4 ? 8 : 4; };
+// Shape of a CTA: up to four heads per KV head run sixteen warps with four keys per lane group and chunk (the kernel
+// is bound by the length of each thread's dependent instruction chain, so the work of a chunk is spread over more
+// threads); eight heads keep eight warps (their registers would not fit sixteen). Either way a chunk is
+// WARPS * (32 / lanes per key) * KPG keys.
+template <int REP> struct KeysPerGroup { static constexpr int value = 4; };
+template <int REP> struct WarpsPerCta { static constexpr int value = REP <= 4 ? 16 : 8; };
 
 template <typename T, int REP, int HD>
 int launch_decode(const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out, bool pdl,
                   cudaStream_t stream) {
-  return launch_kernel(attn_decode_kernel<T, REP, HD, KeysPerGroup<REP>::value>, grid, dim3(kWarps * 32), 0, stream, pdl, a, (const T*)q, (const T*)k,
+  return launch_kernel(attn_decode_kernel<T, REP, HD, KeysPerGroup<REP>::value, WarpsPerCta<REP>::value>, grid,
+                       dim3(WarpsPerCta<REP>::value * 32), 0, stream, pdl, a, (const T*)q, (const T*)k,
                        (const T*)v, token, (T*)out) == cudaSuccess
              ? 1
              : 0;
@@ -673,7 +678,7 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   }
   // Keys one CTA handles per chunk (see the kernel): no split should be shorter than that.
   const long long lanes_per_key = s.head_dim * (long long)dtype_size(s.dtype) / 16;
-  const long long chunk = kWarps * (32 / lanes_per_key) * (rep <= 4 ? 8 : 4);
+  const long long chunk = (rep <= 4 ? 16 : 8) * (32 / lanes_per_key) * 4;
   // About four CTAs per SM in total, so that the tail of the last wave is short next to the whole.
   long long want = (4ll * sm_count + tiles - 1) / tiles;
   long long max_splits = std::max<long long>(1, s.kv_len / chunk);

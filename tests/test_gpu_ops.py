@@ -355,3 +355,42 @@ def test_decode_attention_every_visible_length(gpu_backend, monkeypatch, kernel,
             want = run_oracle(b, [q, k, v, np.array(token, np.int32)])[0]
             assert_close(got, want, 1e-5 if dtype == P.F32 else 2e-2, what=f"{kernel} token {token}")
         assert np.isfinite(got.astype(np.float32)).all()
+
+
+def test_executable_cache_compiles_reuses_and_evicts(gpu_backend):
+    """src/runtime/client_residency_tests.zig:184-267 with real executables: the second compile of a fingerprint leases
+    the resident executable (same handle, no compile), an idle executable over the byte budget is destroyed and its
+    device memory returned, and the fingerprint compiles again afterwards with the same results."""
+    be = gpu_backend
+    cache = be_mod.ExecutableCache(be)
+    b, _ = cases.u8_chain()
+    lhs = be.buffer_from_host(np.array([1, 2, 3, 4], np.uint8))
+    first = cache.compile(b, [0])
+    assert not first.reused and first.fingerprint == be.plan_fingerprint(b)
+    e = cache.entry(first.fingerprint)
+    assert e["resident"] and e["reference_count"] == 1 and e["resident_bytes"] >= 4 and e["compile_latency_us"] > 0
+    second = cache.compile(b, [0])
+    assert second.reused and second.handle == first.handle
+    s = cache.stats()
+    assert (s["misses"], s["hits"], s["resident_entries"], s["compile_latency_samples"]) == (1, 1, 1, 1)
+    assert cache.entry(first.fingerprint)["reference_count"] == 2
+    assert be.execute_executable(second, [lhs])[0].to_numpy().tolist() == [6, 15, 28, 45]
+    assert first.stats()["execute_count"] == 1                  # one executable behind both leases
+    second.destroy()
+    first.destroy()
+    e = cache.entry(first.fingerprint)
+    assert e["resident"] and e["reference_count"] == 0
+    held = be.memory_stats()["bytes_in_use"]
+    cache.set_max_resident_bytes(0)
+    e2 = cache.entry(first.fingerprint)
+    assert not e2["resident"]
+    assert be.memory_stats()["bytes_in_use"] <= held - e["resident_bytes"]
+    s = cache.stats()
+    assert (s["evictions"], s["evicted_resident_bytes"], s["resident_bytes"]) == (1, e["resident_bytes"], 0)
+    third = cache.compile(b, [0])
+    assert not third.reused
+    assert be.execute_executable(third, [lhs])[0].to_numpy().tolist() == [6, 15, 28, 45]
+    third.destroy()                                               # budget 0: evicted as soon as it is idle
+    assert not cache.entry(first.fingerprint)["resident"]
+    assert cache.stats()["evictions"] == 2
+    cache.destroy()
