@@ -369,6 +369,92 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """`--workload prefill`: the 8B-shape prefill (batch 4 x 2048 tokens, uniform ids, LM head on the last position)
+    on one GPU. Not the headline line: it reports the compute-bound half of the path with a tensor-pipe roofline."""
+    import pjrtx_b200
+
+    be = pjrtx_b200.Backend()
+    device = 0
+    be.enumerate_devices()
+    cfg, batch, seq = llama.LLAMA3_8B, 4, 2048
+    workload = f"llama3-8b-shape bf16 prefill batch {batch} x seq {seq}"
+    if args.layers:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, layers=args.layers)
+        workload += f" (truncated to {args.layers} layers)"
+    builder, names = llama.build_prefill(cfg, batch, seq)
+    t0 = time.time()
+    exe = be.compile_executable(builder, [device])
+    compile_s = time.time() - t0
+    table = param_table(cfg, builder, names, 1)
+    gen = make_device_weights(be, cfg, names[1:], table, device, 0, 1)
+    weights = [reshape_buffer(be, buf, dims, device) for buf, dims in gen]
+    tokens = be.buffer_from_host(np.random.default_rng(2).integers(0, cfg.vocab, size=(batch, seq), dtype=np.int32), device)
+    be.synchronize(device)
+
+    def step():
+        outs = be.execute_executable(exe, [tokens] + weights)
+        for o in outs[1:]:
+            o.destroy()  # the KV caches of this pass
+        return outs[0]
+
+    for _ in range(args.warmup):
+        step()
+    be.synchronize(device)
+    launches0 = exe.stats()["kernel_launch_total"]
+    sampler = ClockSampler(device)
+    if not os.environ.get("PJRTX_BENCH_NO_SAMPLER"):
+        sampler.start()
+    start = be.record_event(device)
+    for _ in range(args.steps):
+        step()
+    stop = be.record_event(device)
+    ms = be.elapsed_ms(start, stop)
+    be.synchronize(device)
+    clocks = sampler.stop()
+    launches = exe.stats()["kernel_launch_total"] - launches0
+    exe.set_profiling(True)
+    step()
+    times = exe.step_times_ms()
+    exe.set_profiling(False)
+    per_type = {}
+    for st, t in zip(exe.describe()["kernel_plan"]["steps"], times):
+        label = st["type"] + (f"/path{st['path']}{'/umma' if st.get('umma') else ''}" if st["type"] == "dot" else ("/row" if st.get("row") else ""))
+        per_type.setdefault(label, [0, 0.0])
+        per_type[label][0] += 1
+        per_type[label][1] += float(t)
+    tokens_n = batch * seq
+    per_layer = cfg.d_model * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.d_model + 3 * cfg.d_model * cfg.ffn
+    linear = 2.0 * cfg.layers * per_layer * tokens_n + 2.0 * cfg.d_model * cfg.vocab * batch
+    attention = cfg.layers * 2 * (2.0 * batch * cfg.heads * seq * seq * cfg.head_dim)  # the full S x S square, as written
+    flops = linear + attention
+    step_ms = ms / args.steps
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    peak_kind = "measured (sustained)" if "bf16_tflops_sustained" in peaks else "fallback"
+    achieved = flops / (step_ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "prefill tok/s + % tensor roofline: 8B-shape on 1 GPU", "value": tokens_n / (step_ms * 1e-3), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload, "batch": batch, "seq": seq, "layers": cfg.layers,
+                   "l2": "weights and activations exceed L2; no flush needed", "lm_head": "last position only"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "algorithmic_flops": flops,
+                     "linear_flops": linear, "attention_flops_full_square": attention, "kernel": "whole step"},
+        "clocks": clocks,
+        "kernel_time_ms_per_step": {k: {"launches": v[0], "ms": round(v[1], 4)} for k, v in sorted(per_type.items())},
+        "compile_s": round(compile_s, 2),
+    }))
+
+
 def cpu_baseline(cfg, batch, filled, budget_layers=2, steps=2):
     """Times the CPU plan interpreter (float32 BLAS contractions, all host threads) on a truncated copy of the
     workload: `budget_layers` decoder layers plus the full LM head, then scales the layer time to the full depth."""
@@ -440,11 +526,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences decoded together on one GPU (1 = the headline workload; 16 and 32 are the batched-decode configs)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode = the headline line; prefill = 8B-shape batch 4 x 2048 on one GPU (give it --steps 5)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 

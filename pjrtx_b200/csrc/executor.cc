@@ -348,7 +348,9 @@ bool lowering_issue(const Plan& plan, size_t device_count, Issue* out) {
       }
       case Kind::custom_call: {
         SdpaShape s;
-        if (ins.custom_call_target == "pjrtx.b200.internal.attention_decode") break;
+        if (ins.custom_call_target == "pjrtx.b200.internal.attention_decode" ||
+            ins.custom_call_target == "pjrtx.b200.internal.attention_prefill")
+          break;
         if (is_sdpa_target(ins.custom_call_target)) {
           if (!analyze_sdpa(plan, ins, &s, &why)) {
             *out = Issue{(long)i, -1, why, ins.custom_call_target};
@@ -391,17 +393,41 @@ bool lowering_issue(const Plan& plan, size_t device_count, Issue* out) {
 // exp(. - max) -> sum -> / sum -> [convert] -> dot_general(., V) becomes one internal attention call, so the split-KV
 // kernel reads the cache once instead of three kernels round-tripping scores and probabilities through memory.
 // Anything that deviates from this exact dataflow is left alone and runs as separate steps.
+//
+// The same chain one rank higher is causal self-attention over whole sequences (prefill): q [B, G, S, rep, hd],
+// K / V [B, S, G, hd], scores [B, G, S, rep, S'], mask = iota(key axis) <= iota(position axis). It becomes the
+// prefill attention call, which keeps scores and probabilities on the SM.
 
 const char* kAttnDecodeTarget = "pjrtx.b200.internal.attention_decode";
+const char* kAttnPrefillTarget = "pjrtx.b200.internal.attention_prefill";
 
 struct AttnMatch {
   size_t d1 = 0, d2 = 0;
   std::vector<size_t> consumed;
   uint32_t q = 0, k = 0, v = 0, pos = 0, out = 0;
   float scale = 1.f;
+  bool prefill = false;
 };
 
+AttnPrefillShape prefill_shape(const Value& q, const Value& k, float scale) {
+  AttnPrefillShape s;
+  s.dtype = q.dtype;
+  s.batch = q.dims[0];
+  s.kv_heads = q.dims[1];
+  s.seq = q.dims[2];
+  s.rep = q.dims[3];
+  s.head_dim = q.dims[4];
+  s.kv_batch_stride = k.dims[1] * k.dims[2] * k.dims[3];
+  s.kv_row_stride = k.dims[2] * k.dims[3];
+  s.kv_head_stride = k.dims[3];
+  s.round_scores = 1;
+  s.scale = scale;
+  return s;
+}
+
 void fuse_decode_attention(Plan* plan) {
+  const char* prefill_env = getenv("PJRTX_B200_ATTENTION_PREFILL");
+  const bool prefill_enabled = !(prefill_env && prefill_env[0] == '0');
   const size_t nv = plan->values.size();
   std::vector<long> producer(nv, -1);
   std::vector<std::vector<size_t>> users(nv);
@@ -442,17 +468,21 @@ void fuse_decode_attention(Plan* plan) {
     if (d1.kind != Kind::dot_general || d1.inputs.size() != 2) continue;
     const Value& q = plan->values[d1.inputs[0]];
     const Value& k = plan->values[d1.inputs[1]];
-    if (q.dims.size() != 4 || k.dims.size() != 4 || !dtype_is_float(q.dtype)) continue;
+    if ((q.dims.size() != 4 && q.dims.size() != 5) || k.dims.size() != 4 || !dtype_is_float(q.dtype)) continue;
+    const bool prefill = q.dims.size() == 5;
+    if (prefill && !prefill_enabled) continue;
+    const int64_t key_axis = prefill ? 4 : 3;  // of the scores
+    const std::vector<int64_t> lead = prefill ? std::vector<int64_t>{0, 1, 2, 3} : std::vector<int64_t>{0, 1, 2};
     if (!is_list(d1.list("lhs_batch_dimensions"), {0, 1}) || !is_list(d1.list("rhs_batch_dimensions"), {0, 2}) ||
-        !is_list(d1.list("lhs_contracting_dimensions"), {3}) || !is_list(d1.list("rhs_contracting_dimensions"), {3}))
+        !is_list(d1.list("lhs_contracting_dimensions"), {key_axis}) || !is_list(d1.list("rhs_contracting_dimensions"), {3}))
       continue;
     AttnMatch m;
+    m.prefill = prefill;
     m.d1 = i;
     m.q = d1.inputs[0];
     m.k = d1.inputs[1];
     m.consumed.push_back(i);
     uint32_t x = d1.outputs[0];
-    const std::vector<int64_t> sdims = plan->values[x].dims;  // [B, G, rep, S]
     long u = sole_user(x);
     if (u < 0) continue;
     const Instruction* n = &plan->instructions[u];
@@ -479,11 +509,18 @@ void fuse_decode_attention(Plan* plan) {
       if (!cmp || cmp->kind != Kind::compare || cmp->scalar("compare_direction", -1) != (int64_t)CompareOp::le) continue;
       const Instruction* io = ins_of(cmp->inputs[0]);
       const Instruction* pb = ins_of(cmp->inputs[1]);
-      if (!io || io->kind != Kind::iota || io->scalar("iota_dimension", -1) != 3) continue;
-      if (!pb || pb->kind != Kind::broadcast_in_dim || plan->values[pb->inputs[0]].count() != 1 ||
-          !plan->values[pb->inputs[0]].dims.empty() || !dtype_is_int(plan->values[pb->inputs[0]].dtype))
-        continue;
-      m.pos = pb->inputs[0];
+      if (!io || io->kind != Kind::iota || io->scalar("iota_dimension", -1) != key_axis) continue;
+      if (prefill) {  // key index <= position index
+        if (!pb || pb->kind != Kind::iota || pb->scalar("iota_dimension", -1) != 2) continue;
+        if (plan->values[io->outputs[0]].dims != plan->values[x].dims || plan->values[pb->outputs[0]].dims != plan->values[x].dims ||
+            !dtype_is_int(plan->values[io->outputs[0]].dtype) || plan->values[io->outputs[0]].dtype != plan->values[pb->outputs[0]].dtype)
+          continue;
+      } else {
+        if (!pb || pb->kind != Kind::broadcast_in_dim || plan->values[pb->inputs[0]].count() != 1 ||
+            !plan->values[pb->inputs[0]].dims.empty() || !dtype_is_int(plan->values[pb->inputs[0]].dtype))
+          continue;
+        m.pos = pb->inputs[0];
+      }
     }
     m.consumed.push_back(u);
     x = n->outputs[0];
@@ -492,14 +529,14 @@ void fuse_decode_attention(Plan* plan) {
     long rmax = -1, sub = -1;
     for (size_t w : users[x]) {
       const Instruction& c = plan->instructions[w];
-      if (c.kind == Kind::reduce_max && c.outputs.size() == 1 && is_list(c.list("reduce_dimensions"), {3})) rmax = (long)w;
+      if (c.kind == Kind::reduce_max && c.outputs.size() == 1 && is_list(c.list("reduce_dimensions"), {key_axis})) rmax = (long)w;
       if (c.kind == Kind::subtract && c.inputs[0] == x) sub = (long)w;
     }
     if (rmax < 0 || sub < 0) continue;
     {
       const Instruction* bm = ins_of(plan->instructions[sub].inputs[1]);
       if (!bm || bm->kind != Kind::broadcast_in_dim || bm->inputs[0] != plan->instructions[rmax].outputs[0] ||
-          !is_list(bm->list("broadcast_dimensions"), {0, 1, 2}) || sole_user(plan->instructions[rmax].outputs[0]) != producer[bm->outputs[0]] ||
+          bm->list("broadcast_dimensions") != lead || sole_user(plan->instructions[rmax].outputs[0]) != producer[bm->outputs[0]] ||
           sole_user(bm->outputs[0]) != sub)
         continue;
       m.consumed.push_back(rmax);
@@ -514,14 +551,14 @@ void fuse_decode_attention(Plan* plan) {
     long rsum = -1, div = -1;
     for (size_t w : users[x]) {
       const Instruction& c = plan->instructions[w];
-      if (c.kind == Kind::reduce_sum && is_list(c.list("reduce_dimensions"), {3})) rsum = (long)w;
+      if (c.kind == Kind::reduce_sum && is_list(c.list("reduce_dimensions"), {key_axis})) rsum = (long)w;
       if (c.kind == Kind::divide && c.inputs[0] == x) div = (long)w;
     }
     if (rsum < 0 || div < 0) continue;
     {
       const Instruction* bz = ins_of(plan->instructions[div].inputs[1]);
       if (!bz || bz->kind != Kind::broadcast_in_dim || bz->inputs[0] != plan->instructions[rsum].outputs[0] ||
-          !is_list(bz->list("broadcast_dimensions"), {0, 1, 2}) || sole_user(plan->instructions[rsum].outputs[0]) != producer[bz->outputs[0]] ||
+          bz->list("broadcast_dimensions") != lead || sole_user(plan->instructions[rsum].outputs[0]) != producer[bz->outputs[0]] ||
           sole_user(bz->outputs[0]) != div)
         continue;
       m.consumed.push_back(rsum);
@@ -539,15 +576,27 @@ void fuse_decode_attention(Plan* plan) {
     }
     if (n->kind != Kind::dot_general || n->inputs[0] != x) continue;
     if (!is_list(n->list("lhs_batch_dimensions"), {0, 1}) || !is_list(n->list("rhs_batch_dimensions"), {0, 2}) ||
-        !is_list(n->list("lhs_contracting_dimensions"), {3}) || !is_list(n->list("rhs_contracting_dimensions"), {1}))
+        !is_list(n->list("lhs_contracting_dimensions"), {key_axis}) || !is_list(n->list("rhs_contracting_dimensions"), {1}))
       continue;
     const Value& vv = plan->values[n->inputs[1]];
     if (vv.dims != k.dims || vv.dtype != q.dtype || k.dtype != q.dtype || plan->values[x].dtype != q.dtype) continue;
-    if (producer[n->inputs[1]] > (long)i || producer[m.pos] > (long)i) continue;  // every input exists before the first dot
+    if (producer[n->inputs[1]] > (long)i || (!prefill && producer[m.pos] > (long)i)) continue;  // every input exists before the first dot
     m.d2 = (size_t)u;
     m.v = n->inputs[1];
     m.out = n->outputs[0];
     m.consumed.push_back(u);
+    if (prefill) {
+      // q [B, G, S, rep, hd], k / v [B, S, G, hd]; the kernel must support the shape.
+      if (k.dims[0] != q.dims[0] || k.dims[2] != q.dims[1] || k.dims[1] != q.dims[2] || k.dims[3] != q.dims[4] ||
+          !attn_prefill_supported(prefill_shape(q, k, 1.f)))
+        continue;
+      bool clash = false;
+      for (size_t c : m.consumed) clash |= taken[c] != 0;
+      if (clash) continue;
+      for (size_t c : m.consumed) taken[c] = 1;
+      matches.push_back(m);
+      continue;
+    }
     // The split-KV kernel must support the shape.
     AttnDecodeShape shape;
     shape.dtype = q.dtype;
@@ -575,8 +624,9 @@ void fuse_decode_attention(Plan* plan) {
     erase[m.d1] = 0;
     Instruction call;
     call.kind = Kind::custom_call;
-    call.custom_call_target = kAttnDecodeTarget;
+    call.custom_call_target = m.prefill ? kAttnPrefillTarget : kAttnDecodeTarget;
     call.inputs = {m.q, m.k, m.v, m.pos};
+    if (m.prefill) call.inputs.pop_back();
     call.outputs = {m.out};
     uint32_t bits;
     memcpy(&bits, &m.scale, 4);
@@ -861,7 +911,17 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
         for (uint32_t v : ins.inputs) st.inputs.push_back(kp->root[v]);
         st.outputs = {ins.outputs[0]};
         AttnDecodeShape& ad = st.attn;
-        if (ins.custom_call_target == kAttnDecodeTarget) {
+        if (ins.custom_call_target == kAttnPrefillTarget) {
+          float scale;
+          uint32_t bits = (uint32_t)ins.scalar("scale_bits", 0);
+          memcpy(&scale, &bits, 4);
+          st.attn_prefill = prefill_shape(plan.values[ins.inputs[0]], plan.values[ins.inputs[1]], scale);
+          if (!attn_prefill_supported(st.attn_prefill)) {
+            *error = format_issue(plan, Issue{(long)i, -1, "internal attention call has an unsupported shape", "b200-attention"});
+            return false;
+          }
+          st.type = Step::kAttnPrefill;
+        } else if (ins.custom_call_target == kAttnDecodeTarget) {
           const Value& q = plan.values[ins.inputs[0]];
           const Value& k = plan.values[ins.inputs[1]];
           ad.dtype = q.dtype;
@@ -1042,7 +1102,8 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
 }
 
 std::string step_type_name(Step::Type t) {
-  static const char* names[] = {"fused", "dot", "slice_update", "sdpa", "all_reduce", "all_gather", "copy", "attention_decode"};
+  static const char* names[] = {"fused", "dot", "slice_update", "sdpa", "all_reduce", "all_gather", "copy", "attention_decode",
+                                "attention_prefill"};
   return names[(int)t];
 }
 
@@ -1084,6 +1145,9 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
     } else if (st.type == Step::kAttnDecode) {
       s += strfmt(",\"mma\":%d,\"splits\":%d,\"batch\":%lld,\"heads\":%lld,\"kv_heads\":%lld,\"kv_len\":%lld,\"head_dim\":%lld",
                   st.attn_plan.mma, st.attn_plan.splits, st.attn.batch, st.attn.heads, st.attn.kv_heads, st.attn.kv_len, st.attn.head_dim);
+    } else if (st.type == Step::kAttnPrefill) {
+      s += strfmt(",\"batch\":%lld,\"kv_heads\":%lld,\"rep\":%lld,\"seq\":%lld,\"head_dim\":%lld", st.attn_prefill.batch,
+                  st.attn_prefill.kv_heads, st.attn_prefill.rep, st.attn_prefill.seq, st.attn_prefill.head_dim);
     }
     s += "}";
   }
@@ -1268,6 +1332,14 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         if (!attn_decode_launch(st.attn, st.attn_plan, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]),
                                 ptr.of(st.inputs[3]), ptr.of(st.outputs[0]), (char*)ds.scratch + st.scratch_offset,
                                 (char*)ds.scratch + st.counter_offset, exe->pdl, dev->stream)) {
+          *error = "attention kernel refused the shape";
+          return false;
+        }
+        (*launches)++;
+        break;
+      case Step::kAttnPrefill:
+        if (!attn_prefill_launch(st.attn_prefill, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]),
+                                 ptr.of(st.outputs[0]), exe->pdl, dev->stream)) {
           *error = "attention kernel refused the shape";
           return false;
         }

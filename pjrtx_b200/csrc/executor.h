@@ -50,7 +50,7 @@ struct ExecutableStats {
 };
 
 struct Step {
-  enum Type { kFused, kDot, kSliceUpdate, kSdpa, kAllReduce, kAllGather, kCopy, kAttnDecode } type = kFused;
+  enum Type { kFused, kDot, kSliceUpdate, kSdpa, kAllReduce, kAllGather, kCopy, kAttnDecode, kAttnPrefill } type = kFused;
   std::vector<size_t> nodes;        // plan instructions this step covers
   std::vector<uint32_t> inputs;     // root values read
   std::vector<uint32_t> outputs;    // root values written
@@ -66,6 +66,7 @@ struct Step {
   SdpaShape sdpa;
   AttnDecodeShape attn;
   AttnDecodePlan attn_plan;
+  AttnPrefillShape attn_prefill;
   uint64_t bytes = 0;  // kCopy / collectives
   uint64_t count = 0;
   int dtype = 0;

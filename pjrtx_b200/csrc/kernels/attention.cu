@@ -614,12 +614,12 @@ int dispatch_decode_mma(int rep, int hd, const DecodeArgs& a, dim3 grid, const v
   return 0;
 }
 
-// Shape of a CTA: up to four heads per KV head run sixteen warps with four keys per lane group and chunk (the kernel
-// is bound by the length of each thread's dependent instruction chain, so the work of a chunk is spread over more
-// threads); eight heads keep eight warps (their registers would not fit sixteen). Either way a chunk is
-// WARPS * (32 / lanes per key) * KPG keys.
-template <int REP> struct KeysPerGroup { static constexpr int value = 4; };
-template <int REP> struct WarpsPerCta { static constexpr int value = REP <= 4 ? 16 : 8; };
+// Shape of a CTA: eight warps; eight keys per lane group and chunk while the scores of all heads still fit in
+// registers, four beyond. A chunk is WARPS * (32 / lanes per key) * KPG keys. Sixteen warps with four keys each
+// (same chunk, half the instruction stream per thread) measured slower at batch 1: 0.77 instead of 0.68 ms for the 32
+// launches of an 8B-shape step (the kernel then spills at 128 registers).
+template <int REP> struct KeysPerGroup { static constexpr int value = REP <= 4 ? 8 : 4; };
+template <int REP> struct WarpsPerCta { static constexpr int value = 8; };
 
 template <typename T, int REP, int HD>
 int launch_decode(const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out, bool pdl,
@@ -639,6 +639,220 @@ int dispatch_decode(int rep, int hd, const DecodeArgs& a, dim3 grid, const void*
   CASE(1, 128) CASE(2, 128) CASE(4, 128) CASE(8, 128) CASE(1, 64) CASE(2, 64) CASE(4, 64) CASE(8, 64)
 #undef CASE
   return 0;
+}
+
+
+// ---- Causal self-attention over whole sequences (prefill) ---------------------------------------------------------
+//
+// out[b, g, s, r, :] = softmax_j( q[b, g, s, r, :] . k[b, j, g, :] * scale  for j <= s ) . v[b, j, g, :]
+//
+// q and out are [batch, kv_heads, seq, rep, head_dim] (the operand and result layout of the recognised
+// dot_general -> masked softmax -> dot_general form), so the `seq * rep` query rows that share one KV head are one
+// contiguous row-major matrix; row `x` belongs to position x / rep. One CTA (4 warps) owns 64 consecutive rows and
+// walks the keys 0..(its last position) in stages of 64 through the same cp.async ring and swizzled layout as the
+// decode kernel above; every warp owns 16 rows and multiplies them with all 64 keys of a stage:
+//   S[16 x 64] = Q[16 x HD] . K^T (mma.m16n8k16, Q fragments in registers), mask key <= position, online softmax on
+//   the fragments, O[16 x HD] += P[16 x 64] . V with the rounded probabilities as A fragments.
+// Scores and probabilities never leave the SM (the explicit form writes and re-reads batch*heads*seq*seq elements
+// twice per layer). Row tiles are scheduled longest first (the last rows see the most keys), and a warp skips the
+// stages that lie wholly above its rows' diagonal.
+struct PrefillArgs {
+  long long seq = 0, rows = 0;  // rows = seq * rep per (sequence, KV head)
+  int rep = 1, kv_heads = 1;
+  long long kv_batch_stride = 0, kv_row_stride = 0, kv_head_stride = 0;
+  float scale = 1.f;
+  int round_scores = 0;
+};
+constexpr int kPrefillRows = 16 * kMmaWarps;
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                        T* __restrict__ out) {
+  static_assert(sizeof(T) == 2 && (HD == 64 || HD == 128), "16-bit elements, head_dim 64 or 128");
+  constexpr int THREADS = kMmaWarps * 32;
+  constexpr int CPR = HD / 8;
+  constexpr int TILE_BYTES = kMmaStageKeys * HD * 2;
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  extern __shared__ __align__(1024) unsigned char smem_attn[];
+  PJRTX_PDL_PROLOGUE();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = blockIdx.y, b = blockIdx.z;
+  const long long tile_row0 = (long long)(gridDim.x - 1 - blockIdx.x) * kPrefillRows;  // longest tiles first
+  const long long last_row = min(tile_row0 + kPrefillRows, a.rows) - 1;
+  const long long j_end = last_row / a.rep + 1;  // keys 0 .. last position of the tile
+  const int stages_total = (int)((j_end + kMmaStageKeys - 1) / kMmaStageKeys);
+
+  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride;
+  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride;
+  const long long bg = ((long long)b * a.kv_heads + g) * a.rows;
+  const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_attn);
+  auto tile_offset = [](int row, int c) { return (unsigned)((c >> 3) * (kMmaStageKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)); };
+  auto issue_stage = [&](int st) {
+    const unsigned dst = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
+    const long long j0 = (long long)st * kMmaStageKeys;
+    for (int idx = threadIdx.x; idx < kMmaStageKeys * CPR; idx += THREADS) {
+      const int row = idx / CPR, c = idx % CPR;
+      const long long j = j0 + row;
+      const bool in = j < j_end;
+      const long long jj = in ? j : 0;
+      cp_async16(dst + tile_offset(row, c), kb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
+      cp_async16(dst + TILE_BYTES + tile_offset(row, c), vb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
+    }
+  };
+  for (int st = 0; st < kMmaStages - 1; st++) {
+    if (st < stages_total) issue_stage(st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  // This thread's two rows (accumulator rows lane / 4 and lane / 4 + 8 of the warp's 16) and their positions;
+  // rows past the matrix end get position -1: every key is masked and nothing is stored.
+  const long long row_lo = tile_row0 + warp * 16 + (lane >> 2);
+  const long long rows2[2] = {row_lo, row_lo + 8};
+  long long pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; h++) pos[h] = rows2[h] < a.rows ? rows2[h] / a.rep : -1;
+  const long long warp_last_pos = min(tile_row0 + warp * 16 + 15, a.rows - 1) / a.rep;  // < 0 never: the tile has a row
+
+  unsigned qa[HD / 16][4];
+  {
+    const int c0 = (lane & 3) * 2;
+    const T* qrow0 = q + (bg + rows2[0]) * HD;
+    const T* qrow1 = q + (bg + rows2[1]) * HD;
+    const bool in0 = rows2[0] < a.rows, in1 = rows2[1] < a.rows;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) {
+      qa[ks][0] = in0 ? __ldg(reinterpret_cast<const unsigned*>(qrow0 + ks * 16 + c0)) : 0u;
+      qa[ks][1] = in1 ? __ldg(reinterpret_cast<const unsigned*>(qrow1 + ks * 16 + c0)) : 0u;
+      qa[ks][2] = in0 ? __ldg(reinterpret_cast<const unsigned*>(qrow0 + ks * 16 + c0 + 8)) : 0u;
+      qa[ks][3] = in1 ? __ldg(reinterpret_cast<const unsigned*>(qrow1 + ks * 16 + c0 + 8)) : 0u;
+    }
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HD / 8; nt++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
+
+  for (int st = 0; st < stages_total; st++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kMmaStages - 2) : "memory");
+    __syncthreads();  // stage st is complete for everyone, and everyone is done with stage st - 1
+    if (st + kMmaStages - 1 < stages_total) issue_stage(st + kMmaStages - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const long long key0 = (long long)st * kMmaStageKeys;
+    if (key0 > warp_last_pos) continue;  // wholly above this warp's diagonal
+
+    const unsigned ktile = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
+    const unsigned vtile = ktile + TILE_BYTES;
+    // S = Q . K^T for 64 keys: eight accumulator tiles of 8 keys.
+    float sc[kMmaStageKeys / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < kMmaStageKeys / 8; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) sc[nt][e] = 0.f;
+#pragma unroll
+    for (int kb16 = 0; kb16 < kMmaStageKeys / 16; kb16++) {
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ks++) {
+        unsigned bk[4];
+        const int key = kb16 * 16 + ((lane >> 4) << 3) + (lane & 7);
+        const int chunk = ks * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(bk, ktile + tile_offset(key, chunk));
+        MmaOps<T>::mma(sc[2 * kb16], qa[ks], bk[0], bk[1]);
+        MmaOps<T>::mma(sc[2 * kb16 + 1], qa[ks], bk[2], bk[3]);
+      }
+    }
+    // Accumulator element e of tile nt: row h = e / 2, key key0 + nt * 8 + (lane % 4) * 2 + (e % 2).
+    const long long key_base = key0 + (lane & 3) * 2;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < kMmaStageKeys / 8; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float d = sc[nt][e];
+        if (a.round_scores) d = Elem<T>::round(d);
+        const bool ok = key_base + nt * 8 + (e & 1) <= pos[e >> 1];
+        d = ok ? d * a.scale : -INFINITY;
+        sc[nt][e] = d;
+        mx[e >> 1] = fmaxf(mx[e >> 1], d);
+      }
+    unsigned pa[kMmaStageKeys / 16][4];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      const float corr = m_run[h] == -INFINITY ? 0.f : (m_new == m_run[h] ? 1.f : __expf(m_run[h] - m_new));
+      if (corr != 1.f) {
+        l_part[h] *= corr;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; nt++) {
+          o[nt][2 * h] *= corr;
+          o[nt][2 * h + 1] *= corr;
+        }
+      }
+      m_run[h] = m_new;
+#pragma unroll
+      for (int kb16 = 0; kb16 < kMmaStageKeys / 16; kb16++) {
+        float p[4];
+#pragma unroll
+        for (int t = 0; t < 2; t++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const float sv = sc[2 * kb16 + t][2 * h + e];
+            p[t * 2 + e] = sv == -INFINITY ? 0.f : __expf(sv - m_new);
+          }
+        // The probabilities enter the second contraction in the element type; the row sum uses the same rounded values.
+        pa[kb16][h] = MmaOps<T>::pack(p[0], p[1]);
+        pa[kb16][2 + h] = MmaOps<T>::pack(p[2], p[3]);
+        l_part[h] += Elem<T>::round(p[0]) + Elem<T>::round(p[1]) + Elem<T>::round(p[2]) + Elem<T>::round(p[3]);
+      }
+    }
+    // O += P . V
+#pragma unroll
+    for (int kb16 = 0; kb16 < kMmaStageKeys / 16; kb16++) {
+#pragma unroll
+      for (int np = 0; np < HD / 16; np++) {
+        unsigned bv[4];
+        const int key = kb16 * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+        const int chunk = np * 2 + (lane >> 4);
+        ldmatrix_x4_trans(bv, vtile + tile_offset(key, chunk));
+        MmaOps<T>::mma(o[2 * np], pa[kb16], bv[0], bv[1]);
+        MmaOps<T>::mma(o[2 * np + 1], pa[kb16], bv[2], bv[3]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  const int c0 = (lane & 3) * 2;
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    l_part[h] += __shfl_xor_sync(0xffffffffu, l_part[h], 1);
+    l_part[h] += __shfl_xor_sync(0xffffffffu, l_part[h], 2);
+    if (rows2[h] >= a.rows) continue;
+    const float inv = l_part[h] > 0.f ? 1.f / l_part[h] : 0.f;
+    T* orow = out + (bg + rows2[h]) * HD + c0;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; nt++)
+      *reinterpret_cast<unsigned*>(orow + nt * 8) = MmaOps<T>::pack(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+  }
+}
+
+template <typename T, int HD>
+int launch_prefill_mma(const PrefillArgs& a, dim3 grid, const void* q, const void* k, const void* v, void* out, bool pdl,
+                       cudaStream_t stream) {
+  constexpr size_t smem = (size_t)kMmaStages * 2 * kMmaStageKeys * HD * 2;
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_prefill_mma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    configured = true;
+  }
+  return launch_kernel(attn_prefill_mma_kernel<T, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q, (const T*)k,
+                       (const T*)v, (T*)out) == cudaSuccess
+             ? 1
+             : 0;
 }
 
 }  // namespace
@@ -678,7 +892,7 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   }
   // Keys one CTA handles per chunk (see the kernel): no split should be shorter than that.
   const long long lanes_per_key = s.head_dim * (long long)dtype_size(s.dtype) / 16;
-  const long long chunk = (rep <= 4 ? 16 : 8) * (32 / lanes_per_key) * 4;
+  const long long chunk = 8 * (32 / lanes_per_key) * (rep <= 4 ? 8 : 4);
   // About four CTAs per SM in total, so that the tail of the last wave is short next to the whole.
   long long want = (4ll * sm_count + tiles - 1) / tiles;
   long long max_splits = std::max<long long>(1, s.kv_len / chunk);
@@ -718,6 +932,38 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
   }
   if (s.dtype == kF16) return dispatch_decode<__half>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
   return dispatch_decode<__nv_bfloat16>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
+}
+
+bool attn_prefill_supported(const AttnPrefillShape& s) {
+  if (s.dtype != kF16 && s.dtype != kBF16) return false;
+  if (s.head_dim != 64 && s.head_dim != 128) return false;
+  if (s.batch < 1 || s.kv_heads < 1 || s.rep < 1 || s.seq < 1) return false;
+  if (s.batch > 65535 || s.kv_heads > 65535) return false;
+  if ((s.seq * s.rep + kPrefillRows - 1) / kPrefillRows > 0x7fffffffLL) return false;
+  // 16-byte key/value rows.
+  if (s.kv_row_stride % 8 || s.kv_head_stride % 8 || s.kv_batch_stride % 8) return false;
+  return true;
+}
+
+int attn_prefill_launch(const AttnPrefillShape& s, const void* q, const void* k, const void* v, void* out, bool pdl,
+                        cudaStream_t stream) {
+  if (!attn_prefill_supported(s)) return 0;
+  PrefillArgs a;
+  a.seq = s.seq;
+  a.rep = (int)s.rep;
+  a.rows = s.seq * s.rep;
+  a.kv_heads = (int)s.kv_heads;
+  a.kv_batch_stride = s.kv_batch_stride;
+  a.kv_row_stride = s.kv_row_stride;
+  a.kv_head_stride = s.kv_head_stride;
+  a.scale = s.scale;
+  a.round_scores = s.round_scores;
+  dim3 grid((unsigned)((a.rows + kPrefillRows - 1) / kPrefillRows), (unsigned)s.kv_heads, (unsigned)s.batch);
+  if (s.dtype == kBF16)
+    return s.head_dim == 128 ? launch_prefill_mma<__nv_bfloat16, 128>(a, grid, q, k, v, out, pdl, stream)
+                             : launch_prefill_mma<__nv_bfloat16, 64>(a, grid, q, k, v, out, pdl, stream);
+  return s.head_dim == 128 ? launch_prefill_mma<__half, 128>(a, grid, q, k, v, out, pdl, stream)
+                           : launch_prefill_mma<__half, 64>(a, grid, q, k, v, out, pdl, stream);
 }
 
 }  // namespace pjrtx

@@ -125,6 +125,20 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count);
 int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, const void* q, const void* k, const void* v,
                        const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream);
 
+// Causal self-attention over whole sequences (prefill) as one tensor-core kernel. q / out: [batch, kv_heads, seq, rep,
+// head_dim] contiguous (query head = kv head * rep + r); k / v: [batch, seq, kv_heads, head_dim] through the strides;
+// position s sees keys 0..s.
+struct AttnPrefillShape {
+  int dtype = 0;
+  long long batch = 1, kv_heads = 1, rep = 1, seq = 1, head_dim = 1;
+  long long kv_batch_stride = 0, kv_row_stride = 0, kv_head_stride = 0;
+  int round_scores = 0;  // round q.k to the element type before scaling (what an explicit dot_general does)
+  float scale = 1.f;
+};
+bool attn_prefill_supported(const AttnPrefillShape& s);
+int attn_prefill_launch(const AttnPrefillShape& s, const void* q, const void* k, const void* v, void* out, bool pdl,
+                        cudaStream_t stream);
+
 // All-reduce (sum) over peer-mapped regions, one launch per rank (kernels/peer_reduce.cu). `regions[r]` is rank r's
 // region as mapped into this process (regions[rank] is the local one), `peer_region_bytes(slot_bytes)` long.
 // Returns 0 when the call does not fit (more than 8 ranks, size not a multiple of 8 x ranks bytes, or a part of it

@@ -129,6 +129,30 @@ def sdpa_random(dtype=P.BF16_CODE, batch=2, q_len=3, heads=8, kv_len=40, kv_head
     return b, [q, k, v, t]
 
 
+def prefill_attention(dtype=P.BF16_CODE, batch=2, kv_heads=2, rep=4, seq=96, head_dim=64, seed=13):
+    """Causal self-attention over whole sequences, written op by op the way the prefill program writes it:
+    scores = dot_general(q [B,G,S,rep,hd], k [B,S,G,hd]) -> f32 -> * 1/sqrt(hd) -> select(key <= position, ., -inf)
+    -> max / exp / sum / divide -> element type -> dot_general(., v)."""
+    rng = np.random.default_rng(seed)
+    dt = P.np_dtype(dtype)
+    q = rng.standard_normal((batch, kv_heads, seq, rep, head_dim), dtype=np.float32).astype(dt)
+    k = rng.standard_normal((batch, seq, kv_heads, head_dim), dtype=np.float32).astype(dt)
+    v = rng.standard_normal((batch, seq, kv_heads, head_dim), dtype=np.float32).astype(dt)
+    b = PlanBuilder()
+    pq, pk, pv = _params(b, [q, k, v])
+    sdims = [batch, kv_heads, seq, rep, seq]
+    causal = b.compare(b.iota(P.S32, sdims, 4), b.iota(P.S32, sdims, 2), P.LE)
+    sf = b.convert(b.dot_general(pq, pk, [4], [3], [0, 1], [0, 2]), P.F32)
+    sf = sf * b.scalar_like(sf, np.float32(1.0 / np.sqrt(np.float32(head_dim))))
+    sf = b.select(causal, sf, b.scalar_like(sf, np.float32(-np.inf)))
+    m = b.reduce("reduce_max", sf, [4])
+    e = b.unary("exp", sf - b.broadcast_in_dim(m, sdims, [0, 1, 2, 3]))
+    z = b.reduce("reduce_sum", e, [4])
+    probs = b.convert(e / b.broadcast_in_dim(z, sdims, [0, 1, 2, 3]), dtype)
+    b.set_outputs([b.dot_general(probs, pv, [4], [1], [0, 1], [0, 2])])
+    return b, [q, k, v]
+
+
 # ---- op-suite style cases (jax_op_suite.py) ---------------------------------------------------------------
 
 def elementwise_float_chain():

@@ -394,3 +394,32 @@ def test_executable_cache_compiles_reuses_and_evicts(gpu_backend):
     assert not cache.entry(first.fingerprint)["resident"]
     assert cache.stats()["evictions"] == 2
     cache.destroy()
+
+
+@pytest.mark.parametrize("dtype,kv_heads,rep,seq,hd", [
+    (P.BF16_CODE, 2, 4, 1, 64),      # a single position: one row tile, one stage, rows past the end
+    (P.BF16_CODE, 2, 4, 63, 64),
+    (P.BF16_CODE, 1, 1, 64, 128),    # one head per KV head: a row tile spans 64 positions
+    (P.BF16_CODE, 2, 4, 65, 128),    # second key stage holds a single key
+    (P.F16, 2, 8, 200, 64),          # eight heads per KV head, ragged last row tile
+    (P.BF16_CODE, 1, 4, 333, 128),   # six key stages: the copy ring wraps
+    (P.F16, 1, 3, 130, 128),         # positions straddle warps (rep does not divide 16)
+])
+def test_prefill_attention_matches_oracle(gpu_backend, dtype, kv_heads, rep, seq, hd):
+    """Causal self-attention over whole sequences on the prefill kernel against the op-by-op oracle."""
+    b, args = cases.prefill_attention(dtype=dtype, batch=2, kv_heads=kv_heads, rep=rep, seq=seq, head_dim=hd)
+    exe = gpu_backend.compile_executable(b, [0])
+    assert [s["type"] for s in exe.describe()["kernel_plan"]["steps"]] == ["attention_prefill"]
+    got = run_backend(gpu_backend, b, args, exe=exe)
+    assert_outputs(b, got, run_oracle(b, args), f"prefill attention {kv_heads}x{rep} seq {seq} hd {hd}")
+
+
+def test_prefill_attention_same_as_written_chain(gpu_backend, monkeypatch):
+    """The kernel and the unfused chain (dot -> softmax row kernel -> dot) agree within the 16-bit tolerance."""
+    b, args = cases.prefill_attention(seq=150, rep=4, head_dim=128)
+    fused = run_backend(gpu_backend, b, args)
+    monkeypatch.setenv("PJRTX_B200_ATTENTION_PREFILL", "0")
+    exe = gpu_backend.compile_executable(b, [0])
+    assert "attention_prefill" not in [s["type"] for s in exe.describe()["kernel_plan"]["steps"]]
+    plain = run_backend(gpu_backend, b, args, exe=exe)
+    assert_close(fused[0], plain[0], 2e-2, what="prefill attention kernel vs chain")

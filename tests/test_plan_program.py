@@ -241,6 +241,28 @@ def test_execute_requires_gpu_and_fails_loudly(backend):
         backend.buffer_from_host(np.zeros(4, np.float32))
 
 
+def test_prefill_attention_is_one_kernel(backend, monkeypatch):
+    """The rank-5 causal chain (scores -> masked softmax -> context) of the prefill program maps onto the prefill
+    attention kernel: scores and probabilities are never stored. Shapes the kernel does not cover, and the switch,
+    leave the chain as written."""
+    b, _ = cases.prefill_attention()
+    steps = backend.describe_kernels(b)["steps"]
+    assert [s["type"] for s in steps] == ["attention_prefill"]
+    assert (steps[0]["batch"], steps[0]["kv_heads"], steps[0]["rep"], steps[0]["seq"], steps[0]["head_dim"]) == (2, 2, 4, 96, 64)
+    b32, _ = cases.prefill_attention(head_dim=32)                   # head_dim outside {64, 128}
+    assert "attention_prefill" not in [s["type"] for s in backend.describe_kernels(b32)["steps"]]
+    bf, _ = cases.prefill_attention(dtype=P.F32)                    # 32-bit elements
+    assert "attention_prefill" not in [s["type"] for s in backend.describe_kernels(bf)["steps"]]
+    cfg = llama.TINY
+    pb, _ = llama.build_prefill(cfg, 2, 24)
+    types = [s["type"] for s in backend.describe_kernels(pb)["steps"]]
+    assert types.count("attention_prefill") == cfg.layers
+    assert types.count("dot") == 4 * cfg.layers + 1                 # q/k/v, o, gate/up, down (+ LM head)
+    monkeypatch.setenv("PJRTX_B200_ATTENTION_PREFILL", "0")
+    types0 = [s["type"] for s in backend.describe_kernels(pb)["steps"]]
+    assert types0.count("attention_prefill") == 0 and types0.count("dot") == 6 * cfg.layers + 1
+
+
 def test_partitioned_decode_keeps_attention_recognisable(backend):
     """Splatted scale / mask operands are rebuilt at the local shape, not sliced out of full-size tensors, so every
     partition still maps its attention block onto the split-KV kernel and carries no full-size mask."""
