@@ -420,7 +420,6 @@ AttnPrefillShape prefill_shape(const Value& q, const Value& k, float scale) {
   s.kv_batch_stride = k.dims[1] * k.dims[2] * k.dims[3];
   s.kv_row_stride = k.dims[2] * k.dims[3];
   s.kv_head_stride = k.dims[3];
-  s.round_scores = 1;
   s.scale = scale;
   return s;
 }

@@ -661,12 +661,18 @@ struct PrefillArgs {
   int rep = 1, kv_heads = 1;
   long long kv_batch_stride = 0, kv_row_stride = 0, kv_head_stride = 0;
   float scale = 1.f;
-  int round_scores = 0;
 };
 constexpr int kPrefillRows = 16 * kMmaWarps;
+constexpr int kPrefillStages = 2;  // 64 KiB per CTA at head_dim 128: three CTAs (twelve warps) per SM
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <typename T, int HD>
-__global__ void __launch_bounds__(kMmaWarps * 32)
+__global__ void __launch_bounds__(kMmaWarps * 32, 3)
 attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                         T* __restrict__ out) {
   static_assert(sizeof(T) == 2 && (HD == 64 || HD == 128), "16-bit elements, head_dim 64 or 128");
@@ -681,8 +687,8 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
   const int g = blockIdx.y, b = blockIdx.z;
   const long long tile_row0 = (long long)(gridDim.x - 1 - blockIdx.x) * kPrefillRows;  // longest tiles first
   const long long last_row = min(tile_row0 + kPrefillRows, a.rows) - 1;
-  const long long j_end = last_row / a.rep + 1;  // keys 0 .. last position of the tile
-  const int stages_total = (int)((j_end + kMmaStageKeys - 1) / kMmaStageKeys);
+  const int j_end = (int)(last_row / a.rep) + 1;  // keys 0 .. last position of the tile
+  const int stages_total = (j_end + kMmaStageKeys - 1) / kMmaStageKeys;
 
   const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride;
   const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride;
@@ -690,18 +696,18 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
   const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_attn);
   auto tile_offset = [](int row, int c) { return (unsigned)((c >> 3) * (kMmaStageKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)); };
   auto issue_stage = [&](int st) {
-    const unsigned dst = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
-    const long long j0 = (long long)st * kMmaStageKeys;
+    const unsigned dst = smem_base + (unsigned)(st % kPrefillStages) * STAGE_BYTES;
+    const int j0 = st * kMmaStageKeys;
     for (int idx = threadIdx.x; idx < kMmaStageKeys * CPR; idx += THREADS) {
       const int row = idx / CPR, c = idx % CPR;
-      const long long j = j0 + row;
+      const int j = j0 + row;
       const bool in = j < j_end;
       const long long jj = in ? j : 0;
       cp_async16(dst + tile_offset(row, c), kb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
       cp_async16(dst + TILE_BYTES + tile_offset(row, c), vb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
     }
   };
-  for (int st = 0; st < kMmaStages - 1; st++) {
+  for (int st = 0; st < kPrefillStages - 1; st++) {
     if (st < stages_total) issue_stage(st);
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
@@ -710,10 +716,11 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
   // rows past the matrix end get position -1: every key is masked and nothing is stored.
   const long long row_lo = tile_row0 + warp * 16 + (lane >> 2);
   const long long rows2[2] = {row_lo, row_lo + 8};
-  long long pos[2];
+  int pos[2];
 #pragma unroll
-  for (int h = 0; h < 2; h++) pos[h] = rows2[h] < a.rows ? rows2[h] / a.rep : -1;
-  const long long warp_last_pos = min(tile_row0 + warp * 16 + 15, a.rows - 1) / a.rep;  // < 0 never: the tile has a row
+  for (int h = 0; h < 2; h++) pos[h] = rows2[h] < a.rows ? (int)(rows2[h] / a.rep) : -1;
+  const int warp_first_pos = (int)((tile_row0 + warp * 16) / a.rep);
+  const int warp_last_pos = (int)(min(tile_row0 + warp * 16 + 15, a.rows - 1) / a.rep);
 
   unsigned qa[HD / 16][4];
   {
@@ -729,7 +736,12 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
       qa[ks][3] = in1 ? __ldg(reinterpret_cast<const unsigned*>(qrow1 + ks * 16 + c0 + 8)) : 0u;
     }
   }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};
+  // Scores are kept in log2 units (score * scale * log2 e), so a probability is one ex2 of a difference. The row
+  // sums are one more accumulator tile: P times a matrix of ones, in the tensor pipe instead of 32 adds per thread.
+  const float c_log2 = a.scale * 1.4426950408889634f;
+  const unsigned ones = MmaOps<T>::pack(1.f, 1.f);
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float lacc[4] = {0.f, 0.f, 0.f, 0.f};
   float o[HD / 8][4];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; nt++)
@@ -737,14 +749,14 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
     for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
 
   for (int st = 0; st < stages_total; st++) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(kMmaStages - 2) : "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPrefillStages - 2) : "memory");
     __syncthreads();  // stage st is complete for everyone, and everyone is done with stage st - 1
-    if (st + kMmaStages - 1 < stages_total) issue_stage(st + kMmaStages - 1);
+    if (st + kPrefillStages - 1 < stages_total) issue_stage(st + kPrefillStages - 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    const long long key0 = (long long)st * kMmaStageKeys;
+    const int key0 = st * kMmaStageKeys;
     if (key0 > warp_last_pos) continue;  // wholly above this warp's diagonal
 
-    const unsigned ktile = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
+    const unsigned ktile = smem_base + (unsigned)(st % kPrefillStages) * STAGE_BYTES;
     const unsigned vtile = ktile + TILE_BYTES;
     // S = Q . K^T for 64 keys: eight accumulator tiles of 8 keys.
     float sc[kMmaStageKeys / 8][4];
@@ -764,17 +776,17 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
         MmaOps<T>::mma(sc[2 * kb16 + 1], qa[ks], bk[2], bk[3]);
       }
     }
-    // Accumulator element e of tile nt: row h = e / 2, key key0 + nt * 8 + (lane % 4) * 2 + (e % 2).
-    const long long key_base = key0 + (lane & 3) * 2;
+    // Accumulator element e of tile nt: row h = e / 2, key key0 + nt * 8 + (lane % 4) * 2 + (e % 2). The explicit
+    // form rounds q.k to the element type before it scales; only stages that touch the diagonal need the mask.
+    const bool diagonal = key0 + kMmaStageKeys - 1 > warp_first_pos;
+    const int key_base = key0 + (lane & 3) * 2;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < kMmaStageKeys / 8; nt++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        float d = sc[nt][e];
-        if (a.round_scores) d = Elem<T>::round(d);
-        const bool ok = key_base + nt * 8 + (e & 1) <= pos[e >> 1];
-        d = ok ? d * a.scale : -INFINITY;
+        float d = Elem<T>::round(sc[nt][e]) * c_log2;
+        if (diagonal && key_base + nt * 8 + (e & 1) > pos[e >> 1]) d = -INFINITY;
         sc[nt][e] = d;
         mx[e >> 1] = fmaxf(mx[e >> 1], d);
       }
@@ -784,9 +796,12 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
       const float m_new = fmaxf(m_run[h], mx[h]);
-      const float corr = m_run[h] == -INFINITY ? 0.f : (m_new == m_run[h] ? 1.f : __expf(m_run[h] - m_new));
-      if (corr != 1.f) {
-        l_part[h] *= corr;
+      // Rows with no visible key yet (only rows past the matrix end) keep everything at zero.
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = ex2_approx(m_run[h] - m_use);
+      if (m_new != m_run[h]) {
+        lacc[2 * h] *= corr;
+        lacc[2 * h + 1] *= corr;
 #pragma unroll
         for (int nt = 0; nt < HD / 8; nt++) {
           o[nt][2 * h] *= corr;
@@ -796,23 +811,15 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
       m_run[h] = m_new;
 #pragma unroll
       for (int kb16 = 0; kb16 < kMmaStageKeys / 16; kb16++) {
-        float p[4];
-#pragma unroll
-        for (int t = 0; t < 2; t++)
-#pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const float sv = sc[2 * kb16 + t][2 * h + e];
-            p[t * 2 + e] = sv == -INFINITY ? 0.f : __expf(sv - m_new);
-          }
-        // The probabilities enter the second contraction in the element type; the row sum uses the same rounded values.
-        pa[kb16][h] = MmaOps<T>::pack(p[0], p[1]);
-        pa[kb16][2 + h] = MmaOps<T>::pack(p[2], p[3]);
-        l_part[h] += Elem<T>::round(p[0]) + Elem<T>::round(p[1]) + Elem<T>::round(p[2]) + Elem<T>::round(p[3]);
+        // The probabilities enter both products (values and row sum) rounded to the element type.
+        pa[kb16][h] = MmaOps<T>::pack(ex2_approx(sc[2 * kb16][2 * h] - m_use), ex2_approx(sc[2 * kb16][2 * h + 1] - m_use));
+        pa[kb16][2 + h] = MmaOps<T>::pack(ex2_approx(sc[2 * kb16 + 1][2 * h] - m_use), ex2_approx(sc[2 * kb16 + 1][2 * h + 1] - m_use));
       }
     }
-    // O += P . V
+    // O += P . V and l += P . 1
 #pragma unroll
     for (int kb16 = 0; kb16 < kMmaStageKeys / 16; kb16++) {
+      MmaOps<T>::mma(lacc, pa[kb16], ones, ones);
 #pragma unroll
       for (int np = 0; np < HD / 16; np++) {
         unsigned bv[4];
@@ -829,10 +836,9 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
   const int c0 = (lane & 3) * 2;
 #pragma unroll
   for (int h = 0; h < 2; h++) {
-    l_part[h] += __shfl_xor_sync(0xffffffffu, l_part[h], 1);
-    l_part[h] += __shfl_xor_sync(0xffffffffu, l_part[h], 2);
     if (rows2[h] >= a.rows) continue;
-    const float inv = l_part[h] > 0.f ? 1.f / l_part[h] : 0.f;
+    const float l = lacc[2 * h];
+    const float inv = l > 0.f ? 1.f / l : 0.f;
     T* orow = out + (bg + rows2[h]) * HD + c0;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; nt++)
@@ -843,7 +849,7 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
 template <typename T, int HD>
 int launch_prefill_mma(const PrefillArgs& a, dim3 grid, const void* q, const void* k, const void* v, void* out, bool pdl,
                        cudaStream_t stream) {
-  constexpr size_t smem = (size_t)kMmaStages * 2 * kMmaStageKeys * HD * 2;
+  constexpr size_t smem = (size_t)kPrefillStages * 2 * kMmaStageKeys * HD * 2;
   static bool configured = false;  // per instantiation
   if (!configured) {
     if (cudaFuncSetAttribute(attn_prefill_mma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
@@ -937,7 +943,7 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
 bool attn_prefill_supported(const AttnPrefillShape& s) {
   if (s.dtype != kF16 && s.dtype != kBF16) return false;
   if (s.head_dim != 64 && s.head_dim != 128) return false;
-  if (s.batch < 1 || s.kv_heads < 1 || s.rep < 1 || s.seq < 1) return false;
+  if (s.batch < 1 || s.kv_heads < 1 || s.rep < 1 || s.seq < 1 || s.seq > (1LL << 30)) return false;
   if (s.batch > 65535 || s.kv_heads > 65535) return false;
   if ((s.seq * s.rep + kPrefillRows - 1) / kPrefillRows > 0x7fffffffLL) return false;
   // 16-byte key/value rows.
@@ -957,7 +963,6 @@ int attn_prefill_launch(const AttnPrefillShape& s, const void* q, const void* k,
   a.kv_row_stride = s.kv_row_stride;
   a.kv_head_stride = s.kv_head_stride;
   a.scale = s.scale;
-  a.round_scores = s.round_scores;
   dim3 grid((unsigned)((a.rows + kPrefillRows - 1) / kPrefillRows), (unsigned)s.kv_heads, (unsigned)s.batch);
   if (s.dtype == kBF16)
     return s.head_dim == 128 ? launch_prefill_mma<__nv_bfloat16, 128>(a, grid, q, k, v, out, pdl, stream)

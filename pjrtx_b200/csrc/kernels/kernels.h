@@ -127,12 +127,11 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
 
 // Causal self-attention over whole sequences (prefill) as one tensor-core kernel. q / out: [batch, kv_heads, seq, rep,
 // head_dim] contiguous (query head = kv head * rep + r); k / v: [batch, seq, kv_heads, head_dim] through the strides;
-// position s sees keys 0..s.
+// position s sees keys 0..s. q.k is rounded to the element type before it is scaled, as the explicit dot_general does.
 struct AttnPrefillShape {
   int dtype = 0;
   long long batch = 1, kv_heads = 1, rep = 1, seq = 1, head_dim = 1;
   long long kv_batch_stride = 0, kv_row_stride = 0, kv_head_stride = 0;
-  int round_scores = 0;  // round q.k to the element type before scaling (what an explicit dot_general does)
   float scale = 1.f;
 };
 bool attn_prefill_supported(const AttnPrefillShape& s);
