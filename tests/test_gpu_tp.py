@@ -5,6 +5,7 @@ reproduce the CPU oracle's logits of the unpartitioned program; once with NCCL's
 all-reduce over peer-mapped memory. Skipped when fewer than two GPUs are visible.
 NVLS is switched off so that a rank that dies mid-test leaves nothing bound inside the switch.
 """
+import dataclasses
 import os
 import socket
 
@@ -50,10 +51,15 @@ def _worker(rank, world, port, batch, peer, queue):
         dist.destroy_process_group()
 
 
+def _config(world):
+    """Two KV heads shard over two ranks; four ranks get a copy with twice the heads."""
+    return llama.TINY if world <= 2 else dataclasses.replace(llama.TINY, heads=2 * world, kv_heads=world)
+
+
 def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
     if True:
         be = pjrtx_b200.Backend()
-        cfg = llama.TINY
+        cfg = _config(world)
         max_len, filled = 64, 40
         full, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=world, return_logits=True)
         weights = llama.make_weights(cfg, seed=0)
@@ -80,16 +86,16 @@ def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
                                  for r in results]))
 
 
-@pytest.mark.parametrize("batch,peer", [(2, False), (16, False), (2, True), (16, True)])
-def test_two_gpu_tensor_parallel_decode_matches_oracle(batch, peer):
+@pytest.mark.parametrize("world,batch,peer", [(2, 2, False), (2, 16, False), (2, 2, True), (2, 16, True),
+                                              (4, 16, False), (4, 2, True), (4, 16, True), (8, 16, True)])
+def test_tensor_parallel_decode_matches_oracle(world, batch, peer):
     import torch
     import torch.multiprocessing as mp
 
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     from oracle import plan_interp
 
-    world = 2
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
@@ -109,7 +115,7 @@ def test_two_gpu_tensor_parallel_decode_matches_oracle(batch, peer):
                 p.terminate()
     assert all(p.exitcode == 0 for p in procs)
 
-    cfg = llama.TINY
+    cfg = _config(world)
     max_len, filled = 64, 40
     full, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=1, return_logits=True)
     weights = llama.make_weights(cfg, seed=0)
@@ -130,4 +136,5 @@ def test_two_gpu_tensor_parallel_decode_matches_oracle(batch, peer):
             ref = np.sort(want_logits, axis=1)[:, -2:]
             decisive = (ref[:, 1] - ref[:, 0]) > 2 * err
             assert np.array_equal(np.asarray(tok)[decisive], np.asarray(want[0])[decisive])
-    assert np.array_equal(got[0][1][0][0], got[1][1][0][0])  # both ranks pick the same tokens
+    for rank in range(1, world):
+        assert np.array_equal(got[0][1][0][0], got[rank][1][0][0])  # every rank picks the same tokens
