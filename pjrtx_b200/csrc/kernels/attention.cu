@@ -888,8 +888,11 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   const bool large = tiles * s.kv_len >= (long long)sm_count * 256;  // measured: ahead from batch 4 at 2K keys, 8 KV heads
   p.mma = mma_ok && (force && *force ? atoi(force) != 0 : (rep == 8 || large)) ? 1 : 0;
   if (p.mma) {
-    // Two CTAs per SM are resident; aim for two waves of them, with splits no shorter than two stages of keys.
-    long long want = (4ll * sm_count + tiles - 1) / tiles;
+    // Two CTAs per SM are resident: one wave of them, no more (measured at 4K keys, batch 32: 32 / 64 / 128 / 256
+    // (sequence, KV head) pairs run fastest with 9 / 4 / 2 / 1 splits — 25.5 / 36 / 57 / 84 us against 44 / 50 / 68 /
+    // 103 us with twice as many CTAs), and no split shorter than two stages of keys.
+    long long want = std::max<long long>(1, 2ll * sm_count / tiles);
+    if (const char* w = getenv("PJRTX_B200_ATTENTION_SPLITS")) want = std::max(1, atoi(w));  // experiments
     long long max_splits = std::max<long long>(1, s.kv_len / (2 * kMmaStageKeys));
     p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
     p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
