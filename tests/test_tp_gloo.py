@@ -1,4 +1,4 @@
-"""Tensor-parallel planner checked numerically on CPU: two gloo ranks interpret their partition plans with the oracle,
+"""Tensor-parallel planner checked numerically on CPU: two or four gloo ranks interpret their partition plans with the oracle,
 exchanging all_reduce / all_gather over torch.distributed, and must reproduce the unpartitioned program."""
 import os
 import socket
@@ -23,9 +23,15 @@ def _shard(arr, split_dim, rank, world):
     return np.ascontiguousarray(np.take(arr, range(rank * n, (rank + 1) * n), axis=split_dim))
 
 
-def _worker(rank, world, port, int8, queue):
+def _config(world, int8):
+    """Two KV heads shard over two ranks; more ranks get a copy with as many KV heads as ranks."""
     import dataclasses
 
+    cfg = dataclasses.replace(llama.TINY, int8_weights=int8)
+    return cfg if world <= 2 else dataclasses.replace(cfg, heads=2 * world, kv_heads=world)
+
+
+def _worker(rank, world, port, int8, queue):
     import torch
     import torch.distributed as dist
 
@@ -36,7 +42,7 @@ def _worker(rank, world, port, int8, queue):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        cfg = dataclasses.replace(llama.TINY, int8_weights=int8)
+        cfg = _config(world, int8)
         batch, max_len, filled = 2, 32, 20
         full, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=world, return_logits=True)
         weights = llama.make_weights(cfg, seed=0)
@@ -65,11 +71,10 @@ def _worker(rank, world, port, int8, queue):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("int8", [False, True])
-def test_two_rank_partition_plans_reproduce_the_full_program(int8):
+@pytest.mark.parametrize("world,int8", [(2, False), (2, True), (4, False)])
+def test_partition_plans_reproduce_the_full_program(world, int8):
     import torch.multiprocessing as mp
 
-    world = 2
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
@@ -84,7 +89,7 @@ def test_two_rank_partition_plans_reproduce_the_full_program(int8):
         p.join(timeout=60)
         assert p.exitcode == 0
     want = results[0][1]
-    cfg = llama.TINY
+    cfg = _config(world, int8)
     for rank in range(world):
         got = results[rank][0]
         # logits are replicated after the all_gather; caches stay split along the KV-head axis
@@ -95,5 +100,6 @@ def test_two_rank_partition_plans_reproduce_the_full_program(int8):
             full_cache = want[2 + l]
             half = cfg.kv_heads // world
             np.testing.assert_allclose(got[2 + l], full_cache[:, :, rank * half:(rank + 1) * half], rtol=2e-2, atol=2e-2 * np.abs(full_cache).max())
-    # both ranks agree on the greedy token
-    assert np.array_equal(results[0][0][0], results[1][0][0])
+    # every rank agrees on the greedy token
+    for rank in range(1, world):
+        assert np.array_equal(results[0][0][0], results[rank][0][0])
