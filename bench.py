@@ -364,7 +364,7 @@ def run_ours(args):
         "compile_s": round(compile_s, 2), "setup_s": round(setup_s, 2),
     }
     if rank == 0 and world == 1 and batch == 1 and not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_baseline(llama.LLAMA3_8B, 1, filled, budget_layers=args.cpu_layers)
+        result["cpu_baseline"] = cpu_baseline(llama.LLAMA3_8B, 1, filled, budget_layers=args.cpu_layers, steps=8)
     if rank == 0:
         print(json.dumps(result))
     if world > 1:
@@ -505,7 +505,8 @@ def run_reference(args):
     if rank != 0:
         return
     cfg, batch, filled = (llama.LLAMA3_8B, 1, 2048) if world == 1 else (llama.LLAMA3_70B, 32, 4096)
-    base = cpu_baseline(cfg, batch, filled, budget_layers=args.cpu_layers, steps=max(1, min(args.steps, 2)))
+    base = cpu_baseline(cfg, batch, filled, budget_layers=args.cpu_layers,
+                        steps=max(1, min(args.steps, 16 if world == 1 else 2)))
     workload = ("llama3-8b-shape bf16 decode batch 1, KV prefilled 2048" if world == 1
                 else f"llama3-70b-shape bf16 decode batch 32, KV 4096, TP={world}")
     line = {
