@@ -221,10 +221,10 @@ def run_ours(args):
         uid = [be.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         be.comm_init(device, uid[0], rank, world)
-        # All-reduce over peer memory: on by default where it has been verified against NCCL on hardware (two ranks);
-        # PJRTX_B200_PEER_ALLREDUCE=1 turns it on for any world size, =0 keeps NCCL.
+        # All-reduce over peer memory: on by default where it has been verified against the oracle and timed against
+        # NCCL on hardware (two and four ranks); PJRTX_B200_PEER_ALLREDUCE=1 turns it on for any world size, =0 keeps NCCL.
         peer = os.environ.get("PJRTX_B200_PEER_ALLREDUCE")
-        if peer == "1" or (peer is None and world == 2):
+        if peer == "1" or (peer is None and world in (2, 4)):
             be.enable_peer_all_reduce(device, rank, world, dist.all_gather_object)
     t0 = time.time()
     _progress("compiling")
