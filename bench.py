@@ -196,35 +196,50 @@ def run_ours(args):
 
     import pjrtx_b200
 
+    import dataclasses
+
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # One collective configuration, the one the multi-GPU tests run: NVLink SHARP (NVLS) off.
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if world > 1:
         dist.init_process_group("gloo")  # host-side plumbing only: unique-id exchange, barriers, max over ranks
     be = pjrtx_b200.Backend()
     device = local_rank
-    be.enumerate_devices()
-    if world == 1:
-        cfg, batch, filled = llama.LLAMA3_8B, max(1, args.batch), 2048
-        workload = f"llama3-8b-shape bf16 decode batch {batch}, KV prefilled 2048"
-    else:
+    devices = be.enumerate_devices()
+    repeats = max(1, args.repeats)
+    total_steps = args.warmup + repeats * args.steps
+    tail = max(256, 2 * total_steps + 3 * args.steps + 16)  # positions the run appends after the prefilled ones
+    if args.workload == "int8":
+        cfg, batch, filled = dataclasses.replace(llama.LLAMA3_8B, int8_weights=True), 16, 4096
+        workload = f"llama3-8b-shape int8-weight decode batch 16, KV 4096, TP={world}"
+    elif args.workload == "70b" or world > 1:
         cfg, batch, filled = llama.LLAMA3_70B, 32, 4096
         workload = f"llama3-70b-shape bf16 decode batch 32, KV 4096, TP={world}"
-    if args.layers:
-        import dataclasses
+        if world == 1 and not args.layers:
+            # One GPU cannot hold the 80 layers: keep as many as fit beside the embedding, the LM head and working space.
+            per_layer = (cfg.d_model * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.d_model + 3 * cfg.d_model * cfg.ffn) * 2 \
+                + 2 * batch * (filled + tail) * cfg.kv_dim * 2
+            fixed = 2 * cfg.d_model * cfg.vocab * 2 + (6 << 30)
+            fit = int((0.97 * devices[device]["memory_bytes"] - fixed) // per_layer)
+            args.layers = max(1, min(cfg.layers, fit))
+    else:
+        cfg, batch, filled = llama.LLAMA3_8B, max(1, args.batch), 2048
+        workload = f"llama3-8b-shape bf16 decode batch {batch}, KV prefilled 2048"
+    if args.layers and args.layers != cfg.layers:
         cfg = dataclasses.replace(cfg, layers=args.layers)
         workload += f" (truncated to {args.layers} layers)"
-    total_steps = args.warmup + args.steps
-    max_len = filled + max(256, 2 * total_steps + 8)
+    max_len = filled + tail
     builder, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=world)
     if world > 1:
         uid = [be.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         be.comm_init(device, uid[0], rank, world)
         # All-reduce over peer memory: on by default where it has been verified against the oracle and timed against
-        # NCCL on hardware (two and four ranks); PJRTX_B200_PEER_ALLREDUCE=1 turns it on for any world size, =0 keeps NCCL.
+        # NCCL on hardware (two, four and eight ranks); PJRTX_B200_PEER_ALLREDUCE=0 keeps NCCL's.
         peer = os.environ.get("PJRTX_B200_PEER_ALLREDUCE")
-        if peer == "1" or (peer is None and world in (2, 4)):
+        if peer == "1" or (peer is None and world in (2, 4, 8)):
             be.enable_peer_all_reduce(device, rank, world, dist.all_gather_object)
     t0 = time.time()
     _progress("compiling")
@@ -246,7 +261,9 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
 
-    pos_bufs = [be.buffer_from_host(np.array(filled + i, np.int32), device) for i in range(2 * total_steps)]
+    barrier()  # every rank has compiled and holds its weights: nobody reaches a collective while a peer is still busy
+
+    pos_bufs = [be.buffer_from_host(np.array(filled + i, np.int32), device) for i in range(total_steps + 8)]
     token = be.buffer_from_host(np.full((batch,), 1, np.int32), device)
 
     def step(tok, pos_buf, caches):
@@ -263,19 +280,26 @@ def run_ours(args):
     sampler = ClockSampler(device)
     if rank == 0 and not os.environ.get("PJRTX_BENCH_NO_SAMPLER"):
         sampler.start()
-    start = be.record_event(device)
-    for _ in range(args.steps):
-        token, caches = step(token, pos_bufs[pi], caches); pi += 1
-    stop = be.record_event(device)
-    ms = be.elapsed_ms(start, stop)
-    barrier()
+    # The timed region is `steps` steps; it is repeated (same executable, the position keeps advancing) so that the
+    # clock sampler sees the GPU under load for longer than one poll, and the median repeat is reported.
+    times = []
+    for _ in range(repeats):
+        barrier()
+        start = be.record_event(device)
+        for _ in range(args.steps):
+            token, caches = step(token, pos_bufs[pi], caches); pi += 1
+        stop = be.record_event(device)
+        t_ms = be.elapsed_ms(start, stop)
+        barrier()
+        if world > 1:
+            t = torch.tensor([t_ms], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = float(t.item())
+        times.append(t_ms)
+    ms = float(np.median(times))
     clocks = sampler.stop() if rank == 0 else None
     _progress(f"timed loop done: {ms / args.steps:.3f} ms/step")
-    launches = exe.stats()["kernel_launch_total"] - launches0
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    launches = (exe.stats()["kernel_launch_total"] - launches0) // repeats
 
     # ---- end to end: pinned host -> device every step, token read back every step ----
     pinned_tok = torch.empty((batch,), dtype=torch.int32).pin_memory()
@@ -328,7 +352,9 @@ def run_ours(args):
         per_type[label][0] += 1
         per_type[label][1] += float(t)
         if st["type"] == "dot" and st["path"] == 1 and st["b0"] * st["b1"] == 1:
-            stream_bytes += st["k"] * st["n"] * esize + st["m"] * (st["k"] + st["n"]) * esize
+            # weights once + activations in and out (a chained launch reports the weights of all its segments)
+            weight_elems = st.get("weight_elems", st["k"] * st["n"])
+            stream_bytes += weight_elems * esize + st["m"] * (weight_elems // max(st["k"], 1) + st["k"]) * esize
             stream_ms += float(t)
             tensor_core |= bool(st.get("umma"))
     peak, peak_kind = measured_peaks()
@@ -341,7 +367,9 @@ def run_ours(args):
         "value": batch * args.steps / (ms * 1e-3),
         "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 (s8 weights dequantised to f16/bf16)" if cfg.int8_weights else "bf16", "data": "synthetic",
+        "timed_repeats": {"count": repeats, "ms_per_step": [round(t / args.steps, 4) for t in times], "reported": "median"},
         "config": {"workload": workload, "batch": batch, "kv_prefill": filled, "kv_buffer": max_len, "layers": cfg.layers,
                    "parallelism": f"tp{world}", "l2": "inputs (weights) exceed L2 by >100x; no flush needed",
                    "weights": "N(0,0.02) generated on device by seeded plans"},
@@ -363,7 +391,7 @@ def run_ours(args):
         "kernel_time_ms_per_step": {k: {"launches": v[0], "ms": round(v[1], 4)} for k, v in sorted(per_type.items())},
         "compile_s": round(compile_s, 2), "setup_s": round(setup_s, 2),
     }
-    if rank == 0 and world == 1 and batch == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and batch == 1 and args.workload == "decode" and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(llama.LLAMA3_8B, 1, filled, budget_layers=args.cpu_layers, steps=8)
     if rank == 0:
         print(json.dumps(result))
@@ -530,8 +558,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences decoded together on one GPU (1 = the headline workload; 16 and 32 are the batched-decode configs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode = the headline line; prefill = 8B-shape batch 4 x 2048 on one GPU (give it --steps 5)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "70b", "int8"],
+                    help="decode = the headline line (8B-shape batch 1 on one GPU, 70B-shape tensor parallel on more); "
+                         "prefill = 8B-shape batch 4 x 2048 on one GPU (give it --steps 5); 70b = the 70B shape also on one GPU, "
+                         "truncated to the layers that fit; int8 = 8B-shape int8 weights, batch 16, KV 4096, any GPU count")
+    ap.add_argument("--repeats", type=int, default=5, help="how often the timed region of --steps steps is run (median reported)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

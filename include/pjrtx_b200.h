@@ -252,6 +252,11 @@ uint64_t pjrtx_b200_plan_describe(PjrtxB200Plan *plan, char *out, uint64_t capac
  * version, compile options, shardings, donation, values, instructions with attributes, constants, call targets). A host
  * keeps compiled executables under this key. Same text-out convention as plan_describe. */
 uint64_t pjrtx_b200_plan_fingerprint(PjrtxB200Plan *plan, char *out, uint64_t capacity);
+/* The same key with the target devices mixed in, as the reference hashes the resolved device ids and local hardware ids
+ * of the executable's devices (src/runtime/executable_fingerprint.zig:38-56): the key to use with the executable cache,
+ * whose acquire refuses a resident executable that was compiled for other devices. */
+uint64_t pjrtx_b200_plan_fingerprint_for_devices(PjrtxB200Plan *plan, const int32_t *device_ordinals, uint64_t device_count,
+                                                 char *out, uint64_t capacity);
 /* Backend program graph (nodes, edges, fusion groups, schedule, liveness) as JSON; needs no device.
  * Returns the full length; writes at most capacity-1 bytes. program_build.build (program_build.zig:10-207). */
 uint64_t pjrtx_b200_plan_describe_program(PjrtxB200Plan *plan, char *out, uint64_t capacity);
@@ -419,9 +424,16 @@ int pjrtx_b200_comm_peer_import(int device_ordinal, const uint8_t *handles, int 
  *    or order them with events;
  *  - the first call on a device resolves the array's address and raises the kernel's shared-memory limit; make that
  *    first call before any stream capture begins.
- * `stream` is a cudaStream_t (NULL = the default stream). Returns 1 on success, 0 with pjrtx_b200_last_error() set. */
+ * The caller's current CUDA device is left as it was. `stream` is a cudaStream_t (NULL = the default stream).
+ * Returns 1 when the work was enqueued, 0 with pjrtx_b200_last_error() set. */
 int pjrtx_b200_dot_static_scratch(int device_ordinal, int dtype, const void *lhs, const void *rhs, void *out, int64_t m,
                                   int64_t k, int64_t n, void *stream);
+/* No counterpart in the reference. Completion status of the most recent pjrtx_b200_dot_static_scratch call on the
+ * device: waits for `stream`, reads the kernel's error word out of the static array (a 4-byte copy into a stack
+ * variable; nothing is allocated) and returns 1 when the kernel ran to completion, 0 with last_error set when one of
+ * its bounded device-side waits gave up (the output of that call is then not valid). Ask before the next call on the
+ * device: every call clears the word. */
+int pjrtx_b200_dot_static_scratch_status(int device_ordinal, void *stream);
 
 /* ---- generated-kernel check (no device needed) ---------------------------- */
 /* Compiles CUDA source for sm_100a with the run-time compiler; 1 when it compiles. The log goes to `out`. */

@@ -207,23 +207,19 @@ def _argmax_pair(values: np.ndarray, indices: np.ndarray, dims: Sequence[int]):
 
 
 def _dot_general(a, b, ins) -> np.ndarray:
-    lb, rb = ins.attrs.get("lhs_batch_dimensions", []), ins.attrs.get("rhs_batch_dimensions", [])
-    lc, rc = ins.attrs["lhs_contracting_dimensions"], ins.attrs["rhs_contracting_dimensions"]
+    """float64 contraction: batch axes first, then lhs free axes, then rhs free axes (StableHLO's result order).
+    Operands are brought to [batch..., M, K] x [batch..., K, N] and multiplied with the float64 BLAS."""
+    lb, rb = list(ins.attrs.get("lhs_batch_dimensions", [])), list(ins.attrs.get("rhs_batch_dimensions", []))
+    lc, rc = list(ins.attrs["lhs_contracting_dimensions"]), list(ins.attrs["rhs_contracting_dimensions"])
     lf = [d for d in range(a.ndim) if d not in lb and d not in lc]
     rf = [d for d in range(b.ndim) if d not in rb and d not in rc]
-    letters = "abcdefghijklmnopqrstuvwxyz"
-    la, lbl = [None] * a.ndim, [None] * b.ndim
-    nxt = iter(letters)
-    out = []
-    for x, y in zip(lb, rb):
-        c = next(nxt); la[x] = c; lbl[y] = c; out.append(c)
-    for x, y in zip(lc, rc):
-        c = next(nxt); la[x] = c; lbl[y] = c
-    for x in lf:
-        c = next(nxt); la[x] = c; out.append(c)
-    for y in rf:
-        c = next(nxt); lbl[y] = c; out.append(c)
-    return np.einsum(f"{''.join(la)},{''.join(lbl)}->{''.join(out)}", _f64(a), _f64(b))
+    batch_shape = [a.shape[d] for d in lb]
+    m_shape, n_shape = [a.shape[d] for d in lf], [b.shape[d] for d in rf]
+    k = int(np.prod([a.shape[d] for d in lc], dtype=np.int64))
+    m, n = int(np.prod(m_shape, dtype=np.int64)), int(np.prod(n_shape, dtype=np.int64))
+    at = np.transpose(_f64(a), lb + lf + lc).reshape(batch_shape + [m, k])
+    bt = np.transpose(_f64(b), rb + rc + rf).reshape(batch_shape + [k, n])
+    return np.matmul(at, bt).reshape(batch_shape + m_shape + n_shape)
 
 
 def _sdpa(q, k, v, token) -> np.ndarray:
@@ -287,12 +283,24 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
     CPU baseline); `weight_cache` keeps widened copies of parameters between calls."""
     env: Dict[int, np.ndarray] = {}
     assert len(arguments) == len(builder.parameter_ids)
+    # Intermediates are dropped after their last reader so that full-width programs fit in host memory.
+    last_use: Dict[int, int] = {}
+    for index, ins in enumerate(builder.instructions):
+        for i in ins.inputs:
+            last_use[i] = index
+    keep = set(builder.output_ids)
+
+    def release(index, ins):
+        for i in ins.inputs:
+            if last_use.get(i) == index and i not in keep:
+                env.pop(i, None)
+
     for vid, arr in zip(builder.parameter_ids, arguments):
         desc = builder.values[vid]
         a = np.asarray(arr)
         assert tuple(a.shape) == desc.dims and a.dtype == P.np_dtype(desc.dtype), (vid, a.shape, desc.dims, a.dtype)
         env[vid] = a
-    for ins in builder.instructions:
+    for index, ins in enumerate(builder.instructions):
         out_desc = builder.values[ins.outputs[0]]
         code, dims = out_desc.dtype, out_desc.dims
         x = [env[i] for i in ins.inputs]
@@ -347,6 +355,22 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
             r = np.flip(x[0], axis=tuple(ins.attrs["dimensions"]))
         elif k == "concatenate":
             r = np.concatenate(x, axis=ins.attrs["dimension"][0])
+        elif k == "pad":
+            # stablehlo.pad: interior padding first, then edge padding; negative edge padding removes elements.
+            lo, hi = ins.attrs["edge_padding_low"], ins.attrs["edge_padding_high"]
+            gaps = ins.attrs.get("interior_padding") or [0] * x[0].ndim
+            src = x[0]
+            spread_shape = [0 if n == 0 else (n - 1) * (g + 1) + 1 for n, g in zip(src.shape, gaps)]
+            spread = np.full(spread_shape, np.asarray(x[1]).reshape(()), dtype=src.dtype)
+            spread[tuple(slice(None, None, g + 1) for g in gaps)] = src
+            r = np.full(dims, np.asarray(x[1]).reshape(()), dtype=src.dtype)
+            dst_sel, src_sel = [], []
+            for d, (l, h) in enumerate(zip(lo, hi)):
+                s0 = max(0, -l)
+                s1 = spread_shape[d] - max(0, -h)
+                dst_sel.append(slice(max(0, l), max(0, l) + max(0, s1 - s0)))
+                src_sel.append(slice(s0, max(s0, s1)))
+            r[tuple(dst_sel)] = spread[tuple(src_sel)]
         elif k == "iota":
             d = ins.attrs["iota_dimension"][0]
             shape = [1] * len(dims)
@@ -396,6 +420,8 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
             val, idx = _argmax_pair(x[0], x[1], ins.attrs["reduce_dimensions"])
             env[ins.outputs[0]] = _round_to(val, code).reshape(dims)
             env[ins.outputs[1]] = idx.reshape(dims)
+            del x
+            release(index, ins)
             continue
         elif k == "custom_call":
             if ins.target and ins.target.endswith("scaled_dot_product_attention"):
@@ -418,4 +444,6 @@ def run_plan(builder: P.PlanBuilder, arguments: Sequence[np.ndarray], all_reduce
         if r.dtype != P.np_dtype(code):
             r = _round_to(r, code)
         env[ins.outputs[0]] = r
+        del x
+        release(index, ins)
     return [env[o] for o in builder.output_ids]

@@ -141,6 +141,8 @@ SYMBOLS = {
     "pjrtx_b200_plan_verify": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_fingerprint": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
+    "pjrtx_b200_plan_fingerprint_for_devices": (ctypes.c_uint64, [_P, ctypes.POINTER(ctypes.c_int32), ctypes.c_uint64,
+                                                                  ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_program": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_describe_kernels": (ctypes.c_uint64, [_P, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_plan_partition": (_P, [_P, ctypes.c_int32, ctypes.c_int32]),
@@ -168,6 +170,7 @@ SYMBOLS = {
     "pjrtx_b200_comm_peer_import": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint8), ctypes.c_int, ctypes.c_int]),
     "pjrtx_b200_dot_static_scratch": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _P, _P, _P, ctypes.c_int64, ctypes.c_int64,
                                                       ctypes.c_int64, _P]),
+    "pjrtx_b200_dot_static_scratch_status": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p]),
     "pjrtx_b200_compile_check": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_executable_cache_create": (_P, [ctypes.c_uint64]),
     "pjrtx_b200_executable_cache_destroy": (None, [_P]),
@@ -337,9 +340,9 @@ class ExecutableCache:
         """`recordCompile` + `acquireBackendExecutable`: a resident executable is leased again, otherwise the plan compiles."""
         plan = builder.build(self.lib)
         try:
-            fp = fingerprint or _text(self.lib, self.lib.pjrtx_b200_plan_fingerprint, plan)
-            self.record_compile(fp)
             devs = (ctypes.c_int32 * len(devices))(*devices)
+            fp = fingerprint or _text(self.lib, self.lib.pjrtx_b200_plan_fingerprint_for_devices, plan, devs, len(devices))
+            self.record_compile(fp)
             reused = ctypes.c_int(0)
             trim = ExecutableCacheTrim()
             h = self.lib.pjrtx_b200_executable_cache_acquire(self.handle, fp.encode(), plan, devs, len(devices),
@@ -534,10 +537,14 @@ class Backend:
         finally:
             self.lib.pjrtx_b200_plan_destroy(plan)
 
-    def plan_fingerprint(self, builder: plan_mod.PlanBuilder) -> str:
-        """Cache key of the plan under the current backend state (custom-call registry version included)."""
+    def plan_fingerprint(self, builder: plan_mod.PlanBuilder, devices: Optional[Sequence[int]] = None) -> str:
+        """Cache key of the plan under the current backend state (custom-call registry version included); with
+        `devices` the target device ordinals are part of the key (the form the executable cache uses)."""
         plan = builder.build(self.lib)
         try:
+            if devices is not None:
+                devs = (ctypes.c_int32 * len(devices))(*devices)
+                return _text(self.lib, self.lib.pjrtx_b200_plan_fingerprint_for_devices, plan, devs, len(devices))
             return _text(self.lib, self.lib.pjrtx_b200_plan_fingerprint, plan)
         finally:
             self.lib.pjrtx_b200_plan_destroy(plan)
@@ -669,6 +676,12 @@ class Backend:
         ok = self.lib.pjrtx_b200_dot_static_scratch(device, dtype, ctypes.c_void_p(lhs_ptr), ctypes.c_void_p(rhs_ptr),
                                                     ctypes.c_void_p(out_ptr), m, k, n, ctypes.c_void_p(stream))
         if not ok:
+            raise BackendError("CommandSubmissionFailed", self._err())
+
+    def dot_static_scratch_status(self, device: int = 0, stream: int = 0) -> None:
+        """Waits for `stream` and raises if the most recent `dot_static_scratch` call on the device gave up one of its
+        bounded device-side waits (its output is then not valid). Allocates nothing; ask before the next call."""
+        if not self.lib.pjrtx_b200_dot_static_scratch_status(device, ctypes.c_void_p(stream)):
             raise BackendError("CommandSubmissionFailed", self._err())
 
     def compile_check(self, source: str) -> str:

@@ -354,6 +354,13 @@ uint64_t pjrtx_b200_plan_fingerprint(PjrtxB200Plan* plan, char* out, uint64_t ca
   GUARD_INT(if (!plan) return 0; return write_text(plan_fingerprint(plan->plan, "b200_cuda", custom_call_registry_version()), out, capacity);)
 }
 
+uint64_t pjrtx_b200_plan_fingerprint_for_devices(PjrtxB200Plan* plan, const int32_t* device_ordinals, uint64_t device_count,
+                                                 char* out, uint64_t capacity) {
+  GUARD_INT(if (!plan || (device_count && !device_ordinals)) return 0;
+            std::vector<int32_t> devs(device_ordinals, device_ordinals + device_count);
+            return write_text(plan_fingerprint(plan->plan, "b200_cuda", custom_call_registry_version(), devs), out, capacity);)
+}
+
 uint64_t pjrtx_b200_plan_describe_program(PjrtxB200Plan* plan, char* out, uint64_t capacity) {
   GUARD_INT(if (!plan) return 0; std::string msg = verify_plan(plan->plan); if (!msg.empty()) {
     set_last_error("%s", msg.c_str());
@@ -557,10 +564,19 @@ PjrtxB200Executable* pjrtx_b200_executable_cache_acquire(PjrtxB200ExecutableCach
       if (!cache->cache.entry(fingerprint, &snap)) {
         set_last_error("fingerprint %s was not recorded", fingerprint);
         return nullptr;
-      } if (void* h = cache->cache.retain_resident(fingerprint)) {
-        if (out_reused) *out_reused = 1;
-        return static_cast<PjrtxB200Executable*>(h);
       } std::vector<int> devs(device_ordinals, device_ordinals + device_count);
+      if (void* h = cache->cache.retain_resident(fingerprint)) {
+        // A key that does not cover the target devices would hand out an executable of another GPU: refuse it.
+        PjrtxB200Executable* held = static_cast<PjrtxB200Executable*>(h);
+        if (held->exe && executable_device_ordinals(held->exe) != devs) {
+          cache->cache.release(fingerprint);
+          set_last_error("fingerprint %s is resident for other devices; key the request with pjrtx_b200_plan_fingerprint_for_devices",
+                         fingerprint);
+          return nullptr;
+        }
+        if (out_reused) *out_reused = 1;
+        return held;
+      }
       std::string err; auto t0 = std::chrono::steady_clock::now(); Executable* exe = compile_executable(plan->plan, devs, &err);
       if (!exe) {
         set_last_error("%s", err.c_str());
@@ -693,6 +709,10 @@ void pjrtx_b200_comm_destroy(int device_ordinal) {
 int pjrtx_b200_dot_static_scratch(int device_ordinal, int dtype, const void* lhs, const void* rhs, void* out, int64_t m, int64_t k,
                                   int64_t n, void* stream) {
   GUARD_INT(return stream_dot_static_scratch(device_ordinal, dtype, lhs, rhs, out, m, k, n, (cudaStream_t)stream);)
+}
+
+int pjrtx_b200_dot_static_scratch_status(int device_ordinal, void* stream) {
+  GUARD_INT(return stream_dot_static_scratch_status(device_ordinal, (cudaStream_t)stream);)
 }
 
 int pjrtx_b200_compile_check(const char* source, char* out, uint64_t capacity) {

@@ -769,6 +769,53 @@ class Gen {
         }
         return emit(in(0), Idx{index_var(linearize(sc, sd)), IdxClass::GEN});
       }
+      case Kind::pad: {
+        // out[o] = operand[(o - low) / (interior + 1)] where every axis lands on an operand element, else the padding
+        // scalar. Negative edge padding crops (src/backend/mlx_metal/api.cc:2637 pads with non-negative widths only;
+        // StableHLO allows both).
+        const auto& sd = val(in(0)).dims;
+        const auto& lo = ins.list("edge_padding_low");
+        const auto& interior = ins.list("interior_padding");
+        if (lo.size() != sd.size() || (!interior.empty() && interior.size() != sd.size())) fail("pad attributes do not match the operand rank");
+        std::vector<std::string> oc = coords(idx.var, out.dims), sc(sd.size());
+        std::string cond;
+        for (size_t d = 0; d < sd.size(); d++) {
+          const int64_t step = (interior.empty() ? 0 : interior[d]) + 1;
+          if (step < 1) fail("negative interior padding");
+          std::string t = index_var("((idx_t)" + oc[d] + " - (idx_t)" + std::to_string(lo[d]) + ")");
+          std::string inside = "(" + t + " >= 0 && " + t + " < (idx_t)" + std::to_string((sd[d] - 1) * step + 1);
+          if (step > 1) inside += " && " + t + " % " + std::to_string(step) + " == 0";
+          inside += ")";
+          cond += (cond.empty() ? "" : " && ") + inside;
+          sc[d] = step > 1 ? "(" + t + " / " + std::to_string(step) + ")" : t;
+        }
+        if (cond.empty()) cond = "true";
+        std::string name = tmp("t");
+        line(std::string(comp_type(dt)) + " " + name + ";");
+        line("if (" + cond + ") {");
+        {
+          Scope inner;
+          inner.indent = scope().indent + 2;
+          scopes_.push_back(&inner);
+          std::string e = emit(in(0), Idx{index_var(linearize(sc, sd)), IdxClass::GEN});
+          line(name + " = " + e + ";");
+          scopes_.pop_back();
+          scope().code += inner.code;
+        }
+        line("} else {");
+        {
+          Scope inner;
+          inner.indent = scope().indent + 2;
+          scopes_.push_back(&inner);
+          std::string e = emit(in(1), scalar_index());
+          line(name + " = " + e + ";");
+          scopes_.pop_back();
+          scope().code += inner.code;
+        }
+        line("}");
+        scope().memo[{v, idx.var}] = name;
+        return name;
+      }
       case Kind::concatenate: {
         int64_t dim = ins.scalar("dimension", 0);
         std::vector<std::string> oc = coords(idx.var, out.dims);
@@ -1039,10 +1086,15 @@ class Gen {
     int block = 32;
     // Many rows: a few items per thread keep the SMs full with small CTAs. Fewer rows than SMs: latency is what
     // counts, so one item per thread (every loop over the row is then a single round of loads).
+    static const int few_rows_max = [] {
+      const char* v = getenv("PJRTX_B200_ROW_BLOCK_MAX");
+      const int n = v && *v ? atoi(v) : 1024;
+      return n < 32 ? 32 : n > 1024 ? 1024 : n;
+    }();
     if (R_ >= sm_count_) {
       while (block < 512 && block * 4 < items) block *= 2;
     } else {
-      while (block < 1024 && block < items) block *= 2;
+      while (block < few_rows_max && block < items) block *= 2;
     }
     k->block = block;
     k->grid = std::max<int64_t>(1, std::min<int64_t>(R_, (int64_t)sm_count_ * std::max(1, 2048 / block)));
@@ -1211,6 +1263,23 @@ bool codegen_fusible(const Plan& plan, const Instruction& ins) {
       return ins.outputs.size() == 1 || (ins.kind == Kind::reduce_max && ins.outputs.size() == 2 && ins.inputs.size() >= 2);
     case Kind::iota: case Kind::concatenate: case Kind::dynamic_slice: case Kind::reverse:
       return true;
+    case Kind::pad: {
+      if (ins.inputs.size() != 2 || plan.values[ins.inputs[1]].count() != 1) return false;
+      const Value& operand = plan.values[ins.inputs[0]];
+      const Value& result = plan.values[ins.outputs[0]];
+      const auto& lo = ins.list("edge_padding_low");
+      const auto& hi = ins.list("edge_padding_high");
+      const auto& interior = ins.list("interior_padding");
+      if (lo.size() != operand.dims.size() || hi.size() != operand.dims.size() || result.dims.size() != operand.dims.size()) return false;
+      if (!interior.empty() && interior.size() != operand.dims.size()) return false;
+      for (size_t d = 0; d < operand.dims.size(); d++) {
+        const int64_t gap = interior.empty() ? 0 : interior[d];
+        if (gap < 0) return false;
+        const int64_t span = operand.dims[d] == 0 ? 0 : (operand.dims[d] - 1) * (gap + 1) + 1;
+        if (result.dims[d] != std::max<int64_t>(0, lo[d] + span + hi[d])) return false;
+      }
+      return operand.dtype == result.dtype && plan.values[ins.inputs[1]].dtype == operand.dtype;
+    }
     case Kind::optimization_barrier:
       return ins.inputs.size() == 1 && ins.outputs.size() == 1;
     case Kind::gather: {

@@ -1010,6 +1010,283 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     kp->steps = std::move(merged);
   }
 
+  // Streaming contractions on the CUDA-core kernel take over what the small kernels around them did, and consecutive
+  // ones run as one launch (kernels/stream_tma.cuh):
+  //   * a generated kernel that only computes silu(gate) * up for the next contraction's lhs becomes that
+  //     contraction's lhs transform;
+  //   * a generated row kernel that only computes RMSNorm(x) * gain (optionally of x = a + b, where one addend is the
+  //     previous contraction's result) for the next contraction's lhs becomes an lhs transform, and the addition becomes
+  //     the previous contraction's residual epilogue;
+  //   * adjacent streaming contractions are chained (up to kDotChainMax segments per launch).
+  // The dataflow is matched exactly; anything else keeps its generated kernel.
+  // Both are off unless PJRTX_B200_DOT_FUSE=1 (and PJRTX_B200_DOT_CHAIN=1): measured on the 8B-shape decode step, ms per
+  // step with programmatic dependent launch between kernels: separate launches 3.50; transforms and residuals folded in
+  // 3.58 (every CTA repeats the row reduction after it has waited for its predecessor, where the one-CTA norm kernel ran
+  // concurrently with the next contraction's ramp); chained 4.16 (a segment boundary - fold, grid barrier, factors,
+  // first lhs values - is 7 to 8 us of dependent round trips against the 4 us of weights the rings hold).
+  if (env_flag_local("PJRTX_B200_DOT_FUSE", false)) {
+    auto chainable = [&](const Step& st) {
+      return st.type == Step::kDot && st.dot_scratch.path == 1 && st.dot_scratch.tma == 1 && st.dot_scratch.umma == 0 &&
+             st.dot.b0 * st.dot.b1 == 1;
+    };
+    for (Step& st : kp->steps) {
+      if (!chainable(st)) continue;
+      DotSeg seg;
+      if (st.dot_group.size() > 1) seg.group = st.dot_group;
+      else seg.group = {st.dot};
+      seg.lhs = st.inputs[0];
+      for (size_t g = 1; g < st.inputs.size(); g++) seg.rhs.push_back(st.inputs[g]);
+      seg.out = st.outputs;
+      seg.residual.assign(seg.out.size(), UINT32_MAX);
+      st.segs.push_back(std::move(seg));
+    }
+    // Readers of a storage class: every live instruction that reads a value of the class.
+    auto class_users = [&](uint32_t r) {
+      std::vector<size_t> out;
+      for (size_t v = 0; v < nv; v++)
+        if (kp->root[v] == r)
+          for (size_t u : users[v])
+            if (!is_alias_kind(plan.instructions[u])) out.push_back(u);
+      return out;
+    };
+    auto subset_of = [&](const std::vector<size_t>& a, const std::vector<size_t>& nodes) {
+      for (size_t x : a)
+        if (std::find(nodes.begin(), nodes.end(), x) == nodes.end()) return false;
+      return true;
+    };
+    auto in_step = [&](const Step& f, uint32_t v) -> const Instruction* {
+      const long pi = producer[v];
+      if (pi < 0 || std::find(f.nodes.begin(), f.nodes.end(), (size_t)pi) == f.nodes.end()) return nullptr;
+      return &plan.instructions[pi];
+    };
+    auto scalar_f32 = [&](uint32_t v, float* out) {
+      long pi = producer[v];
+      if (pi >= 0 && plan.instructions[pi].kind == Kind::broadcast_in_dim) {
+        v = plan.instructions[pi].inputs[0];
+        pi = producer[v];
+      }
+      if (pi < 0 || plan.instructions[pi].kind != Kind::constant) return false;
+      const Instruction& c = plan.instructions[pi];
+      if (plan.values[v].dtype != kF32 || c.literal.size() != 4) return false;
+      memcpy(out, c.literal.data(), 4);
+      return true;
+    };
+    auto non_alias_nodes = [&](const Step& f) {
+      size_t n = 0;
+      for (size_t i : f.nodes) n += is_alias_kind(plan.instructions[i]) ? 0 : 1;
+      return n;
+    };
+    auto replace_value = [](std::vector<uint32_t>& list, uint32_t from, uint32_t to) {
+      for (uint32_t& v : list)
+        if (v == from) v = to;
+    };
+    auto add_unique = [](std::vector<uint32_t>& list, uint32_t v) {
+      if (std::find(list.begin(), list.end(), v) == list.end()) list.push_back(v);
+    };
+
+    // silu(gate) * up feeding the lhs of D.
+    auto match_silu = [&](const Step& f, Step& d) {
+      if (f.type != Step::kFused || f.fused.row || f.outputs.size() != 1 || !f.fused.scatter_dst.empty()) return false;
+      DotSeg& seg = d.segs[0];
+      const uint32_t act = f.outputs[0];
+      if (fusion_debug)
+        fprintf(stderr, "pjrtx_b200 fusion: silu candidate lhs=%u act=%u nodes=%zu users_ok=%d\n", seg.lhs, act, non_alias_nodes(f),
+                (int)subset_of(class_users(act), d.nodes));
+      if (seg.lhs != act || is_output[act] || non_alias_nodes(f) != 3) return false;
+      if (!subset_of(class_users(act), d.nodes)) return false;
+      const Instruction* top = nullptr;
+      for (size_t i : f.nodes)
+        if (plan.instructions[i].kind == Kind::multiply && kp->root[plan.instructions[i].outputs[0]] == act) top = &plan.instructions[i];
+      if (!top) return false;
+      for (int swap_top = 0; swap_top < 2; swap_top++) {
+        const uint32_t t2 = top->inputs[swap_top], u = top->inputs[1 - swap_top];
+        const Instruction* inner = in_step(f, t2);
+        if (!inner || inner->kind != Kind::multiply || in_step(f, u)) continue;
+        for (int swap_in = 0; swap_in < 2; swap_in++) {
+          const uint32_t g = inner->inputs[swap_in], sg = inner->inputs[1 - swap_in];
+          const Instruction* lg = in_step(f, sg);
+          if (!lg || lg->kind != Kind::logistic || lg->inputs[0] != g || in_step(f, g)) continue;
+          const Value& gv = plan.values[g];
+          const Value& uv = plan.values[u];
+          if (gv.dtype != seg.group[0].dtype || uv.dtype != gv.dtype || gv.dims != uv.dims) continue;
+          if ((int64_t)gv.count() != seg.group[0].m * seg.group[0].k || seg.group[0].lhs_k != 1 ||
+              (seg.group[0].m > 1 && seg.group[0].lhs_m != seg.group[0].k))
+            continue;
+          seg.lhs = kp->root[g];
+          seg.lhs2 = kp->root[u];
+          seg.lhs_desc.kind = kDotLhsSiluMul;
+          replace_value(d.inputs, act, seg.lhs);
+          add_unique(d.inputs, seg.lhs2);
+          return true;
+        }
+      }
+      return false;
+    };
+
+    // RMSNorm(x) * gain feeding the lhs of D, x optionally the sum of two values one of which P produced.
+    auto match_norm = [&](const Step& f, Step& d, Step* p) {
+      if (f.type != Step::kFused || !f.fused.row || !f.fused.scatter_dst.empty() || f.outputs.empty() || f.outputs.size() > 2) return false;
+      DotSeg& seg = d.segs[0];
+      const uint32_t h = seg.lhs;
+      if (std::find(f.outputs.begin(), f.outputs.end(), h) == f.outputs.end() || is_output[h]) return false;
+      if (!subset_of(class_users(h), d.nodes)) return false;
+      const int dt = seg.group[0].dtype;
+      if (dt != kBF16 && dt != kF16) return false;
+      const Instruction* top = nullptr;
+      for (size_t i : f.nodes)
+        if (plan.instructions[i].kind == Kind::multiply && kp->root[plan.instructions[i].outputs[0]] == h) top = &plan.instructions[i];
+      if (!top) return false;
+      std::set<const Instruction*> seen;
+      auto pick = [&](const Instruction* ins, Kind first_kind, uint32_t* a, uint32_t* b) {
+        // Orders the two operands of a commutative instruction so that *a is produced inside the step by `first_kind`.
+        for (int sw = 0; sw < 2; sw++) {
+          const Instruction* q = in_step(f, ins->inputs[sw]);
+          if (q && q->kind == first_kind) {
+            *a = ins->inputs[sw];
+            *b = ins->inputs[1 - sw];
+            return true;
+          }
+        }
+        return false;
+      };
+      uint32_t xn, wb;
+      if (!pick(top, Kind::convert, &xn, &wb)) return false;
+      const Instruction* wbi = in_step(f, wb);
+      if (!wbi || wbi->kind != Kind::broadcast_in_dim) return false;
+      const uint32_t w = wbi->inputs[0];
+      const Value& hv = plan.values[top->outputs[0]];
+      const size_t rank = hv.dims.size();
+      if (rank != 2 || in_step(f, w) || plan.values[w].dims.size() != 1 || plan.values[w].dims[0] != hv.dims[1] ||
+          plan.values[w].dtype != dt || wbi->list("broadcast_dimensions") != std::vector<int64_t>{1})
+        return false;
+      const Instruction* xni = in_step(f, xn);
+      const Instruction* mul32 = in_step(f, xni->inputs[0]);
+      if (!mul32 || mul32->kind != Kind::multiply || plan.values[mul32->outputs[0]].dtype != kF32 || hv.dtype != dt) return false;
+      uint32_t xf, rb;
+      if (!pick(mul32, Kind::convert, &xf, &rb)) return false;
+      const Instruction* xfi = in_step(f, xf);
+      const Instruction* rbi = in_step(f, rb);
+      if (!rbi || rbi->kind != Kind::broadcast_in_dim || rbi->list("broadcast_dimensions") != std::vector<int64_t>{0}) return false;
+      const Instruction* rs = in_step(f, rbi->inputs[0]);
+      if (!rs || rs->kind != Kind::rsqrt) return false;
+      const Instruction* addi = in_step(f, rs->inputs[0]);
+      if (!addi || addi->kind != Kind::add) return false;
+      uint32_t mean, ceps;
+      if (!pick(addi, Kind::multiply, &mean, &ceps)) return false;
+      const Instruction* meani = in_step(f, mean);
+      uint32_t ssum, cscale;
+      if (!pick(meani, Kind::reduce_sum, &ssum, &cscale)) return false;
+      const Instruction* sumi = in_step(f, ssum);
+      if (sumi->outputs.size() != 1 || sumi->list("reduce_dimensions") != std::vector<int64_t>{1}) return false;
+      const Instruction* sq = in_step(f, sumi->inputs[0]);
+      if (!sq || sq->kind != Kind::multiply || sq->inputs[0] != xf || sq->inputs[1] != xf) return false;
+      float scale = 0.f, eps = 0.f;
+      if (!scalar_f32(cscale, &scale) || !scalar_f32(ceps, &eps)) return false;
+      const uint32_t xs = xfi->inputs[0];
+      if (plan.values[xs].dtype != dt || plan.values[xs].dims != hv.dims) return false;
+      if ((int64_t)hv.dims[0] != seg.group[0].m || (int64_t)hv.dims[1] != seg.group[0].k || seg.group[0].lhs_k != 1 ||
+          (seg.group[0].m > 1 && seg.group[0].lhs_m != seg.group[0].k))
+        return false;
+      size_t matched = 11;  // top, wb, xn, mul32, xf, rb, rsqrt, add, mean, sum, square (+ broadcasts of the scalars)
+      for (uint32_t c : {cscale, ceps})
+        if (const Instruction* q = in_step(f, c)) matched += q->kind == Kind::broadcast_in_dim ? 1 : 100;
+      const Instruction* addx = in_step(f, xs);
+      uint32_t lhs_root;
+      if (!addx) {
+        if (f.outputs.size() != 1 || non_alias_nodes(f) != matched) return false;
+        lhs_root = kp->root[xs];
+      } else {
+        // x = a + b: one addend is the result of the previous contraction (read by nothing else), the other the residual.
+        if (addx->kind != Kind::add || non_alias_nodes(f) != matched + 1 || !p || p->segs.empty()) return false;
+        if (f.outputs.size() == 2 && std::find(f.outputs.begin(), f.outputs.end(), kp->root[xs]) == f.outputs.end()) return false;
+        if (f.outputs.size() == 1 && !class_users(kp->root[xs]).empty() && !subset_of(class_users(kp->root[xs]), f.nodes)) return false;
+        DotSeg& ps = p->segs.back();
+        int slot = -1;
+        uint32_t res = UINT32_MAX;
+        for (int sw = 0; sw < 2 && slot < 0; sw++) {
+          const uint32_t y = kp->root[addx->inputs[sw]], other = kp->root[addx->inputs[1 - sw]];
+          for (size_t j = 0; j < ps.out.size(); j++)
+            if (ps.out[j] == y && ps.residual[j] == UINT32_MAX && !is_output[y] &&
+                std::find(ps.out.begin(), ps.out.end(), other) == ps.out.end() && in_step(f, addx->inputs[1 - sw]) == nullptr &&
+                class_users(y) == std::vector<size_t>{(size_t)(addx - plan.instructions.data())}) {
+              slot = (int)j;
+              res = other;
+            }
+        }
+        if (slot < 0 || plan.values[res].dims != hv.dims || plan.values[res].dtype != dt) return false;
+        const DotShape& pd = ps.group[slot];
+        if (pd.m != (int64_t)hv.dims[0] || pd.n != (int64_t)hv.dims[1] || pd.out_m != pd.n) return false;
+        const uint32_t y = ps.out[slot];
+        lhs_root = kp->root[xs];
+        ps.residual[slot] = res;
+        ps.out[slot] = lhs_root;
+        replace_value(p->outputs, y, lhs_root);
+        add_unique(p->inputs, res);
+      }
+      seg.lhs = lhs_root;
+      seg.lhs2 = kp->root[w];
+      seg.lhs_desc.kind = kDotLhsRmsNorm;
+      seg.lhs_desc.norm_scale = scale;
+      seg.lhs_desc.norm_eps = eps;
+      replace_value(d.inputs, h, lhs_root);
+      add_unique(d.inputs, seg.lhs2);
+      return true;
+    };
+
+    std::vector<Step> fused;
+    for (size_t i = 0; i < kp->steps.size(); i++) {
+      Step& d = kp->steps[i];
+      if (!d.segs.empty() && !fused.empty() && fused.back().type == Step::kFused) {
+        Step* prev_dot = fused.size() >= 2 && !fused[fused.size() - 2].segs.empty() ? &fused[fused.size() - 2] : nullptr;
+        if (match_silu(fused.back(), d) || match_norm(fused.back(), d, prev_dot)) {
+          for (size_t n : fused.back().nodes) d.nodes.push_back(n);
+          fused.pop_back();
+        }
+      }
+      fused.push_back(std::move(d));
+    }
+    kp->steps = std::move(fused);
+
+    if (env_flag_local("PJRTX_B200_DOT_CHAIN", false)) {
+      std::vector<Step> chained;
+      for (Step& st : kp->steps) {
+        Step* prev = chained.empty() ? nullptr : &chained.back();
+        const bool can = prev && !prev->segs.empty() && !st.segs.empty() &&
+                         prev->segs.size() + st.segs.size() <= (size_t)kDotChainMax &&
+                         prev->segs[0].group[0].dtype == st.segs[0].group[0].dtype &&
+                         prev->segs[0].group[0].m == st.segs[0].group[0].m;
+        if (!can) {
+          chained.push_back(std::move(st));
+          continue;
+        }
+        for (DotSeg& sg : st.segs) prev->segs.push_back(std::move(sg));
+        for (size_t n : st.nodes) prev->nodes.push_back(n);
+        for (uint32_t v : st.inputs) add_unique(prev->inputs, v);
+        for (uint32_t v : st.outputs) add_unique(prev->outputs, v);
+      }
+      kp->steps = std::move(chained);
+    }
+    for (Step& st : kp->steps) {
+      if (st.segs.empty()) continue;
+      if (st.segs.size() == 1 && st.segs[0].lhs_desc.kind == kDotLhsPlain &&
+          std::all_of(st.segs[0].residual.begin(), st.segs[0].residual.end(), [](uint32_t r) { return r == UINT32_MAX; })) {
+        st.segs.clear();  // nothing folded in: the plain launch
+        continue;
+      }
+      std::vector<DotChainSegment> desc(st.segs.size());
+      for (size_t q = 0; q < st.segs.size(); q++) {
+        desc[q].count = (int)st.segs[q].group.size();
+        for (int g = 0; g < desc[q].count; g++) desc[q].shapes[g] = st.segs[q].group[g];
+        desc[q].lhs = st.segs[q].lhs_desc;
+        desc[q].norm_of_previous = q > 0 && st.segs[q - 1].out.size() == 1 && st.segs[q - 1].out[0] == st.segs[q].lhs;
+      }
+      st.chain_plan = dot_chain_plan(desc.data(), (int)desc.size(), sm_count);
+      st.dot_scratch.partial_bytes = st.chain_plan.partial_bytes;
+      st.dot_scratch.counter_bytes = st.chain_plan.counter_bytes;
+      st.dot_scratch.grid = st.chain_plan.grid;
+    }
+  }
+
   // Storage: parameters, constants, arena intervals for everything produced by a step.
   kp->storage.assign(nv, Storage{});
   for (size_t p = 0; p < kp->params.size(); p++) kp->storage[kp->params[p]] = Storage{Storage::kParameter, 0, (uint32_t)p};
@@ -1069,11 +1346,51 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
     for (Step& st : kp->steps) {
       if (st.type != Step::kDot) continue;
       bool ok = true;
-      for (size_t g = 1; g < st.inputs.size(); g++) {
-        const Storage& sg = kp->storage[st.inputs[g]];
-        ok &= (sg.kind == Storage::kParameter || sg.kind == Storage::kConstant) && !written.count(st.inputs[g]);
+      std::vector<uint32_t> weights;
+      if (st.segs.empty()) weights.assign(st.inputs.begin() + 1, st.inputs.end());
+      for (const DotSeg& sg : st.segs) weights.insert(weights.end(), sg.rhs.begin(), sg.rhs.end());
+      for (uint32_t wv : weights) {
+        const Storage& sg = kp->storage[wv];
+        ok &= (sg.kind == Storage::kParameter || sg.kind == Storage::kConstant) && !written.count(wv);
       }
       st.early_rhs = ok;
+    }
+  }
+  // Decode attention whose caches are only touched, earlier in the step, by the in-place write of the row at its own
+  // token index: the rows below that index hold what previous steps left, so the kernel may request them before its
+  // predecessor has finished. The token itself must be a parameter no step writes.
+  {
+    std::set<uint32_t> written;
+    for (const Step& st : kp->steps)
+      for (uint32_t r : st.outputs) written.insert(r);
+    for (size_t si = 0; si < kp->steps.size(); si++) {
+      Step& st = kp->steps[si];
+      if (st.type != Step::kAttnDecode || st.inputs.size() < 4) continue;
+      const uint32_t tok = st.inputs[3];
+      if (kp->storage[tok].kind != Storage::kParameter || written.count(tok)) continue;
+      bool ok = true;
+      for (int which = 1; which <= 2 && ok; which++) {
+        const uint32_t cache = st.inputs[which];
+        if (plan.values[cache].dims.size() != 4) ok = false;
+        for (size_t e = 0; e < si && ok; e++) {
+          const Step& w = kp->steps[e];
+          if (std::find(w.outputs.begin(), w.outputs.end(), cache) == w.outputs.end()) continue;
+          if (w.type != Step::kFused) ok = false;
+          for (size_t n : w.nodes) {
+            const Instruction& wi = plan.instructions[n];
+            bool touches = false;
+            for (uint32_t o : wi.outputs) touches |= kp->root[o] == cache;
+            if (!touches || !ok) continue;
+            if (wi.kind != Kind::dynamic_update_slice || wi.inputs.size() != 6) {
+              ok = false;
+              continue;
+            }
+            const Value& up = plan.values[wi.inputs[1]];
+            if (up.dims.size() != 4 || up.dims[1] != 1 || kp->root[wi.inputs[3]] != tok) ok = false;
+          }
+        }
+      }
+      st.early_kv = ok;
     }
   }
   // Scratch for split-K partials and their counters (counters first: they must start at zero).
@@ -1139,11 +1456,27 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
       s += strfmt(",\"path\":%d,\"tma\":%d,\"umma\":%d,\"grid\":%d,\"ksplit\":%d,\"b0\":%lld,\"b1\":%lld,\"m\":%lld,\"n\":%lld,\"k\":%lld,\"group\":%zu",
                   st.dot_scratch.path, st.dot_scratch.tma, st.dot_scratch.umma, st.dot_scratch.grid, st.dot_scratch.ksplit, (long long)st.dot.b0, (long long)st.dot.b1, (long long)st.dot.m,
                   n_total, (long long)st.dot.k, std::max<size_t>(st.dot_group.size(), 1));
+      long long weight_elems = 0;
+      if (st.segs.empty()) {
+        weight_elems = n_total * (long long)st.dot.k * st.dot.b0 * st.dot.b1;
+      } else {
+        s += strfmt(",\"segments\":%zu,\"lhs_kinds\":[", st.segs.size());
+        for (size_t q = 0; q < st.segs.size(); q++) {
+          s += strfmt(q ? ",%d" : "%d", st.segs[q].lhs_desc.kind);
+          for (const DotShape& d : st.segs[q].group) weight_elems += (long long)d.k * d.n;
+        }
+        s += "],\"residuals\":";
+        size_t residuals = 0;
+        for (const DotSeg& sg : st.segs)
+          for (uint32_t r : sg.residual) residuals += r != UINT32_MAX;
+        s += strfmt("%zu", residuals);
+      }
+      s += strfmt(",\"weight_elems\":%lld", weight_elems);
     } else if (st.type == Step::kSliceUpdate) {
       s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");
     } else if (st.type == Step::kAttnDecode) {
-      s += strfmt(",\"mma\":%d,\"splits\":%d,\"batch\":%lld,\"heads\":%lld,\"kv_heads\":%lld,\"kv_len\":%lld,\"head_dim\":%lld",
-                  st.attn_plan.mma, st.attn_plan.splits, st.attn.batch, st.attn.heads, st.attn.kv_heads, st.attn.kv_len, st.attn.head_dim);
+      s += strfmt(",\"mma\":%d,\"early_kv\":%d,\"splits\":%d,\"batch\":%lld,\"heads\":%lld,\"kv_heads\":%lld,\"kv_len\":%lld,\"head_dim\":%lld",
+                  st.attn_plan.mma, st.early_kv ? 1 : 0, st.attn_plan.splits, st.attn.batch, st.attn.heads, st.attn.kv_heads, st.attn.kv_len, st.attn.head_dim);
     } else if (st.type == Step::kAttnPrefill) {
       s += strfmt(",\"batch\":%lld,\"kv_heads\":%lld,\"rep\":%lld,\"seq\":%lld,\"head_dim\":%lld", st.attn_prefill.batch,
                   st.attn_prefill.kv_heads, st.attn_prefill.rep, st.attn_prefill.seq, st.attn_prefill.head_dim);
@@ -1244,10 +1577,23 @@ void collect_step_times(Executable* exe) {
 // `timed`: an event is recorded before every step and after the last one. Outside a stream capture the call then
 // waits and fills step_ms; inside a capture (`capturing`) the records become graph nodes and the caller reads the
 // times after it has launched the graph (collect_step_times).
+//
+// `ordered_first`: the first kernel of the call is launched without the programmatic-launch attribute. Outside a graph
+// the stream predecessor of that kernel belongs to other work (another executable that may still be writing a buffer
+// this one treats as a never-written weight, or this executable's previous run); a fully ordered first kernel makes
+// every later kernel of the call, which waits on its predecessor, ordered after that work too. A graph launch is
+// ordered as a whole, so captures do not need it.
 bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* launches, std::string* error,
-               bool timed = false, bool capturing = false) {
+               bool timed = false, bool capturing = false, bool ordered_first = false) {
   Device* dev = ds.dev;
   const KernelPlan& kp = exe->kp;
+  const bool pdl_setting = exe->pdl;
+  struct RestorePdl {
+    Executable* exe;
+    bool value;
+    ~RestorePdl() { exe->pdl = value; }
+  } restore{exe, pdl_setting};
+  const uint64_t launches_at_entry = *launches;
   if (timed) {
     while (exe->step_events.size() < kp.steps.size() + 1) {
       cudaEvent_t e;
@@ -1260,6 +1606,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
   for (const Step& st : kp.steps) {
     if (timed && step_index > 0) record_step_event(exe->step_events[step_index], dev->stream, capturing);
     step_index++;
+    exe->pdl = pdl_setting && !(ordered_first && *launches == launches_at_entry);
     switch (st.type) {
       case Step::kFused: {
         std::vector<void*> addr;
@@ -1289,7 +1636,26 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         void* partials = st.dot_scratch.partial_bytes ? (char*)ds.scratch + st.scratch_offset : nullptr;
         void* counters = st.dot_scratch.counter_bytes ? (char*)ds.scratch + st.counter_offset : nullptr;
         int n;
-        if (st.dot_group.size() > 1) {
+        if (!st.segs.empty()) {
+          DotChainSegment desc[kDotChainMax];
+          DotChainArgs cargs[kDotChainMax];
+          for (size_t q = 0; q < st.segs.size(); q++) {
+            const DotSeg& sg = st.segs[q];
+            desc[q].count = (int)sg.group.size();
+            desc[q].lhs = sg.lhs_desc;
+            desc[q].norm_of_previous = q > 0 && st.segs[q - 1].out.size() == 1 && st.segs[q - 1].out[0] == sg.lhs;
+            cargs[q].lhs = ptr.of(sg.lhs);
+            cargs[q].lhs2 = sg.lhs2 == UINT32_MAX ? nullptr : ptr.of(sg.lhs2);
+            for (size_t g = 0; g < sg.group.size(); g++) {
+              desc[q].shapes[g] = sg.group[g];
+              cargs[q].rhs[g] = ptr.of(sg.rhs[g]);
+              cargs[q].out[g] = ptr.of(sg.out[g]);
+              cargs[q].residual[g] = sg.residual[g] == UINT32_MAX ? nullptr : ptr.of(sg.residual[g]);
+            }
+          }
+          n = dot_chain_launch(desc, cargs, (int)st.segs.size(), st.chain_plan, partials, counters, dev->error_flag_dev,
+                               st.early_rhs, exe->pdl, dev->stream);
+        } else if (st.dot_group.size() > 1) {
           const void* rhs[kDotGroupMax];
           void* out[kDotGroupMax];
           for (size_t g = 0; g < st.dot_group.size(); g++) {
@@ -1327,15 +1693,31 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         (*launches)++;
         break;
       }
-      case Step::kAttnDecode:
+      case Step::kAttnDecode: {
+        // The contraction that follows streams weights nothing writes: let the attention CTAs ask for them.
+        const void* next_weights = nullptr;
+        uint64_t next_bytes = 0;
+        if (step_index < kp.steps.size()) {
+          const Step& nx = kp.steps[step_index];  // step_index already points past this step
+          if (nx.type == Step::kDot && nx.early_rhs && nx.dot.b0 * nx.dot.b1 == 1) {
+            const DotShape& d = nx.segs.empty() ? nx.dot : nx.segs[0].group[0];
+            const uint32_t w = nx.segs.empty() ? nx.inputs[1] : nx.segs[0].rhs[0];
+            if (d.rhs_n == 1 && d.rhs_k == d.n) {
+              next_weights = ptr.of(w);
+              next_bytes = std::min<uint64_t>((uint64_t)d.k * d.n * dtype_size(d.dtype), 48ull << 20);
+            }
+          }
+        }
         if (!attn_decode_launch(st.attn, st.attn_plan, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]),
                                 ptr.of(st.inputs[3]), ptr.of(st.outputs[0]), (char*)ds.scratch + st.scratch_offset,
-                                (char*)ds.scratch + st.counter_offset, exe->pdl, dev->stream)) {
+                                (char*)ds.scratch + st.counter_offset, exe->pdl, dev->stream, st.early_kv, dev->error_flag_dev,
+                                next_weights, next_bytes)) {
           *error = "attention kernel refused the shape";
           return false;
         }
         (*launches)++;
         break;
+      }
       case Step::kAttnPrefill:
         if (!attn_prefill_launch(st.attn_prefill, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]),
                                  ptr.of(st.outputs[0]), exe->pdl, dev->stream)) {
@@ -1643,7 +2025,7 @@ bool execute_executable(Executable* exe, size_t device_index, Buffer* const* arg
       ptr.fresh[r] = b->ptr;
       outs[o] = b;
     }
-    if (!run_steps(exe, ds, ptr, &launches, error, exe->profiling)) {
+    if (!run_steps(exe, ds, ptr, &launches, error, exe->profiling, false, /*ordered_first=*/true)) {
       cleanup();
       return false;
     }
@@ -1725,6 +2107,8 @@ ExecutableStats executable_stats(Executable* exe) {
   std::lock_guard<std::mutex> lock(exe->mu);
   return exe->stats;
 }
+
+std::vector<int> executable_device_ordinals(Executable* exe) { return exe->device_ordinals; }
 
 std::string executable_describe(Executable* exe) {
   return "{\"program\":" + describe_program(exe->kp.program) + ",\"kernel_plan\":" + describe_steps(exe->kp, false) + "}";

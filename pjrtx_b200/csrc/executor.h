@@ -49,6 +49,15 @@ struct ExecutableStats {
   uint64_t kernel_launch_total = 0;      // kernels enqueued since compile
 };
 
+// One segment of a chained streaming contraction (kernels.h, DotChainSegment): a group of contractions sharing an
+// lhs, with the lhs transform and the residuals the planner folded into it. Values are storage-class roots.
+struct DotSeg {
+  std::vector<DotShape> group;
+  uint32_t lhs = UINT32_MAX, lhs2 = UINT32_MAX;
+  DotLhs lhs_desc;
+  std::vector<uint32_t> rhs, out, residual;  // per contraction; residual UINT32_MAX = none
+};
+
 struct Step {
   enum Type { kFused, kDot, kSliceUpdate, kSdpa, kAllReduce, kAllGather, kCopy, kAttnDecode, kAttnPrefill } type = kFused;
   std::vector<size_t> nodes;        // plan instructions this step covers
@@ -59,10 +68,14 @@ struct Step {
   DotShape dot;
   std::vector<DotShape> dot_group;  // more than one entry: contractions sharing inputs[0], launched together
   DotScratch dot_scratch;
+  // Non-empty: the step runs as one launch of the chained streaming kernel (dot / dot_group describe its first segment).
+  std::vector<DotSeg> segs;
+  DotChainPlan chain_plan;
   uint64_t scratch_offset = 0, counter_offset = 0;
   SliceUpdateShape dus;
   bool in_place = false;
   bool early_rhs = false;  // every rhs of the contraction is a parameter or constant no step writes
+  bool early_kv = false;   // decode attention: cache rows below the token index are not written earlier in the step
   SdpaShape sdpa;
   AttnDecodeShape attn;
   AttnDecodePlan attn_plan;
@@ -92,6 +105,8 @@ Executable* compile_executable(const Plan& plan, const std::vector<int>& device_
 bool execute_executable(Executable* exe, size_t device_index, Buffer* const* args, size_t nargs,
                         std::vector<Buffer*>* outputs, std::string* error);
 ExecutableStats executable_stats(Executable* exe);
+// Device ordinals the executable was compiled for, in device-index order.
+std::vector<int> executable_device_ordinals(Executable* exe);
 // Per-step device times: when enabled, the next executions run the step list directly (no graph replay) with a
 // CUDA event pair around every step; step_times returns the durations of the latest such execution in
 // milliseconds, in step order (the reference prints the same information as `backend_schedule_item` profile

@@ -84,7 +84,28 @@ struct DecodeArgs {
   int splits;
   float* workspace;   // [batch * kv_heads][splits][REP][HD + 2]
   unsigned* counters;  // [batch * kv_heads]
+  int* error_flag;     // receives a non-zero code when a bounded wait gives up (may be null)
+  int early_kv;        // cache rows below the token index are not written by earlier work of the stream
+  // Weights of the contraction that follows (never written by the stream): requested into L2 by this kernel's CTAs as
+  // they start, so that HBM works through the attention step's latencies instead of idling.
+  const unsigned char* prefetch;
+  unsigned long long prefetch_bytes;
 };
+
+// Every CTA asks for its share of [prefetch, prefetch + prefetch_bytes) in 16 KiB bulk requests (no destination, no
+// completion to wait for).
+__device__ __forceinline__ void prefetch_next_weights(const DecodeArgs& a) {
+  if (!a.prefetch_bytes) return;
+  constexpr unsigned long long kPiece = 16384;
+  const unsigned long long pieces = (a.prefetch_bytes + kPiece - 1) / kPiece;
+  const unsigned long long cta = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+  const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+  for (unsigned long long i = cta * blockDim.x + threadIdx.x; i < pieces; i += ctas * blockDim.x) {
+    const unsigned long long at = i * kPiece;
+    const unsigned size = (unsigned)((a.prefetch_bytes - at < kPiece ? a.prefetch_bytes - at : kPiece) & ~15ull);
+    if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.prefetch + at), "r"(size) : "memory");
+  }
+}
 
 // Second half of a split: after every thread has written its part of this split's (max, sum, out) triple to the
 // workspace, the CTA that arrives last for the (sequence, KV head) merges all splits in split order and writes `out`.
@@ -170,7 +191,9 @@ template <typename T, int REP, int HD, int KPG, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                    const void* __restrict__ token, T* __restrict__ out) {
-  PJRTX_PDL_PROLOGUE();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  prefetch_next_weights(a);
+  if (!a.early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int V = Elem<T>::V;
   constexpr int LPK = HD / V;                  // lanes per key row
   constexpr int GPW = 32 / LPK;                // lane groups per warp
@@ -192,6 +215,21 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
   const long long per_split = (count + a.splits - 1) / a.splits;
   const long long j_begin = (long long)split * per_split;
   const long long j_end = min(j_begin + per_split, count);
+  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
+  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
+  if (a.early_kv) {
+    // Rows below the token index hold what earlier steps left: ask for the first chunk's rows now, so that they come
+    // from L2 once the predecessor (which writes the row at the token index, and the query) has finished.
+#pragma unroll
+    for (int u = 0; u < KPG; u++) {
+      const long long j = j_begin + group + (long long)u * GROUPS;
+      if (j < j_end && j < limit) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + j * a.kv_row_stride));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + j * a.kv_row_stride));
+      }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
 
   // Query slices of the `rep` heads that share this KV head.
   float qf[REP][V];
@@ -209,8 +247,6 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
 #pragma unroll
     for (int i = 0; i < V; i++) o[r][i] = 0.f;
   }
-  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
-  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride + gl * V;
 
   int parity = 0;
   for (long long c0 = j_begin; c0 < j_end; c0 += CHUNK, parity ^= 1) {  // same trip count for every thread of the CTA
@@ -316,6 +352,211 @@ attn_decode_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ 
   }
   if (a.splits == 1) return;
   merge_splits<T, REP, HD, WARPS * 32>(a, tile, b, g, &sm_o[0][0][0], &is_last, out);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Shared-memory staged variant for 16-bit caches and few (sequence, KV head) pairs: batch-1 decode.
+//
+// At batch 1 the whole cache of a step is a few megabytes and the kernel is a chain of latencies. The register-staged
+// kernel above keeps every K/V row of its split in registers (about 54 K registers per CTA), which also keeps the CTAs
+// of the following projection from becoming resident and requesting their weights while attention runs. Here the rows
+// of a split (at most kStagedKeys) are brought into shared memory by bulk asynchronous copies, one 16-byte-aligned row
+// slice per copy, all completing on one mbarrier; no register holds data in flight, the CTA needs about 10 K registers
+// and 75 KiB, and one CTA of the next streaming contraction fits beside it on the SM.
+//   phase 1  scores: a thread owns a key and REP / 2 query heads; K rows are read with 16-byte loads from rows padded
+//            by 16 bytes (conflict-free), the query slices come as broadcasts from an f32 copy in shared memory
+//   phase 2  softmax statistics: one warp per query head (max, exp, sum)
+//   phase 3  context: a thread owns two adjacent output elements of one head and walks the keys
+// Partial (max, sum, out) triples are merged across splits exactly as in the kernel above.
+// With `early_kv` the rows below the token index (which no earlier kernel of the step writes) are requested before
+// the kernel waits for its predecessor; only the row at the token index is requested after the wait.
+constexpr int kStagedKeys = 128;
+constexpr int kStagedThreads = 256;
+constexpr unsigned kStagedSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t attn_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <int REP, int HD> struct StagedLayout {
+  static constexpr int ROW = HD * 2 + 16;            // padded pitch of a K / V row in bytes
+  static constexpr int QROW = HD + 4;                // padded pitch of a query row in floats
+  static constexpr size_t k_off = 0;
+  static constexpr size_t v_off = (size_t)kStagedKeys * ROW;
+  static constexpr size_t q_off = 2 * (size_t)kStagedKeys * ROW;
+  static constexpr size_t s_off = q_off + (size_t)REP * QROW * sizeof(float);
+  static constexpr size_t s_floats = (size_t)REP * kStagedKeys > 64 * REP * 2 ? (size_t)REP * kStagedKeys : 64 * REP * 2;
+  static constexpr size_t ml_off = s_off + s_floats * sizeof(float);
+  static constexpr size_t bar_off = (ml_off + (size_t)REP * 2 * sizeof(float) + 15) / 16 * 16;
+  static constexpr size_t bytes = bar_off + 16;
+};
+
+template <typename T, int REP, int HD>
+__global__ void __launch_bounds__(kStagedThreads)
+attn_decode_staged_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                          const void* __restrict__ token, T* __restrict__ out) {
+  static_assert(sizeof(T) == 2, "16-bit caches");
+  using L = StagedLayout<REP, HD>;
+  constexpr int ROW = L::ROW, QROW = L::QROW;
+  constexpr int TPK = REP >= 2 ? 2 : 1;  // threads per key in the score phase
+  constexpr int HPT = REP / TPK;         // query heads per thread
+  extern __shared__ __align__(128) unsigned char smem_staged[];
+  unsigned char* ks = smem_staged + L::k_off;
+  unsigned char* vs = smem_staged + L::v_off;
+  float* qs = reinterpret_cast<float*>(smem_staged + L::q_off);
+  float* ss = reinterpret_cast<float*>(smem_staged + L::s_off);
+  float* ml = reinterpret_cast<float*>(smem_staged + L::ml_off);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem_staged + L::bar_off);
+  int* is_last = reinterpret_cast<int*>(bar + 1);
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  prefetch_next_weights(a);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(attn_smem_u32(bar)), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (!a.early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
+  long long limit = load_scalar(token, a.token_dtype);  // keys 0..limit are visible
+  if (limit >= a.kv_len) limit = a.kv_len - 1;
+  const long long count = limit + 1;
+  const long long per_split = (count + a.splits - 1) / a.splits;
+  const long long j_begin = (long long)split * per_split;
+  const long long j_end = min(j_begin + per_split, count);
+  const int n = (int)max(0ll, min(j_end - j_begin, (long long)kStagedKeys));
+  if (tid == 0 && n > 0)
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(attn_smem_u32(bar)), "r"(2 * n * HD * 2) : "memory");
+  __syncthreads();  // the barrier expects the bytes before any copy can complete on it
+  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride;
+  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride;
+  auto copy_row = [&](int i) {
+    const int row = i < n ? i : i - n;
+    const T* src = (i < n ? kb : vb) + (j_begin + row) * a.kv_row_stride;
+    unsigned char* dst = (i < n ? ks : vs) + (size_t)row * ROW;
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(attn_smem_u32(dst)),
+                 "l"(src), "r"(HD * 2), "r"(attn_smem_u32(bar))
+                 : "memory");
+  };
+  // Rows written by this step (the one at the token index) may only be read after the predecessor has finished.
+  for (int i = tid; i < 2 * n; i += kStagedThreads) {
+    const int row = i < n ? i : i - n;
+    if (!a.early_kv || j_begin + row < limit) copy_row(i);
+  }
+  if (a.early_kv) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = tid; i < 2 * n; i += kStagedThreads) {
+      const int row = i < n ? i : i - n;
+      if (j_begin + row >= limit) copy_row(i);
+    }
+  }
+  // Query slices of the heads that share this KV head, as f32.
+  for (int idx = tid; idx < REP * HD; idx += kStagedThreads) {
+    const int r = idx / HD, d = idx % HD;
+    qs[r * QROW + d] = (float)q[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d];
+  }
+  __syncthreads();
+  if (n > 0) {
+    bool arrived = false;
+    for (unsigned spin = 0; spin < kStagedSpinLimit && !arrived; spin++) {
+      unsigned ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(attn_smem_u32(bar)), "r"(0)
+          : "memory");
+      arrived = ok != 0;
+    }
+    if (!arrived) {
+      if (a.error_flag && lane == 0) atomicExch(a.error_flag, 3);
+      return;
+    }
+  }
+  // Phase 1: scores.
+  {
+    const int j = tid / TPK, hg = tid % TPK;
+    if (j < n) {
+      float acc[HPT];
+#pragma unroll
+      for (int h = 0; h < HPT; h++) acc[h] = 0.f;
+      const unsigned char* krow = ks + (size_t)j * ROW;
+#pragma unroll 4
+      for (int c = 0; c < HD / 8; c++) {
+        float kf[8];
+        Elem<T>::unpack(*reinterpret_cast<const uint4*>(krow + c * 16), kf);
+#pragma unroll
+        for (int h = 0; h < HPT; h++) {
+          const float4 q0 = *reinterpret_cast<const float4*>(qs + (hg * HPT + h) * QROW + c * 8);
+          const float4 q1 = *reinterpret_cast<const float4*>(qs + (hg * HPT + h) * QROW + c * 8 + 4);
+          acc[h] = fmaf(q0.x, kf[0], acc[h]); acc[h] = fmaf(q0.y, kf[1], acc[h]);
+          acc[h] = fmaf(q0.z, kf[2], acc[h]); acc[h] = fmaf(q0.w, kf[3], acc[h]);
+          acc[h] = fmaf(q1.x, kf[4], acc[h]); acc[h] = fmaf(q1.y, kf[5], acc[h]);
+          acc[h] = fmaf(q1.z, kf[6], acc[h]); acc[h] = fmaf(q1.w, kf[7], acc[h]);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < HPT; h++) {
+        float d = acc[h];
+        if (a.round_scores) d = Elem<T>::round(d);
+        ss[(hg * HPT + h) * kStagedKeys + j] = d * a.scale;
+      }
+    }
+  }
+  __syncthreads();
+  // Phase 2: per head maximum, probabilities relative to it, and their sum.
+  for (int r = warp; r < REP; r += kStagedThreads / 32) {
+    float m = -INFINITY;
+    for (int j = lane; j < n; j += 32) m = fmaxf(m, ss[r * kStagedKeys + j]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float l = 0.f;
+    for (int j = lane; j < n; j += 32) {
+      const float p = __expf(ss[r * kStagedKeys + j] - m);
+      ss[r * kStagedKeys + j] = p;
+      l += p;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    if (lane == 0) {
+      ml[r * 2] = m;
+      ml[r * 2 + 1] = l;
+    }
+  }
+  __syncthreads();
+  // Phase 3: context. A thread owns outputs (r, 2 * d2) and (r, 2 * d2 + 1).
+  const long long tile = (long long)b * a.kv_heads + g;
+  float* ws = a.workspace + (tile * a.splits + split) * (long long)REP * (HD + 2);
+  for (int pi = tid; pi < REP * HD / 2; pi += kStagedThreads) {
+    const int r = pi / (HD / 2), d2 = pi % (HD / 2);
+    float o0 = 0.f, o1 = 0.f;
+    const unsigned char* vcol = vs + d2 * 4;
+    const float* pr = ss + r * kStagedKeys;
+#pragma unroll 8
+    for (int j = 0; j < n; j++) {
+      const uint32_t raw = *reinterpret_cast<const uint32_t*>(vcol + (size_t)j * ROW);
+      const T* pair = reinterpret_cast<const T*>(&raw);
+      const float v0 = (float)pair[0], v1 = (float)pair[1];
+      const float p = pr[j];
+      o0 = fmaf(p, v0, o0);
+      o1 = fmaf(p, v1, o1);
+    }
+    const float l = ml[r * 2 + 1];
+    if (a.splits == 1) {
+      T* dst = out + b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + 2 * d2;
+      dst[0] = Elem<T>::store(l > 0.f ? o0 / l : 0.f);
+      dst[1] = Elem<T>::store(l > 0.f ? o1 / l : 0.f);
+      continue;
+    }
+    ws[r * (HD + 2) + 2 * d2] = o0;
+    ws[r * (HD + 2) + 2 * d2 + 1] = o1;
+    if (d2 == 0) {
+      ws[r * (HD + 2) + HD] = ml[r * 2];
+      ws[r * (HD + 2) + HD + 1] = l;
+    }
+  }
+  if (a.splits == 1) return;
+  __syncthreads();  // the merge scratch overlaps the probabilities
+  merge_splits<T, REP, HD, kStagedThreads>(a, tile, b, g, ss, is_last, out);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -593,11 +834,7 @@ int launch_decode_mma(const DecodeArgs& a, dim3 grid, const void* q, const void*
   constexpr size_t scratch_smem = (size_t)64 * REP * 2 * sizeof(float);
   constexpr size_t smem = stage_smem > merge_smem ? (stage_smem > scratch_smem ? stage_smem : scratch_smem)
                                                   : (merge_smem > scratch_smem ? merge_smem : scratch_smem);
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_mma_kernel<T, REP, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
-    configured = true;
-  }
+  if (!raise_smem_limit((const void*)attn_decode_mma_kernel<T, REP, HD>, (int)smem)) return 0;
   return launch_kernel(attn_decode_mma_kernel<T, REP, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q,
                        (const T*)k, (const T*)v, token, (T*)out) == cudaSuccess
              ? 1
@@ -610,6 +847,27 @@ int dispatch_decode_mma(int rep, int hd, const DecodeArgs& a, dim3 grid, const v
 #define CASE(R, H) \
   if (rep == R && hd == H) return launch_decode_mma<T, R, H>(a, grid, q, k, v, token, out, pdl, stream);
   CASE(4, 128) CASE(8, 128) CASE(4, 64) CASE(8, 64)
+#undef CASE
+  return 0;
+}
+
+template <typename T, int REP, int HD>
+int launch_decode_staged(const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out,
+                         bool pdl, cudaStream_t stream) {
+  constexpr size_t smem = StagedLayout<REP, HD>::bytes;
+  if (!raise_smem_limit((const void*)attn_decode_staged_kernel<T, REP, HD>, (int)smem)) return 0;
+  return launch_kernel(attn_decode_staged_kernel<T, REP, HD>, grid, dim3(kStagedThreads), smem, stream, pdl, a, (const T*)q,
+                       (const T*)k, (const T*)v, token, (T*)out) == cudaSuccess
+             ? 1
+             : 0;
+}
+
+template <typename T>
+int dispatch_decode_staged(int rep, int hd, const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v,
+                           const void* token, void* out, bool pdl, cudaStream_t stream) {
+#define CASE(R, H) \
+  if (rep == R && hd == H) return launch_decode_staged<T, R, H>(a, grid, q, k, v, token, out, pdl, stream);
+  CASE(1, 128) CASE(2, 128) CASE(4, 128) CASE(8, 128) CASE(1, 64) CASE(2, 64) CASE(4, 64) CASE(8, 64)
 #undef CASE
   return 0;
 }
@@ -850,11 +1108,7 @@ template <typename T, int HD>
 int launch_prefill_mma(const PrefillArgs& a, dim3 grid, const void* q, const void* k, const void* v, void* out, bool pdl,
                        cudaStream_t stream) {
   constexpr size_t smem = (size_t)kPrefillStages * 2 * kMmaStageKeys * HD * 2;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_prefill_mma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
-    configured = true;
-  }
+  if (!raise_smem_limit((const void*)attn_prefill_mma_kernel<T, HD>, (int)smem)) return 0;
   return launch_kernel(attn_prefill_mma_kernel<T, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q, (const T*)k,
                        (const T*)v, (T*)out) == cudaSuccess
              ? 1
@@ -886,6 +1140,23 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8);
   const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
   const bool large = tiles * s.kv_len >= (long long)sm_count * 256;  // measured: ahead from batch 4 at 2K keys, 8 KV heads
+  // Few (sequence, KV head) pairs of a 16-bit cache can run on the shared-memory staged kernel (one split per
+  // kStagedKeys keys at least, about one CTA per SM) with PJRTX_B200_ATTENTION_STAGED=1. The register-staged kernel
+  // stays the default: on the 8B-shape decode step it gives 3.50 ms per step against 3.53 ms.
+  const char* staged_env = getenv("PJRTX_B200_ATTENTION_STAGED");
+  const bool staged_on = staged_env && *staged_env && atoi(staged_env) != 0;
+  if (staged_on && !(force && *force) && !large && (s.dtype == kF16 || s.dtype == kBF16)) {
+    const long long need = (s.kv_len + kStagedKeys - 1) / kStagedKeys;
+    long long want = std::max<long long>(need, sm_count / std::max<long long>(tiles, 1));
+    if (const char* w = getenv("PJRTX_B200_ATTENTION_SPLITS")) want = std::max<long long>(need, atoi(w));  // experiments
+    if (need <= 64 && tiles * need <= 2ll * sm_count) {
+      p.mma = 2;
+      p.splits = (int)std::max<long long>(1, std::min<long long>(std::min<long long>(want, s.kv_len), 64));
+      p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
+      p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+      return p;
+    }
+  }
   p.mma = mma_ok && (force && *force ? atoi(force) != 0 : (rep == 8 || large)) ? 1 : 0;
   if (p.mma) {
     // Two CTAs per SM are resident: one wave of them, no more (measured at 4K keys, batch 32: 32 / 64 / 128 / 256
@@ -912,8 +1183,23 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
 }
 
 int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, const void* q, const void* k, const void* v,
-                       const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream) {
+                       const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream,
+                       bool early_kv, int* error_flag, const void* prefetch, uint64_t prefetch_bytes) {
   DecodeArgs a{};
+  a.error_flag = error_flag;
+  // Off unless PJRTX_B200_ATTENTION_PREFETCH=1: measured on the 8B-shape decode step, the 2048 bulk L2 requests for the
+  // 33 MB of the next projection double the attention kernel's time (18 -> 36 us) and the projection gains 3 us.
+  static const bool prefetch_allowed = [] {
+    const char* e = getenv("PJRTX_B200_ATTENTION_PREFETCH");
+    return e && *e && atoi(e) != 0;
+  }();
+  a.prefetch = prefetch_allowed && prefetch && (reinterpret_cast<uintptr_t>(prefetch) & 15) == 0 ? static_cast<const unsigned char*>(prefetch) : nullptr;
+  a.prefetch_bytes = a.prefetch ? prefetch_bytes : 0;
+  static const bool early_allowed = [] {
+    const char* e = getenv("PJRTX_B200_ATTENTION_EARLY_KV");
+    return !(e && *e && atoi(e) == 0);
+  }();
+  a.early_kv = early_kv && early_allowed ? 1 : 0;
   a.batch = s.batch;
   a.heads = s.heads;
   a.kv_heads = s.kv_heads;
@@ -931,6 +1217,10 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
   a.counters = static_cast<unsigned*>(counters);
   dim3 grid((unsigned)plan.splits, (unsigned)s.kv_heads, (unsigned)s.batch);
   const int rep = (int)(s.heads / s.kv_heads);
+  if (plan.mma == 2) {
+    if (s.dtype == kF16) return dispatch_decode_staged<__half>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
+    return dispatch_decode_staged<__nv_bfloat16>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
+  }
   if (plan.mma) {
     if (s.dtype == kF16) return dispatch_decode_mma<__half>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
     return dispatch_decode_mma<__nv_bfloat16>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);

@@ -422,6 +422,33 @@ int umma_eligible(const DotShape& s);
 DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_major);
 }  // namespace
 
+namespace {
+int tma_env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return v && *v ? atoi(v) : fallback;
+}
+
+// Budget of one launch for all of its device-side waits (PJRTX_B200_WAIT_TIMEOUT_MS, two seconds by default).
+unsigned long long tma_timeout_ns() {
+  static const unsigned long long ns = [] {
+    const int ms = tma_env_int("PJRTX_B200_WAIT_TIMEOUT_MS", 2000);
+    return (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+  }();
+  return ns;
+}
+
+// Ring depth and CTAs per SM of the TMA streaming kernel: two CTAs per SM with three 32 KiB stages each while the
+// cross-warp fold buffer is small (m <= 2 for 16-bit types), one CTA with a deeper ring otherwise.
+void tma_ring(int M, int V, int* stages, int* per_sm) {
+  const size_t red = (size_t)tma::kConsumerWarps * M * 32 * V * sizeof(float);
+  const bool two = red <= 16 * 1024;
+  *per_sm = two ? 2 : 1;
+  *stages = two ? 3 : (M <= 4 ? 5 : 4);
+  static const int env_stages = tma_env_int("PJRTX_B200_TMA_STAGES", 0);
+  if (env_stages >= 2 && env_stages <= 6) *stages = env_stages;
+}
+}  // namespace
+
 DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count, bool allow_tensor) {
   DotScratch p;
   p.path = 1;
@@ -441,15 +468,16 @@ DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count, bool 
     if (all_umma) return umma_plan(shapes, count, sm_count, false);
   }
   if (batch == 1) {
-    // Persistent TMA kernel: equal shares of (column tile, 64-row chunk) units per CTA.
+    // Persistent TMA kernel: equal shares of (column tile, row chunk) units per CTA, two CTAs per SM with a ring of
+    // 32 KiB stages each. Measured on the 8B-shape decode step (ms per step): two CTAs x 3 stages 3.50; one CTA x 5
+    // stages 3.67; two CTAs x 6 stages of 16 KiB 3.94; one CTA x 6 stages of 16 KiB 4.95.
     p.tma = 1;
     const int chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
     const int64_t units = tiles * chunks;
-    const size_t red = (size_t)tma::kConsumerWarps * M * 32 * V * sizeof(float);
-    const bool two_per_sm = red <= 16 * 1024;
-    p.stages = two_per_sm ? 3 : (M <= 4 ? 5 : 4);
-    // A fixed grid of one or two CTAs per SM; units are dealt out evenly (shares differ by at most one unit).
-    const int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(units, (int64_t)sm_count * (two_per_sm ? 2 : 1)));
+    int per_sm = 1;
+    tma_ring(M, V, &p.stages, &per_sm);
+    // A fixed grid of one (or two) CTAs per SM; units are dealt out evenly (shares differ by at most one unit).
+    const int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(units, (int64_t)sm_count * per_sm));
     p.grid = (int)ctas;
     p.per_cta = units / ctas;
     p.max_contrib = (int)((chunks + p.per_cta - 1) / p.per_cta) + 1;
@@ -486,79 +514,132 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-template <typename T, int M>
-int launch_tma_m(const tma::Params& prm, const tma::Maps& maps, const DotScratch& plan, bool pdl, cudaStream_t stream) {
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(tma::stream_tma_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 0;
-    configured = true;
-  }
+template <typename T, int M, bool EXTRAS>
+int launch_tma_m(const tma::Params& prm, const tma::Maps& maps, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+  if (!raise_smem_limit((const void*)tma::stream_tma_kernel<T, M, EXTRAS>, 200 * 1024)) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)plan.grid);
+  cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(tma::kThreads);
-  cfg.dynamicSmemBytes = plan.smem;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, tma::stream_tma_kernel<T, M>, prm, maps) == cudaSuccess ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tma::stream_tma_kernel<T, M, EXTRAS>, prm, maps) == cudaSuccess ? 1 : 0;
+}
+
+// Fills one segment of the kernel parameters (and its tensor maps) from a group of contractions sharing an lhs.
+template <typename T>
+bool fill_segment(const DotShape* shapes, int count, const DotLhs& lhs_desc, const void* lhs, const void* lhs2,
+                  const void* const* rhs, void* const* out, const void* const* residual, int max_contrib, float* partials,
+                  unsigned* counters, tma::Segment* sg, CUtensorMap* maps) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int COLS = 32 * V;
+  const DotShape& s = shapes[0];
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return false;
+  sg->lhs = lhs;
+  sg->lhs2 = lhs2;
+  sg->lhs_m = s.lhs_m;
+  sg->lhs_k = s.lhs_k;
+  sg->lhs_kind = lhs_desc.kind;
+  sg->norm_scale = lhs_desc.norm_scale;
+  sg->norm_eps = lhs_desc.norm_eps;
+  sg->m = (int)s.m;
+  sg->k = (int)s.k;
+  sg->count = count;
+  int tiles = 0;
+  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  for (int g = 0; g < count; g++) {
+    sg->tile_begin[g] = tiles;
+    tiles += (int)((shapes[g].n + COLS - 1) / COLS);
+    sg->out[g] = out[g];
+    sg->residual[g] = residual ? residual[g] : nullptr;
+    sg->n[g] = shapes[g].n;
+    cuuint64_t gdim[2] = {(cuuint64_t)shapes[g].n, (cuuint64_t)s.k};
+    cuuint64_t gstride[1] = {(cuuint64_t)shapes[g].rhs_k * sizeof(T)};
+    cuuint32_t box[2] = {(cuuint32_t)COLS, (cuuint32_t)tma::kUnitRows};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&maps[g], dt, 2, const_cast<void*>(rhs[g]), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  for (int g = count; g <= tma::kGroupMax; g++) sg->tile_begin[g] = tiles;
+  for (int g = count; g < tma::kGroupMax; g++) maps[g] = maps[0];
+  sg->chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
+  sg->units = (long long)tiles * sg->chunks;
+  sg->max_contrib = max_contrib;
+  sg->partials = partials;
+  sg->counters = counters;
+  sg->ssq_out = nullptr;
+  sg->ssq_in = nullptr;
+  sg->ssq_tiles = 0;
+  return true;
+}
+
+template <typename T>
+int launch_tma_params(tma::Params& p, const tma::Maps& maps, int m, int grid, int stages, size_t smem, int* error_flag,
+                      bool early_rhs, bool pdl, cudaStream_t stream) {
+  p.error_flag = error_flag;
+  p.timeout_ns = tma_timeout_ns();
+  p.stages = stages;
+  p.early_rhs = early_rhs ? 1 : 0;
+  static const int env_evict = tma_env_int("PJRTX_B200_TMA_EVICT_FIRST", 1);
+  p.evict_first = env_evict;
+  const int M = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8;
+  // The plain contraction (one segment, untransformed lhs, no residual) runs the kernel without the segment machinery.
+  bool extras = p.segments > 1 || p.seg[0].lhs_kind != tma::kLhsPlain;
+  for (int g = 0; g < p.seg[0].count; g++) extras |= p.seg[0].residual[g] != nullptr;
+#define GO(MM) (extras ? launch_tma_m<T, MM, true>(p, maps, grid, smem, pdl, stream) : launch_tma_m<T, MM, false>(p, maps, grid, smem, pdl, stream))
+  switch (M) {
+    case 1: return GO(1);
+    case 2: return GO(2);
+    case 4: return GO(4);
+    default: return GO(8);
+  }
+#undef GO
 }
 
 template <typename T>
 int launch_tma(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs, void* const* out,
                void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
-  constexpr int V = 16 / sizeof(T);
-  constexpr int COLS = 32 * V;
-  const DotShape& s = shapes[0];
-  EncodeTiledFn enc = encode_tiled();
-  if (!enc) return 0;
   tma::Params p{};
   tma::Maps maps{};
-  p.lhs = lhs;
-  p.lhs_m = s.lhs_m;
-  p.lhs_k = s.lhs_k;
-  p.m = (int)s.m;
-  p.k = (int)s.k;
-  p.batch = 1;
-  p.count = count;
-  int tiles = 0;
-  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                 : std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  for (int g = 0; g < count; g++) {
-    p.tile_begin[g] = tiles;
-    tiles += (int)((shapes[g].n + COLS - 1) / COLS);
-    p.rhs[g] = rhs[g];
-    p.out[g] = out[g];
-    p.n[g] = shapes[g].n;
-    p.ldb[g] = shapes[g].rhs_k;
-    cuuint64_t gdim[2] = {(cuuint64_t)shapes[g].n, (cuuint64_t)s.k};
-    cuuint64_t gstride[1] = {(cuuint64_t)shapes[g].rhs_k * sizeof(T)};
-    cuuint32_t box[2] = {(cuuint32_t)COLS, (cuuint32_t)tma::kUnitRows};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&maps.map[g], dt, 2, const_cast<void*>(rhs[g]), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+  p.segments = 1;
+  p.barrier = nullptr;
+  if (!fill_segment<T>(shapes, count, DotLhs{}, lhs, nullptr, rhs, out, nullptr, plan.max_contrib, static_cast<float*>(partials),
+                       static_cast<unsigned*>(counters), &p.seg[0], maps.map[0]))
+    return 0;
+  return launch_tma_params<T>(p, maps, (int)shapes[0].m, plan.grid, plan.stages, plan.smem, error_flag, early_rhs, pdl, stream);
+}
+
+template <typename T>
+int launch_chain(const DotChainSegment* segs, const DotChainArgs* args, int n, const DotChainPlan& plan, void* partials,
+                 void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
+  tma::Params p{};
+  tma::Maps maps{};
+  p.segments = n;
+  unsigned* words = static_cast<unsigned*>(counters);
+  p.barrier = words;  // the barrier words come first, then every segment's tile counters
+  for (int s = 0; s < n; s++) {
+    if (!fill_segment<T>(segs[s].shapes, segs[s].count, segs[s].lhs, args[s].lhs, args[s].lhs2, args[s].rhs, args[s].out,
+                         args[s].residual, plan.max_contrib[s], static_cast<float*>(partials),
+                         words + plan.counter_offset[s] / sizeof(unsigned), &p.seg[s], maps.map[s]))
       return 0;
   }
-  for (int g = count; g <= tma::kGroupMax; g++) p.tile_begin[g] = tiles;
-  for (int g = count; g < tma::kGroupMax; g++) maps.map[g] = maps.map[0];
-  p.chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
-  p.units = (long long)tiles * p.chunks;
-  p.per_cta = plan.per_cta;
-  p.max_contrib = plan.max_contrib;
-  p.partials = static_cast<float*>(partials);
-  p.counters = static_cast<unsigned*>(counters);
-  p.error_flag = error_flag;
-  p.stages = plan.stages;
-  p.early_rhs = early_rhs ? 1 : 0;
-  const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
-  switch (M) {
-    case 1: return launch_tma_m<T, 1>(p, maps, plan, pdl, stream);
-    case 2: return launch_tma_m<T, 2>(p, maps, plan, pdl, stream);
-    case 4: return launch_tma_m<T, 4>(p, maps, plan, pdl, stream);
-    default: return launch_tma_m<T, 8>(p, maps, plan, pdl, stream);
-  }
+  for (int s = 0; s + 1 < n; s++)
+    if (plan.ssq_offset[s]) {
+      float* ssq = reinterpret_cast<float*>(static_cast<unsigned char*>(counters) + plan.ssq_offset[s]);
+      p.seg[s].ssq_out = ssq;
+      p.seg[s + 1].ssq_in = ssq;
+      p.seg[s + 1].ssq_tiles = plan.tiles[s];
+    }
+  for (int s = n; s < tma::kSegmentMax; s++)
+    for (int g = 0; g < tma::kGroupMax; g++) maps.map[s][g] = maps.map[0][0];
+  return launch_tma_params<T>(p, maps, (int)segs[0].shapes[0].m, plan.grid, plan.stages, plan.smem, error_flag, early_rhs, pdl, stream);
 }
 
 
@@ -624,11 +705,7 @@ DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_maj
 
 template <int SUB, int NH>
 int launch_umma_sub(const umma::Params& prm, const umma::Maps& maps, const DotScratch& plan, bool pdl, cudaStream_t stream) {
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(umma::umma_stream_kernel<SUB, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return 0;
-    configured = true;
-  }
+  if (!raise_smem_limit((const void*)umma::umma_stream_kernel<SUB, NH>, 227 * 1024)) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)plan.grid);
   cfg.blockDim = dim3(umma::kThreads);
@@ -730,6 +807,66 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
 }
 
 }  // namespace
+
+bool dot_chain_eligible(const DotShape& s, int sm_count) {
+  if (s.b0 * s.b1 != 1) return false;
+  const DotScratch p = dot_plan(s, sm_count);
+  return p.path == 1 && p.tma == 1 && p.umma == 0;
+}
+
+DotChainPlan dot_chain_plan(const DotChainSegment* segs, int n, int sm_count) {
+  DotChainPlan p;
+  if (n < 1 || n > kDotChainMax) return p;
+  const DotShape& first = segs[0].shapes[0];
+  const int esize = (int)dtype_size(first.dtype);
+  const int V = 16 / esize;
+  const int M = first.m <= 1 ? 1 : first.m <= 2 ? 2 : first.m <= 4 ? 4 : 8;
+  int per_sm = 1;
+  tma_ring(M, V, &p.stages, &per_sm);
+  const bool two_per_sm = per_sm == 2;
+  p.smem = tma::smem_bytes(p.stages, M, 32 * V);
+  // Every CTA takes part in the barriers between segments, so the grid must be wholly resident, and every CTA must own
+  // at least one unit of every segment (the tile bookkeeping assumes consecutive, non-empty shares).
+  int64_t grid = (int64_t)sm_count * (two_per_sm ? 2 : 1);
+  int64_t tiles_all[kDotChainMax], chunks_all[kDotChainMax];
+  for (int s = 0; s < n; s++) {
+    int64_t tiles = 0;
+    for (int g = 0; g < segs[s].count; g++) tiles += (segs[s].shapes[g].n + 32 * V - 1) / (32 * V);
+    const int64_t chunks = (segs[s].shapes[0].k + tma::kUnitRows - 1) / tma::kUnitRows;
+    tiles_all[s] = tiles;
+    chunks_all[s] = chunks;
+    grid = std::min(grid, std::max<int64_t>(1, tiles * chunks));
+  }
+  p.grid = (int)grid;
+  p.segments = n;
+  uint64_t counters = (uint64_t)2 * kDotChainMax * sizeof(unsigned);  // barrier words
+  counters = (counters + 255) / 256 * 256;
+  for (int s = 0; s < n; s++) {
+    const int64_t per_cta = std::max<int64_t>(1, tiles_all[s] * chunks_all[s] / grid);
+    p.max_contrib[s] = (int)std::min<int64_t>(chunks_all[s], (chunks_all[s] + per_cta - 1) / per_cta + 1);
+    p.counter_offset[s] = counters;
+    p.tiles[s] = (int)tiles_all[s];
+    counters += ((uint64_t)tiles_all[s] * sizeof(unsigned) + 255) / 256 * 256;
+    if (s + 1 < n && segs[s + 1].norm_of_previous && segs[s + 1].lhs.kind == kDotLhsRmsNorm && segs[s].count == 1) {
+      p.ssq_offset[s] = counters;
+      counters += ((uint64_t)tiles_all[s] * M * sizeof(float) + 255) / 256 * 256;
+    }
+    p.partial_bytes = std::max<uint64_t>(p.partial_bytes, (uint64_t)tiles_all[s] * p.max_contrib[s] * M * 32 * V * sizeof(float));
+  }
+  p.counter_bytes = counters;
+  return p;
+}
+
+int dot_chain_launch(const DotChainSegment* segs, const DotChainArgs* args, int n, const DotChainPlan& plan, void* partials,
+                     void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
+  if (n < 1 || n > kDotChainMax || plan.segments != n) return 0;
+  switch (segs[0].shapes[0].dtype) {
+    case kF32: return launch_chain<float>(segs, args, n, plan, partials, counters, error_flag, early_rhs, pdl, stream);
+    case kF16: return launch_chain<__half>(segs, args, n, plan, partials, counters, error_flag, early_rhs, pdl, stream);
+    case kBF16: return launch_chain<__nv_bfloat16>(segs, args, n, plan, partials, counters, error_flag, early_rhs, pdl, stream);
+    default: return 0;
+  }
+}
 
 int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
                      void* const* out, void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl,

@@ -5,8 +5,25 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <mutex>
+#include <set>
+#include <utility>
 
 namespace pjrtx {
+
+// A kernel's dynamic shared-memory limit is an attribute of the (kernel, device) pair: raise it once for each device
+// the kernel is launched on (the current device of the calling thread).
+inline bool raise_smem_limit(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, device})) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  done.insert({kernel, device});
+  return true;
+}
 
 // Launch with (optionally) programmatic stream serialization: the kernel may begin while its predecessor in the stream
 // is still running; kernels call griddepcontrol.wait before their first dependent access.
@@ -73,6 +90,52 @@ int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, 
 
 // Chooses the kernel for a shape and sizes its scratch.
 DotScratch dot_plan(const DotShape& s, int sm_count);
+
+// ---- chained streaming contractions --------------------------------------------------------------------------------
+// A chain is a sequence of up to kDotChainMax segments run by ONE launch of the CUDA-core streaming kernel; a segment
+// is a group of up to kDotGroupMax contractions that share an lhs. A segment may read what earlier segments of the
+// chain wrote (the kernel separates segments with a grid-wide barrier while its weight copies run on). The lhs of a
+// segment can be transformed as it is loaded, and a contraction's result can take a residual:
+//   kDotLhsRmsNorm  lhs[m, k] = round(round(x[m, k] * rsqrt(sum_k(x[m, k]^2) * norm_scale + norm_eps)) * gain[k])
+//   kDotLhsSiluMul  lhs[m, k] = round(round(g[m, k] * round(logistic(g[m, k]))) * u[m, k])
+//   residual        out[m, n] = round(residual[m, n] + round(sum))
+// with `round` = rounding to the element type (what the op-by-op program does between instructions).
+constexpr int kDotChainMax = 4;
+enum DotLhsKind { kDotLhsPlain = 0, kDotLhsRmsNorm = 1, kDotLhsSiluMul = 2 };
+struct DotLhs {
+  int kind = kDotLhsPlain;
+  float norm_scale = 0.f, norm_eps = 0.f;
+};
+struct DotChainSegment {
+  DotShape shapes[kDotGroupMax];
+  int count = 0;
+  DotLhs lhs;
+  // rms_norm only: x is the (single) result of the previous segment of the chain. That segment then leaves the sum of
+  // squares of every column tile it completes, and this one adds those instead of reading the row again.
+  bool norm_of_previous = false;
+};
+struct DotChainArgs {
+  const void* lhs = nullptr;    // plain: operand; rms_norm: x; silu_mul: gate
+  const void* lhs2 = nullptr;   // rms_norm: gain; silu_mul: up
+  const void* rhs[kDotGroupMax] = {nullptr, nullptr, nullptr, nullptr};
+  void* out[kDotGroupMax] = {nullptr, nullptr, nullptr, nullptr};
+  const void* residual[kDotGroupMax] = {nullptr, nullptr, nullptr, nullptr};
+};
+struct DotChainPlan {
+  int segments = 0, grid = 0, stages = 0;
+  uint64_t smem = 0;
+  int max_contrib[kDotChainMax] = {};
+  uint64_t counter_offset[kDotChainMax] = {};  // byte offsets into the counter region (after the barrier words)
+  uint64_t ssq_offset[kDotChainMax] = {};      // per segment: where it leaves its tiles' sums of squares (0 = it does not)
+  int tiles[kDotChainMax] = {};
+  uint64_t partial_bytes = 0;   // one region shared by the segments (a segment's partials are consumed inside it)
+  uint64_t counter_bytes = 0;   // barrier words + every segment's tile counters; zero before the first launch
+};
+// True when the contraction runs on the CUDA-core streaming kernel (and can therefore join a chain).
+bool dot_chain_eligible(const DotShape& s, int sm_count);
+DotChainPlan dot_chain_plan(const DotChainSegment* segs, int n, int sm_count);
+int dot_chain_launch(const DotChainSegment* segs, const DotChainArgs* args, int n, const DotChainPlan& plan, void* partials,
+                     void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream);
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out,
                void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream);
 
@@ -80,6 +143,9 @@ int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const
 // array in the library image instead of an allocation. 1 on success, 0 with last_error set.
 int stream_dot_static_scratch(int device, int dtype, const void* lhs, const void* rhs, void* out, int64_t m, int64_t k,
                               int64_t n, cudaStream_t stream);
+// Waits for `stream` and reports whether the most recent static-scratch contraction on the device ran to completion
+// (1) or gave up a bounded device-side wait (0 with last_error set). Allocates nothing.
+int stream_dot_static_scratch_status(int device, cudaStream_t stream);
 
 // dynamic_update_slice: writes `update` into `dst` (already holding the operand)
 // at start indices read from device scalars, clamped as StableHLO requires.
@@ -117,13 +183,22 @@ struct AttnDecodeShape {
 };
 struct AttnDecodePlan {
   int splits = 1;
-  int mma = 0;  // 1: warp-level tensor-core kernel (16-bit caches), 0: CUDA-core kernel
+  // 0: CUDA-core kernel (rows held in registers), 1: warp-level tensor-core kernel (16-bit caches, many rows),
+  // 2: shared-memory staged kernel fed by bulk copies (16-bit caches, few (sequence, KV head) pairs)
+  int mma = 0;
   uint64_t workspace_bytes = 0, counter_bytes = 0;
 };
 bool attn_decode_supported(const AttnDecodeShape& s);
 AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count);
+// `early_kv`: no earlier kernel of the stream writes cache rows below the token index (a decode step appends the row
+// at the token index in place), so those rows may be requested before the preceding kernel has finished.
+// `error_flag` (device-visible int, may be null) receives a non-zero code if a bounded device-side wait gives up.
+// `prefetch` / `prefetch_bytes`: a 16-byte aligned range that no work of the stream writes (the weights of the
+// contraction that follows); the kernel's CTAs request it into L2 as they start.
 int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, const void* q, const void* k, const void* v,
-                       const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream);
+                       const void* token, void* out, void* workspace, void* counters, bool pdl, cudaStream_t stream,
+                       bool early_kv = false, int* error_flag = nullptr, const void* prefetch = nullptr,
+                       uint64_t prefetch_bytes = 0);
 
 // Causal self-attention over whole sequences (prefill) as one tensor-core kernel. q / out: [batch, kv_heads, seq, rep,
 // head_dim] contiguous (query head = kv head * rep + r); k / v: [batch, seq, kv_heads, head_dim] through the strides;

@@ -13,13 +13,18 @@
 // Every rank computes a part exactly once and everybody receives the same rounded values: results are bit-identical
 // across ranks and runs. Two sets of slots alternate with the step number: a rank can reach step s + 2 only after it
 // has received step s + 1 from everybody, which they send after finishing step s. The step number lives in the region
-// (advanced by the CTA that arrives last), so a captured launch replays correctly. Polls are bounded: on a timeout the
-// kernel raises the error word and carries on, so nothing hangs if a rank is missing. No kernel waits on another kernel
-// of the same GPU.
+// (advanced by the CTA that arrives last), so a captured launch replays correctly. Polls are bounded by TIME: a launch
+// gives its peers `timeout_ns` (two seconds unless PJRTX_B200_PEER_TIMEOUT_MS says otherwise) from the moment it starts;
+// the first thread that sees the deadline pass raises the error word (code 21) and tells its CTA, every other poll of
+// the launch then gives up at once, and the kernel finishes with whatever it has - an absent rank costs one timeout,
+// not one per element, and nothing hangs. The budget is also the skew the ranks may have when they reach a collective
+// (a rank still compiling or paused on the host for longer makes the others report the error). No kernel waits on
+// another kernel of the same GPU.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "../common.h"
 #include "kernels.h"
@@ -30,21 +35,28 @@ namespace {
 
 constexpr int kPeerMax = 8;
 constexpr unsigned kHeaderBytes = 4096;
-constexpr unsigned kSpinLimit = 1u << 22;
-
 struct PeerArgs {
   unsigned char* region[kPeerMax];
   int rank, world;
   unsigned long long slot_bytes;  // one slot: a part (1 / world of the data) in the 16-byte wire format
+  unsigned long long timeout_ns;  // budget of one launch for all its polls
   int* error_flag;
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void st_wire(void* p, unsigned d0, unsigned d1, unsigned step) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(step), "r"(d1), "r"(step) : "memory");
 }
-// Polls until both halves carry `step`; false on a timeout.
-__device__ __forceinline__ bool ld_wire(const void* p, unsigned step, unsigned* d0, unsigned* d1) {
-  for (unsigned spin = 0; spin < kSpinLimit; spin++) {
+// Polls until both halves carry `step`; false when the launch's deadline passed (seen by this thread, or by another
+// thread of the CTA that has set *gave_up).
+__device__ __forceinline__ bool ld_wire(const void* p, unsigned step, unsigned* d0, unsigned* d1, unsigned long long deadline,
+                                        volatile int* gave_up) {
+  for (unsigned spin = 0;; spin++) {
     unsigned a, fa, b, fb;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(p) : "memory");
     if (fa == step && fb == step) {
@@ -52,8 +64,14 @@ __device__ __forceinline__ bool ld_wire(const void* p, unsigned step, unsigned* 
       *d1 = b;
       return true;
     }
+    if ((spin & 63) == 63) {
+      if (*gave_up) return false;
+      if (global_timer_ns() > deadline) {
+        *gave_up = 1;
+        return false;
+      }
+    }
   }
-  return false;
 }
 
 template <typename T> struct Pair;  // 8 data bytes = two 32-bit words
@@ -103,6 +121,9 @@ template <typename T>
 __global__ void __launch_bounds__(256) peer_all_reduce_kernel(PeerArgs a, const uint2* __restrict__ in, uint2* __restrict__ out,
                                                               unsigned long long part_pairs) {
   PJRTX_PDL_PROLOGUE();
+  __shared__ int gave_up;
+  if (threadIdx.x == 0) gave_up = 0;
+  const unsigned long long deadline = global_timer_ns() + a.timeout_ns;
   unsigned* header = reinterpret_cast<unsigned*>(a.region[a.rank]);
   unsigned* arrive = header + 64;  // CTAs of this launch that have read the step number
   unsigned* step_word = header + 65;
@@ -138,7 +159,7 @@ __global__ void __launch_bounds__(256) peer_all_reduce_kernel(PeerArgs a, const 
     for (int q = 0; q < kPeerMax; q++)
       if (q < a.world) {
         unsigned d0 = 0, d1 = 0;
-        ok &= ld_wire(slot(a.rank, 0, q) + j, step, &d0, &d1);
+        ok &= ld_wire(slot(a.rank, 0, q) + j, step, &d0, &d1, deadline, &gave_up);
         Pair<T>::add(acc, d0, d1);
       }
     unsigned r0, r1;
@@ -154,7 +175,7 @@ __global__ void __launch_bounds__(256) peer_all_reduce_kernel(PeerArgs a, const 
     for (int p = 0; p < kPeerMax; p++)
       if (p < a.world && p != a.rank) {
         unsigned d0 = 0, d1 = 0;
-        ok &= ld_wire(slot(a.rank, 1, p) + j, step, &d0, &d1);
+        ok &= ld_wire(slot(a.rank, 1, p) + j, step, &d0, &d1, deadline, &gave_up);
         out[(unsigned long long)p * part_pairs + j] = make_uint2(d0, d1);
       }
   }
@@ -177,6 +198,12 @@ int peer_all_reduce_launch(void* const* regions, int rank, int world, uint64_t s
   a.world = world;
   a.slot_bytes = slot_bytes;
   a.error_flag = error_flag;
+  static const unsigned long long timeout_ms = [] {
+    const char* v = getenv("PJRTX_B200_PEER_TIMEOUT_MS");
+    const long long n = v && *v ? atoll(v) : 2000;
+    return (unsigned long long)(n < 1 ? 1 : n);
+  }();
+  a.timeout_ns = timeout_ms * 1000000ull;
   const unsigned long long part_pairs = bytes / world / 8;
   const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(64, (part_pairs + 255) / 256));
   cudaError_t e;

@@ -50,7 +50,7 @@ unsigned char* setup_device(int device) {
     return nullptr;
   }
 #define RAISE(T, M)                                                                                                          \
-  if ((e = cudaFuncSetAttribute(tma::stream_tma_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) !=   \
+  if ((e = cudaFuncSetAttribute(tma::stream_tma_kernel<T, M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) !=   \
       cudaSuccess) {                                                                                                         \
     set_last_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e));                                                       \
     return nullptr;                                                                                                          \
@@ -62,6 +62,19 @@ unsigned char* setup_device(int device) {
   g_scratch_address[device] = ptr;
   return ptr;
 }
+
+// Makes `device` current for the lifetime of the object and restores the caller's device afterwards.
+struct CurrentDevice {
+  int previous = -1;
+  bool ok = false;
+  explicit CurrentDevice(int device) {
+    if (cudaGetDevice(&previous) != cudaSuccess) previous = -1;
+    ok = cudaSetDevice(device) == cudaSuccess;
+  }
+  ~CurrentDevice() {
+    if (previous >= 0) cudaSetDevice(previous);
+  }
+};
 
 template <typename T>
 int launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, unsigned char* scratch,
@@ -76,41 +89,46 @@ int launch(const DotShape& s, const DotScratch& plan, const void* lhs, const voi
   }
   tma::Params p{};
   tma::Maps maps{};
-  p.lhs = lhs;
-  p.lhs_m = s.lhs_m;
-  p.lhs_k = s.lhs_k;
-  p.m = (int)s.m;
-  p.k = (int)s.k;
-  p.batch = 1;
-  p.count = 1;
+  p.segments = 1;
+  p.barrier = nullptr;
+  tma::Segment& sg = p.seg[0];
+  sg.lhs = lhs;
+  sg.lhs2 = nullptr;
+  sg.lhs_m = s.lhs_m;
+  sg.lhs_k = s.lhs_k;
+  sg.lhs_kind = tma::kLhsPlain;
+  sg.m = (int)s.m;
+  sg.k = (int)s.k;
+  sg.count = 1;
   const int tiles = (int)((s.n + COLS - 1) / COLS);
-  for (int g = 0; g <= tma::kGroupMax; g++) p.tile_begin[g] = g == 0 ? 0 : tiles;
-  p.rhs[0] = rhs;
-  p.out[0] = out;
-  p.n[0] = s.n;
-  p.ldb[0] = s.rhs_k;
+  for (int g = 0; g <= tma::kGroupMax; g++) sg.tile_begin[g] = g == 0 ? 0 : tiles;
+  sg.out[0] = out;
+  sg.residual[0] = nullptr;
+  sg.n[0] = s.n;
   const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : s.dtype == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   cuuint64_t gdim[2] = {(cuuint64_t)s.n, (cuuint64_t)s.k};
   cuuint64_t gstride[1] = {(cuuint64_t)s.rhs_k * sizeof(T)};
   cuuint32_t box[2] = {(cuuint32_t)COLS, (cuuint32_t)tma::kUnitRows};
   cuuint32_t estr[2] = {1, 1};
-  if (((EncodeTiledFn)fn)(&maps.map[0], dt, 2, const_cast<void*>(rhs), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  if (((EncodeTiledFn)fn)(&maps.map[0][0], dt, 2, const_cast<void*>(rhs), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
     set_last_error("tensor map encoding failed (rhs must be 16-byte aligned with a row pitch that is a multiple of 16 bytes)");
     return 0;
   }
-  for (int g = 1; g < tma::kGroupMax; g++) maps.map[g] = maps.map[0];
-  p.chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
-  p.units = (long long)tiles * p.chunks;
-  p.per_cta = plan.per_cta;
-  p.max_contrib = plan.max_contrib;
-  p.partials = reinterpret_cast<float*>(scratch);
-  p.counters = reinterpret_cast<unsigned*>(scratch + kStaticPartialBytes);
+  for (int q = 0; q < tma::kSegmentMax; q++)
+    for (int g = 0; g < tma::kGroupMax; g++) maps.map[q][g] = maps.map[0][0];
+  sg.chunks = (int)((s.k + tma::kUnitRows - 1) / tma::kUnitRows);
+  sg.units = (long long)tiles * sg.chunks;
+  sg.max_contrib = plan.max_contrib;
+  sg.partials = reinterpret_cast<float*>(scratch);
+  sg.counters = reinterpret_cast<unsigned*>(scratch + kStaticPartialBytes);
   p.error_flag = reinterpret_cast<int*>(scratch + kStaticPartialBytes + kStaticCounterBytes);
+  p.timeout_ns = tma::kDefaultTimeoutNs;
   p.stages = plan.stages;
   p.early_rhs = 0;
+  p.evict_first = 1;
   // The array keeps whatever the previous call left: counters and the error word must start at zero.
   if (cudaMemsetAsync(scratch + kStaticPartialBytes, 0, kStaticCounterBytes + 256, stream) != cudaSuccess) {
     set_last_error("clearing the static scratch counters failed");
@@ -118,7 +136,7 @@ int launch(const DotShape& s, const DotScratch& plan, const void* lhs, const voi
   }
   const int M = s.m <= 1 ? 1 : s.m <= 2 ? 2 : s.m <= 4 ? 4 : 8;
   cudaError_t e;
-#define GO(MM) tma::stream_tma_kernel<T, MM><<<plan.grid, tma::kThreads, plan.smem, stream>>>(p, maps)
+#define GO(MM) tma::stream_tma_kernel<T, MM, false><<<plan.grid, tma::kThreads, plan.smem, stream>>>(p, maps)
   if (M == 1) GO(1); else if (M == 2) GO(2); else if (M == 4) GO(4); else GO(8);
 #undef GO
   e = cudaGetLastError();
@@ -147,16 +165,15 @@ int stream_dot_static_scratch(int device, int dtype, const void* lhs, const void
     set_last_error("static-scratch contraction needs 1 <= m <= 8, k >= 1, n a multiple of %d, and 16-byte aligned rhs/out", V);
     return 0;
   }
-  if (cudaSetDevice(device) != cudaSuccess) {
+  CurrentDevice scope(device);  // the caller's current device is put back when the call returns
+  if (!scope.ok) {
     set_last_error("cudaSetDevice(%d) failed", device);
     return 0;
   }
   unsigned char* scratch = setup_device(device);
   if (!scratch) return 0;
-  cudaDeviceProp prop;
   int sm_count = 148;
   if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sm_count = 148;
-  (void)prop;
   DotShape s;
   s.dtype = dtype;
   s.m = m;
@@ -180,6 +197,36 @@ int stream_dot_static_scratch(int device, int dtype, const void* lhs, const void
     case kF16: return launch<__half>(s, plan, lhs, rhs, out, scratch, stream);
     default: return launch<__nv_bfloat16>(s, plan, lhs, rhs, out, scratch, stream);
   }
+}
+
+// The kernel's bounded waits report through an error word inside the static array (the call clears it before the
+// launch). Reading it back is one 4-byte copy into a stack variable followed by a wait on the caller's stream: no
+// allocation here either.
+int stream_dot_static_scratch_status(int device, cudaStream_t stream) {
+  if (device < 0 || device >= kMaxDevices) {
+    set_last_error("device ordinal %d is out of range", device);
+    return 0;
+  }
+  CurrentDevice scope(device);
+  if (!scope.ok) {
+    set_last_error("cudaSetDevice(%d) failed", device);
+    return 0;
+  }
+  unsigned char* scratch = setup_device(device);
+  if (!scratch) return 0;
+  int code = 0;
+  cudaError_t e = cudaMemcpyAsync(&code, scratch + kStaticPartialBytes + kStaticCounterBytes, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) {
+    set_last_error("reading the static-scratch status failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  if (code != 0) {
+    set_last_error("the last static-scratch contraction on device %d gave up a bounded wait (code %d); its output is not valid",
+                   device, code);
+    return 0;
+  }
+  return 1;
 }
 
 }  // namespace pjrtx

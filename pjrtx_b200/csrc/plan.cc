@@ -347,11 +347,15 @@ struct Fnv {
 };
 }  // namespace
 
-std::string plan_fingerprint(const Plan& plan, const char* backend_name, uint64_t custom_call_registry_version) {
+std::string plan_fingerprint(const Plan& plan, const char* backend_name, uint64_t custom_call_registry_version,
+                             const std::vector<int32_t>& target_devices) {
   Fnv f;
-  f.str("pjrtx-b200-executable-cache-v1");
+  f.str("pjrtx-b200-executable-cache-v2");
   f.str(backend_name ? backend_name : "");
   f.pod(custom_call_registry_version);
+  // Target devices (src/runtime/executable_fingerprint.zig:38-56 hashes the resolved device ids and their local
+  // hardware ids even when the plan carries no assignment): the same plan compiled for another GPU is another entry.
+  f.list(target_devices);
   f.pod(plan.num_replicas);
   f.pod(plan.num_partitions);
   f.pod(plan.use_shardy);

@@ -115,10 +115,11 @@ std::string verify_plan(const Plan& plan);
 std::string describe_plan(const Plan& plan);
 
 // Stable cache key of a plan for a backend state: "pjrtx-<16 hex digits>" over a version tag, the backend name, the
-// custom-call registry version, the compile options, shardings, donation and every value and instruction (kinds,
-// operands, attributes, constant payloads, call targets). Same fields as the reference's executable-cache fingerprint
-// (src/runtime/executable_fingerprint.zig:9-140); the hash function differs (64-bit FNV-1a), so keys are not
-// interchangeable with the reference's.
-std::string plan_fingerprint(const Plan& plan, const char* backend_name, uint64_t custom_call_registry_version);
+// custom-call registry version, the ordinals of the devices the executable is compiled for, the compile options,
+// shardings, donation and every value and instruction (kinds, operands, attributes, constant payloads, call targets).
+// Same fields as the reference's executable-cache fingerprint (src/runtime/executable_fingerprint.zig:9-140; target
+// devices :38-56); the hash function differs (64-bit FNV-1a), so keys are not interchangeable with the reference's.
+std::string plan_fingerprint(const Plan& plan, const char* backend_name, uint64_t custom_call_registry_version,
+                             const std::vector<int32_t>& target_devices = {});
 
 }  // namespace pjrtx

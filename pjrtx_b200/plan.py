@@ -237,6 +237,17 @@ class PlanBuilder:
         dims[dimension] = sum(p.dims[dimension] for p in parts)
         return self._emit("concatenate", list(parts), parts[0].dtype, dims, {"dimension": [dimension], "dims": dims})
 
+    def pad(self, a: Val, padding_value: Val, low: Sequence[int], high: Sequence[int],
+            interior: Optional[Sequence[int]] = None) -> Val:
+        """stablehlo.pad: edge padding (negative = cropping) and interior padding with a scalar value."""
+        interior = list(interior) if interior is not None else [0] * len(a.dims)
+        dims = []
+        for d, lo, hi, gap in zip(a.dims, low, high, interior):
+            span = 0 if d == 0 else (d - 1) * (gap + 1) + 1
+            dims.append(max(0, lo + span + hi))
+        return self._emit("pad", [a, padding_value], a.dtype, dims,
+                          {"edge_padding_low": list(low), "edge_padding_high": list(high), "interior_padding": interior})
+
     def iota(self, dtype: int, dims: Sequence[int], iota_dimension: int) -> Val:
         return self._emit("iota", [], dtype, dims, {"iota_dimension": [iota_dimension], "dims": dims})
 

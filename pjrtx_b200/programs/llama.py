@@ -71,34 +71,67 @@ def _is_linear(name: str) -> bool:
     return name.split(".")[-1] in LINEAR
 
 
-def make_weights(cfg: LlamaConfig, seed: int = 0, threads: int = 8) -> Dict[str, np.ndarray]:
+def to_storage(x: np.ndarray, dtype_code: int) -> np.ndarray:
+    """float32 -> storage dtype (round to nearest even)."""
+    return x.astype(P.np_dtype(dtype_code))
+
+
+_BLOCK_ELEMS = 1 << 22  # tensors are generated in row blocks of about this many elements, one RNG stream per block
+
+
+def _row_blocks(shape) -> List[Tuple[int, int]]:
+    rows = shape[0] if len(shape) > 1 else 1
+    per_row = int(np.prod(shape[1:], dtype=np.int64)) if len(shape) > 1 else int(shape[0])
+    step = max(1, _BLOCK_ELEMS // max(per_row, 1))
+    return [(r, min(r + step, rows)) for r in range(0, rows, step)]
+
+
+def make_weights(cfg: LlamaConfig, seed: int = 0, threads: int = 8, embed_period: int = 0) -> Dict[str, np.ndarray]:
     """Random-init weights ~N(0, 0.02) in the storage dtype (norm gains are 1 + N(0, 0.02)).
 
-    Each tensor draws from its own `default_rng([seed, index])`, so the values do not depend on how many
-    threads generate them. With `int8_weights` linear weights are s8 ~U{-127..127} and `<name>.scale` holds
-    per-output-channel f16 scales ~U(0.001, 0.01).
+    `embed_period` > 0 fills the embedding table with a block of that many random rows repeated down the table (a
+    decode step reads `batch` rows of it; full-width tests use this to keep host-side generation short).
+
+    Each row block of each tensor draws from its own `default_rng([seed, index, block])`, so the values do not depend
+    on how many threads generate them. With `int8_weights` linear weights are s8 ~U{-127..127} and `<name>.scale`
+    holds per-output-channel f16 scales ~U(0.001, 0.01).
     """
     dt = P.np_dtype(cfg.dtype)
     shapes = weight_shapes(cfg)
     out: Dict[str, np.ndarray] = {}
+    jobs = []
+    for index, (name, shape) in enumerate(shapes):
+        quant = cfg.int8_weights and _is_linear(name)
+        out[name] = np.empty(shape, dtype=np.int8 if quant else dt)
+        if quant:
+            out[name + ".scale"] = np.random.default_rng([seed, index, 1 << 20]).uniform(0.001, 0.01, size=(shape[-1],)).astype(np.float16)
+        gen_shape = shape
+        if name == "embed" and embed_period and embed_period < shape[0]:
+            gen_shape = (embed_period,) + tuple(shape[1:])
+        for block, (r0, r1) in enumerate(_row_blocks(gen_shape)):
+            jobs.append((index, name, shape, quant, block, r0, r1))
 
-    def gen(item):
-        index, (name, shape) = item
-        rng = np.random.default_rng([seed, index])
-        if cfg.int8_weights and _is_linear(name):
-            w = rng.integers(-127, 128, size=shape, dtype=np.int8)
-            s = rng.uniform(0.001, 0.01, size=(shape[-1],)).astype(np.float16)
-            return name, w, s
-        w = rng.standard_normal(size=shape, dtype=np.float32) * np.float32(0.02)
+    def gen(job):
+        index, name, shape, quant, block, r0, r1 = job
+        rng = np.random.default_rng([seed, index, block])
+        sub = (r1 - r0,) + tuple(shape[1:]) if len(shape) > 1 else tuple(shape)
+        dst = out[name][r0:r1] if len(shape) > 1 else out[name]
+        if quant:
+            dst[...] = rng.integers(-127, 128, size=sub, dtype=np.int8)
+            return
+        w = rng.standard_normal(size=sub, dtype=np.float32)
+        w *= np.float32(0.02)
         if name.endswith("norm"):
-            w = w + np.float32(1.0)
-        return name, w.astype(dt), None
+            w += np.float32(1.0)
+        dst[...] = to_storage(w, cfg.dtype)
 
     with ThreadPoolExecutor(max_workers=max(1, threads)) as pool:
-        for name, w, s in pool.map(gen, enumerate(shapes)):
-            out[name] = w
-            if s is not None:
-                out[name + ".scale"] = s
+        list(pool.map(gen, jobs))
+    if embed_period and "embed" in out and embed_period < out["embed"].shape[0]:
+        table = out["embed"]
+        for r0 in range(embed_period, table.shape[0], embed_period):
+            n = min(embed_period, table.shape[0] - r0)
+            table[r0:r0 + n] = table[:n]
     return out
 
 
@@ -111,7 +144,7 @@ def make_kv_cache(cfg: LlamaConfig, batch: int, max_len: int, filled: int, seed:
             rng = np.random.default_rng([seed, l, which])
             c = np.zeros((batch, max_len, cfg.kv_heads, cfg.head_dim), dtype=dt)
             if filled:
-                c[:, :filled] = rng.standard_normal(size=(batch, filled, cfg.kv_heads, cfg.head_dim), dtype=np.float32).astype(dt)
+                c[:, :filled] = to_storage(rng.standard_normal(size=(batch, filled, cfg.kv_heads, cfg.head_dim), dtype=np.float32), cfg.dtype)
             caches.append(c)
     return caches
 
@@ -275,8 +308,9 @@ def build_decode_step(cfg: LlamaConfig, batch: int, max_len: int, num_partitions
     return b, names
 
 
-def build_prefill(cfg: LlamaConfig, batch: int, seq: int, last_only_logits: bool = True) -> Tuple[PlanBuilder, List[str]]:
-    """Prefill: (tokens[B,S], weights...) -> (next_token[B], k/v caches [B,S,G,hd] per layer).
+def build_prefill(cfg: LlamaConfig, batch: int, seq: int, last_only_logits: bool = True,
+                  return_logits: bool = False) -> Tuple[PlanBuilder, List[str]]:
+    """Prefill: (tokens[B,S], weights...) -> (next_token[B], [logits], k/v caches [B,S,G,hd] per layer).
 
     Causal attention is written as dot_general scores → masked softmax (max / sum reductions) → dot_general
     context, and the whole KV cache is an output. The LM head runs on the last position only when
@@ -330,5 +364,5 @@ def build_prefill(cfg: LlamaConfig, batch: int, seq: int, last_only_logits: bool
     else:
         logits = e.linear(e.rms_norm(x, params["final_norm"]), params["lm_head"], None)  # [B, S, V]
         _, next_token = b.argmax(logits, 2)
-    b.set_outputs([next_token] + outs_cache)
+    b.set_outputs([next_token] + ([logits] if return_logits else []) + outs_cache)
     return b, names

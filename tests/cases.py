@@ -284,6 +284,27 @@ def structural_ops():
     return b, [cube, table, ids, start, upd]
 
 
+def pad_cases():
+    """stablehlo.pad: edge padding, interior padding, cropping by negative edges, a padded value feeding more work
+    (src/backend/mlx_metal/api.cc:2637 is the reference's pad; api.h:310-313 its arguments)."""
+    b = PlanBuilder()
+    cube = F32_CUBE
+    row = np.array([1, 2, 3, 4, 5], np.int32)
+    pc, pr = _params(b, [cube, row])
+    fill = b.constant(np.float32(-7.5))
+    ifill = b.constant(np.int32(9))
+    edge = b.pad(pc, fill, [1, 0, 2], [0, 2, 1])
+    outs = [
+        edge,
+        b.pad(pc, fill, [0, 1, 0], [1, 0, 0], [1, 0, 2]),
+        b.pad(pr, ifill, [-1], [3], [1]),          # crops the first element, spreads the rest, pads the tail
+        b.pad(pr, ifill, [2], [-2]),
+        b.reduce("reduce_sum", edge * 2.0, [2]),
+    ]
+    b.set_outputs(outs)
+    return b, [cube, row]
+
+
 def matmul_small(dtype=P.F32):
     b = PlanBuilder()
     dt = P.np_dtype(dtype)

@@ -175,3 +175,17 @@ def test_compile_needs_a_device(cache):
         cache.compile(b)
     s = cache.stats()
     assert s["misses"] == 1 and s["resident_entries"] == 0
+
+
+def test_fingerprint_covers_the_target_devices():
+    """src/runtime/executable_fingerprint.zig:38-56 hashes the resolved target devices: the same plan for another GPU
+    (or another device list) is another cache entry, and the key is stable for equal lists."""
+    from tests import cases
+
+    backend = be.Backend()
+    b, _ = cases.u8_chain()
+    on0 = backend.plan_fingerprint(b, [0])
+    assert on0 == backend.plan_fingerprint(b, [0])
+    assert on0 != backend.plan_fingerprint(b, [1])
+    assert len({on0, backend.plan_fingerprint(b, [1]), backend.plan_fingerprint(b, [0, 1]), backend.plan_fingerprint(b, [1, 0]),
+                backend.plan_fingerprint(b)}) == 5

@@ -58,6 +58,38 @@ def test_tiny_decode_steps_teacher_forced(gpu_backend, batch):
     print(f"logits max-abs error over 4 steps: {worst:.4e}")
 
 
+@pytest.mark.parametrize("batch,chain", [(1, False), (2, False), (1, True), (2, True)])
+def test_tiny_decode_with_transforms_folded_into_the_contractions(gpu_backend, monkeypatch, batch, chain):
+    """The optional plan in which RMSNorm / SiLU run as lhs transforms of the streaming contractions and the residual
+    additions as their epilogues, as separate launches and chained into one launch per layer (grid barriers between the
+    segments): three teacher-forced steps against the oracle, replayed from one captured graph."""
+    monkeypatch.setenv("PJRTX_B200_DOT_FUSE", "1")
+    monkeypatch.setenv("PJRTX_B200_DOT_CHAIN", "1" if chain else "0")
+    be = gpu_backend
+    cfg = llama.TINY
+    max_len, filled = 64, 40
+    builder, names = llama.build_decode_step(cfg, batch, max_len, return_logits=True)
+    weights = llama.make_weights(cfg, seed=0)
+    caches = llama.make_kv_cache(cfg, batch, max_len, filled)
+    exe = be.compile_executable(builder, [0])
+    dots = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
+    assert any(s.get("segments", 1) == (4 if chain else 1) and 1 in s.get("lhs_kinds", []) for s in dots), dots
+    assert sum(s.get("residuals", 0) for s in dots) == 2 * cfg.layers
+    wbufs = [be.buffer_from_host(weights[n]) for n in names[2:2 + len(weights)]]
+    cbufs = [be.buffer_from_host(c) for c in caches]
+    tokens = np.arange(3, 3 + batch, dtype=np.int32)
+    oracle_caches = caches
+    for step in range(3):
+        pos = filled + step
+        want = run_oracle(builder, _decode_args(cfg, names, weights, oracle_caches, tokens, pos))
+        outs = be.execute_executable(exe, [be.buffer_from_host(tokens), be.buffer_from_host(np.array(pos, np.int32))] + wbufs + cbufs)
+        assert_close(outs[1].to_numpy(), want[1], 2e-2, what=f"chain={chain} batch {batch} step {step} logits")
+        cbufs = outs[2:]
+        oracle_caches = want[2:]
+        tokens = want[0]
+    assert exe.stats()["graph_capture_count"] == 1
+
+
 def test_argmax_of_decode_is_bit_exact_on_identical_logits(gpu_backend):
     """Greedy choice on the oracle's own logits must be the oracle's token, ties included."""
     from pjrtx_b200 import PlanBuilder

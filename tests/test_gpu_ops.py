@@ -18,7 +18,7 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 CASES = ["dot_rhs_transposed", "dot_batched", "attention_scores_context", "argmax_ties", "sdpa_single", "sdpa_gqa",
          "elementwise_float_chain", "reshape_transpose_broadcast", "reduce_cases", "float_unary_math", "is_finite_case",
-         "int_ops", "i8_negate_sub", "predicate_logic", "structural_ops", "matmul_small"]
+         "int_ops", "i8_negate_sub", "predicate_logic", "structural_ops", "pad_cases", "matmul_small"]
 
 
 @pytest.mark.parametrize("name", CASES)
@@ -326,13 +326,27 @@ def test_buffer_round_trip_and_errors(gpu_backend):
     ("mma", P.BF16_CODE, 16, 2, 128, 150),
     ("cuda", P.F16, 16, 2, 64, 200),
     ("cuda", P.F32, 8, 4, 64, 100),
+    ("staged", P.BF16_CODE, 32, 8, 128, 300),
+    ("staged3", P.BF16_CODE, 32, 8, 128, 384),
+    ("staged", P.F16, 16, 2, 64, 200),
+    ("staged", P.BF16_CODE, 16, 2, 128, 150),
+    ("staged", P.BF16_CODE, 8, 8, 128, 130),
+    ("staged", P.F16, 4, 2, 64, 260),
 ])
 def test_decode_attention_every_visible_length(gpu_backend, monkeypatch, kernel, dtype, heads, kv_heads, hd, kv_len):
     """Split-KV decode attention with Llama-like head shapes: every visible length from 1 to the buffer size, so every
     ragged split of the key range is exercised (decode-shaped SDPA call: one query position). Both the CUDA-core and
-    the warp-level tensor-core kernel, 4 and 8 query heads per KV head, head sizes 64 and 128."""
+    the warp-level tensor-core kernel, 4 and 8 query heads per KV head, head sizes 64 and 128; and the shared-memory
+    staged kernel (PJRTX_B200_ATTENTION_STAGED=1) with 1, 2, 4 and 8 query heads per KV head, once with three splits
+    of up to 128 keys (a full stage)."""
     be = gpu_backend
-    monkeypatch.setenv("PJRTX_B200_ATTENTION_MMA", "1" if kernel == "mma" else "0")
+    if kernel.startswith("staged"):
+        monkeypatch.delenv("PJRTX_B200_ATTENTION_MMA", raising=False)
+        monkeypatch.setenv("PJRTX_B200_ATTENTION_STAGED", "1")
+        if kernel == "staged3":
+            monkeypatch.setenv("PJRTX_B200_ATTENTION_SPLITS", "3")
+    else:
+        monkeypatch.setenv("PJRTX_B200_ATTENTION_MMA", "1" if kernel == "mma" else "0")
     rng = np.random.default_rng(23)
     dt = P.np_dtype(dtype)
     batch = 2
@@ -346,7 +360,9 @@ def test_decode_attention_every_visible_length(gpu_backend, monkeypatch, kernel,
     exe = be.compile_executable(b, [0])
     steps = exe.describe()["kernel_plan"]["steps"]
     assert [s["type"] for s in steps] == ["attention_decode"]
-    assert steps[0]["mma"] == (1 if kernel == "mma" else 0)
+    assert steps[0]["mma"] == {"cuda": 0, "mma": 1, "staged": 2, "staged3": 2}[kernel]
+    if kernel == "staged3":
+        assert steps[0]["splits"] == 3
     bufs = [be.buffer_from_host(a) for a in (q, k, v)]
     for token in list(range(0, kv_len)) + [kv_len + 5]:
         tb = be.buffer_from_host(np.array(token, np.int32))
@@ -366,7 +382,7 @@ def test_executable_cache_compiles_reuses_and_evicts(gpu_backend):
     b, _ = cases.u8_chain()
     lhs = be.buffer_from_host(np.array([1, 2, 3, 4], np.uint8))
     first = cache.compile(b, [0])
-    assert not first.reused and first.fingerprint == be.plan_fingerprint(b)
+    assert not first.reused and first.fingerprint == be.plan_fingerprint(b, [0])
     e = cache.entry(first.fingerprint)
     assert e["resident"] and e["reference_count"] == 1 and e["resident_bytes"] >= 4 and e["compile_latency_us"] > 0
     second = cache.compile(b, [0])

@@ -73,6 +73,7 @@ def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
         if peer:  # all-reduce as one kernel per rank over peer-mapped memory instead of the library collective
             be.enable_peer_all_reduce(rank, rank, world, dist.all_gather_object)
         exe = be.compile_executable(full, [rank], partition=rank)
+        dist.barrier()  # every rank has compiled: nobody reaches a collective while a peer is still in the compiler
         kinds = [s["type"] for s in exe.describe()["kernel_plan"]["steps"]]
         results = []
         bufs = [be.buffer_from_host(a, rank) for a in local]
@@ -87,7 +88,8 @@ def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
 
 
 @pytest.mark.parametrize("world,batch,peer", [(2, 2, False), (2, 16, False), (2, 2, True), (2, 16, True),
-                                              (4, 16, False), (4, 2, True), (4, 16, True), (8, 16, True)])
+                                              (4, 16, False), (4, 2, True), (4, 16, True),
+                                              (8, 2, False), (8, 16, False), (8, 2, True), (8, 16, True)])
 def test_tensor_parallel_decode_matches_oracle(world, batch, peer):
     import torch
     import torch.multiprocessing as mp
@@ -132,9 +134,103 @@ def test_tensor_parallel_decode_matches_oracle(world, batch, peer):
         for step, (tok, logits) in enumerate(results):
             # the same token at the same position is decoded twice: the second pass overwrites the same cache row
             err = float(np.abs(np.asarray(logits, np.float32) - want_logits).max())
-            assert err <= 4e-2 * scale, (rank, step, err, scale)
+            print(f"world {world} batch {batch} peer {peer} rank {rank} step {step}: logits max-abs error {err:.4e} (scale {scale:.4e})")
+            assert err <= 2e-2 * scale, (rank, step, err, scale)
             ref = np.sort(want_logits, axis=1)[:, -2:]
             decisive = (ref[:, 1] - ref[:, 0]) > 2 * err
             assert np.array_equal(np.asarray(tok)[decisive], np.asarray(want[0])[decisive])
     for rank in range(1, world):
         assert np.array_equal(got[0][1][0][0], got[rank][1][0][0])  # every rank picks the same tokens
+
+
+def _absent_rank_worker(rank, world, port, queue):
+    import torch.distributed as dist
+
+    import pjrtx_b200
+    from pjrtx_b200 import PlanBuilder
+    from pjrtx_b200 import backend as be_mod
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["PJRTX_B200_PEER_TIMEOUT_MS"] = "300"  # the budget a launch gives its peers before it reports them missing
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        be = pjrtx_b200.Backend()
+        uid = [be.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        be.comm_init(rank, uid[0], rank, world)
+        n = 8192
+        x = (np.arange(n, dtype=np.float32) % 13 + rank).astype(P.np_dtype(P.BF16_CODE))
+        want = sum((np.arange(n, dtype=np.float32) % 13 + r) for r in range(world))
+
+        def one_all_reduce():
+            b = PlanBuilder()
+            b.set_outputs([b.all_reduce(b.parameter(P.BF16_CODE, [n]))])
+            return be.compile_executable(b, [rank])  # its only collective runs over peer memory: no library kernel waits
+
+        report = {}
+        # 1. both ranks present
+        be.enable_peer_all_reduce(rank, rank, world, dist.all_gather_object)
+        exe = one_all_reduce()
+        dist.barrier()
+        got = be.execute_executable(exe, [be.buffer_from_host(x, rank)])[0].to_numpy().astype(np.float32)
+        report["first"] = bool(np.array_equal(got, want))
+        dist.barrier()
+        # 2. rank 1 stays away from one step (it leaves between steps; nothing of its own is in flight)
+        if rank == 0:
+            out = be.execute_executable(exe, [be.buffer_from_host(x, rank)])  # enqueues and returns
+            try:
+                be.synchronize(rank)
+                report["timeout"] = "no error"
+            except be_mod.BackendError as e:
+                report["timeout"] = str(e)
+            del out
+        dist.barrier()
+        # 3. fresh regions (new export / import zeroes the step words), both ranks present again
+        be.enable_peer_all_reduce(rank, rank, world, dist.all_gather_object)
+        exe2 = one_all_reduce()
+        dist.barrier()
+        got = be.execute_executable(exe2, [be.buffer_from_host(x, rank)])[0].to_numpy().astype(np.float32)
+        be.synchronize(rank)
+        report["recovered"] = bool(np.array_equal(got, want))
+        dist.barrier()
+        queue.put((rank, report))
+    except Exception:
+        import traceback
+
+        queue.put((rank, {"error": traceback.format_exc()}))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_absent_rank_runs_out_a_bounded_wait_and_the_pair_recovers():
+    """Failure detection without a GPU fault: one rank does not join a step of the peer-memory all-reduce. The other
+    rank's kernel gives its peer 300 ms, raises the error word (code 21) and returns; the host reads it at the next
+    synchronize and the context stays usable: after the ranks exchange fresh regions the collective works again."""
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    reports = {}
+    try:
+        for _ in range(2):
+            rank, report = queue.get(timeout=300)
+            reports[rank] = report
+    finally:
+        for p in procs:
+            p.join(timeout=120)
+            if p.is_alive():
+                p.terminate()
+    assert all("error" not in r for r in reports.values()), reports
+    assert reports[0]["first"] and reports[1]["first"]
+    assert "gave up a bounded wait (code 21)" in reports[0]["timeout"], reports[0]
+    assert reports[0]["recovered"] and reports[1]["recovered"]

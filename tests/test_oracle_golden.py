@@ -95,3 +95,17 @@ def test_structural_ops_clamp_indices():
     np.testing.assert_array_equal(outs[6], want)
     table = np.arange(40, dtype=np.float32).reshape(10, 4) / np.float32(3.0)
     np.testing.assert_array_equal(outs[7], table[[[3, 9], [0, 9]]])  # id 12 clamped to 9
+
+
+def test_pad_matches_numpy():
+    """stablehlo.pad in the oracle against numpy.pad / explicit spreading (edge, interior and negative edge padding)."""
+    b, (cube, row) = cases.pad_cases()
+    outs = plan_interp.run_plan(b, [cube, row])
+    edge = np.pad(cube, [(1, 0), (0, 2), (2, 1)], constant_values=np.float32(-7.5))
+    assert np.array_equal(outs[0], edge)
+    spread = np.full((2 * cube.shape[0] - 1, cube.shape[1], 3 * (cube.shape[2] - 1) + 1), np.float32(-7.5))
+    spread[::2, :, ::3] = cube
+    assert np.array_equal(outs[1], np.pad(spread, [(0, 1), (1, 0), (0, 0)], constant_values=np.float32(-7.5)))
+    assert outs[2].tolist() == [9, 2, 9, 3, 9, 4, 9, 5, 9, 9, 9]
+    assert outs[3].tolist() == [9, 9, 1, 2, 3]
+    assert np.allclose(outs[4], (edge * 2.0).sum(axis=2))

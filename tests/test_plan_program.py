@@ -164,6 +164,32 @@ def test_config1_is_one_row_kernel_and_compiles(backend):
     assert backend.compile_check(st["source"]) == ""
 
 
+def test_decode_step_chains_the_streaming_contractions(backend, monkeypatch):
+    """Small-batch decode with PJRTX_B200_DOT_FUSE / _CHAIN on: the RMSNorm and SiLU kernels become lhs transforms of the
+    contractions they feed, the residual additions become epilogues, and o_proj -> gate/up -> down_proj -> next layer's
+    q/k/v run as one launch."""
+    monkeypatch.setenv("PJRTX_B200_DOT_FUSE", "1")
+    monkeypatch.setenv("PJRTX_B200_DOT_CHAIN", "1")
+    cfg = llama.TINY
+    b, names = llama.build_decode_step(cfg, 2, 64)
+    k = backend.describe_kernels(b)
+    types = [s["type"] for s in k["steps"]]
+    dots = [s for s in k["steps"] if s["type"] == "dot"]
+    # first q/k/v alone (its norm also gathers the embedding rows), then one chain per layer
+    assert len(dots) == cfg.layers + 1
+    assert dots[0]["group"] == 3 and "segments" not in dots[0]
+    for layer, d in enumerate(dots[1:]):
+        assert d["segments"] == 4 and d["lhs_kinds"] == [0, 1, 2, 1] and d["residuals"] == 2
+        last = layer == cfg.layers - 1
+        per_layer = cfg.q_dim * cfg.d_model + 3 * cfg.d_model * cfg.ffn
+        tail = cfg.d_model * cfg.vocab if last else cfg.d_model * (cfg.q_dim + 2 * cfg.kv_dim)
+        assert d["weight_elems"] == per_layer + tail
+    # three launches per layer (rotation + cache rows, attention, chain) plus embedding/tables, first norm, first q/k/v, argmax
+    assert types.count("attention_decode") == cfg.layers and len(types) == 3 * cfg.layers + 4
+    for src in {s["source"] for s in k["steps"] if s["type"] == "fused"}:
+        assert backend.compile_check(src) == ""
+
+
 def test_decode_step_kernel_plan(backend, monkeypatch):
     cfg = llama.TINY
     b, names = llama.build_decode_step(cfg, 2, 64)

@@ -34,6 +34,7 @@ def test_static_scratch_matches_executable_twice_in_a_row(gpu_backend, dtype, m,
     lhs = rng.standard_normal((m, k), dtype=np.float32).astype(dt)
     rhs = rng.standard_normal((k, n), dtype=np.float32).astype(dt)
     want = _reference_through_executable(be, lhs, rhs, dtype)
+    exact = lhs.astype(np.float64) @ rhs.astype(np.float64)
     # Device memory for the raw-pointer call comes from torch: the entry point itself must not allocate.
     as_bytes = lambda a: torch.from_numpy(a.view(np.uint8).reshape(-1).copy()).cuda()
     dl, dr = as_bytes(lhs), as_bytes(rhs)
@@ -42,12 +43,22 @@ def test_static_scratch_matches_executable_twice_in_a_row(gpu_backend, dtype, m,
     for call in range(2):  # the second call finds the array as the first one left it
         out.fill_(0xAB)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        # What the driver reports as free counts every allocation on the GPU, whoever made it (the first call has
+        # already loaded the kernel and resolved the array); the library's own accounting must not move either.
+        free_before = torch.cuda.mem_get_info()[0] if call else None
+        live_before = be.memory_stats(0)
+        torch_before = torch.cuda.memory_allocated()
         be.dot_static_scratch(dtype, dl.data_ptr(), dr.data_ptr(), out.data_ptr(), m, k, n)
+        be.dot_static_scratch_status(0)  # waits for the stream; raises if a bounded device-side wait gave up
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() == torch_before
+        assert be.memory_stats(0) == live_before
+        if call:
+            assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.current_device() == 0
         got = out.cpu().numpy().view(dt).reshape(m, n)
-        assert_close(got, want, 1e-5 if dtype == P.F32 else 2e-2, what=f"call {call}")
+        assert_close(got, want, 1e-5 if dtype == P.F32 else 2e-2, what=f"call {call} vs the executable path")
+        assert_close(got, exact, 1e-5 if dtype == P.F32 else 2e-2, what=f"call {call} vs the float64 product")
 
 
 def test_static_scratch_rejects_what_does_not_fit(gpu_backend):
