@@ -27,7 +27,7 @@ from pjrtx_b200.programs import llama, random_init  # noqa: E402
 
 
 TRAFFIC_RATIO = 1.021  # (dram read + write) / algorithmic bytes, byte-weighted over the captured launches
-UMMA_TRAFFIC_RATIO = 1.02  # same ratio for the tensor-core kernel (profiles/umma_stream_kernel_llama8b_batch32.md)
+UMMA_TRAFFIC_RATIO = 1.02  # same ratio for the tensor-core kernel, from an ncu capture of four of its launches
 
 
 def measured_peaks():
@@ -231,7 +231,13 @@ def run_ours(args):
         cfg = dataclasses.replace(cfg, layers=args.layers)
         workload += f" (truncated to {args.layers} layers)"
     max_len = filled + tail
-    builder, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=world)
+    # `--shard-of N` (one GPU): the work of ONE rank of an N-way tensor-parallel step, collectives as one-rank copies.
+    # A development view of the shard-shaped kernels; it is not a throughput number of the model.
+    parts = world if world > 1 else max(1, args.shard_of)
+    if parts > 1 and world == 1:
+        workload += f" [rank 0 of {parts} alone, collectives as copies]"
+        be.comm_init(device, be.comm_unique_id(), 0, 1)
+    builder, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=parts)
     if world > 1:
         uid = [be.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
@@ -243,12 +249,12 @@ def run_ours(args):
             be.enable_peer_all_reduce(device, rank, world, dist.all_gather_object)
     t0 = time.time()
     _progress("compiling")
-    exe = be.compile_executable(builder, [device], partition=rank if world > 1 else None)
+    exe = be.compile_executable(builder, [device], partition=rank if parts > 1 else None)
     _progress("compiled")
     compile_s = time.time() - t0
-    table = param_table(cfg, builder, names, world)
+    table = param_table(cfg, builder, names, parts)
     t0 = time.time()
-    gen = make_device_weights(be, cfg, names[2:], table, device, rank, world)
+    gen = make_device_weights(be, cfg, names[2:], table, device, rank, parts)
     params = [reshape_buffer(be, buf, dims, device) for buf, dims in gen]
     be.synchronize(device)
     setup_s = time.time() - t0
@@ -354,13 +360,14 @@ def run_ours(args):
         if st["type"] == "dot" and st["path"] == 1 and st["b0"] * st["b1"] == 1:
             # weights once + activations in and out (a chained launch reports the weights of all its segments)
             weight_elems = st.get("weight_elems", st["k"] * st["n"])
-            stream_bytes += weight_elems * esize + st["m"] * (weight_elems // max(st["k"], 1) + st["k"]) * esize
+            wsize = 1 if st.get("rhs_s8") else esize  # int8 weights stay one byte wide
+            stream_bytes += weight_elems * wsize + st["m"] * (weight_elems // max(st["k"], 1) + st["k"]) * esize
             stream_ms += float(t)
             tensor_core |= bool(st.get("umma"))
     peak, peak_kind = measured_peaks()
     step_ms = ms / args.steps
-    kv_mid = filled + args.warmup + args.steps // 2
-    alg = algorithmic_bytes(cfg, batch, kv_mid, world)
+    kv_mid = filled + args.warmup + (repeats * args.steps) // 2
+    alg = algorithmic_bytes(cfg, batch, kv_mid, parts)
     achieved = stream_bytes / (stream_ms * 1e-3) / 1e9 if stream_ms > 0 else 0.0
     result = {
         "metric": "decode tok/s + % HBM roofline: 8B-shape on 1 GPU, 70B-shape TP 2/4/8",
@@ -378,7 +385,7 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram read+write bytes per step over all launches of this kernel: algorithmic bytes x the ratio an
-                     # ncu capture of one layer's launches gave (profiles/stream_tma_kernel_llama8b_layer.md)
+                     # ncu capture of one layer's launches gave
                      "traffic": stream_bytes * (UMMA_TRAFFIC_RATIO if tensor_core else TRAFFIC_RATIO),
                      "algorithmic_bytes": stream_bytes,
                      "kernel": ("umma::umma_stream_kernel (tcgen05 weight-streaming contraction)" if tensor_core
@@ -424,8 +431,8 @@ def run_prefill(args):
     tokens = be.buffer_from_host(np.random.default_rng(2).integers(0, cfg.vocab, size=(batch, seq), dtype=np.int32), device)
     be.synchronize(device)
 
-    def step():
-        outs = be.execute_executable(exe, [tokens] + weights)
+    def step(tok=None):
+        outs = be.execute_executable(exe, [tok if tok is not None else tokens] + weights)
         for o in outs[1:]:
             o.destroy()  # the KV caches of this pass
         return outs[0]
@@ -445,6 +452,20 @@ def run_prefill(args):
     be.synchronize(device)
     clocks = sampler.stop()
     launches = exe.stats()["kernel_launch_total"] - launches0
+    # ---- end to end: token ids from pinned host memory every pass, next tokens read back every pass ----
+    import torch
+
+    host_tokens = torch.from_numpy(np.random.default_rng(2).integers(0, cfg.vocab, size=(batch, seq), dtype=np.int32)).pin_memory()
+    host_next = torch.empty((batch,), dtype=torch.int32).pin_memory()
+    be.synchronize(device)
+    t_wall = time.perf_counter()
+    e2e_start = be.record_event(device)
+    for _ in range(args.steps):
+        tb = be.buffer_from_pointer(host_tokens.data_ptr(), 4 * batch * seq, P.S32, [batch, seq], device)
+        nxt = step(tb)
+        be.copy_to_pointer(nxt, host_next.data_ptr(), 4 * batch)
+    e2e_stop = be.record_event(device)
+    e2e_ms = max(be.elapsed_ms(e2e_start, e2e_stop), (time.perf_counter() - t_wall) * 1e3)
     exe.set_profiling(True)
     step()
     times = exe.step_times_ms()
@@ -476,6 +497,8 @@ def run_prefill(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload, "batch": batch, "seq": seq, "layers": cfg.layers,
                    "l2": "weights and activations exceed L2; no flush needed", "lm_head": "last position only"},
+        "e2e": {"value": tokens_n * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * batch * seq,
+                "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": f"of {peak_kind}", "algorithmic_flops": flops,
@@ -483,7 +506,35 @@ def run_prefill(args):
         "clocks": clocks,
         "kernel_time_ms_per_step": {k: {"launches": v[0], "ms": round(v[1], 4)} for k, v in sorted(per_type.items())},
         "compile_s": round(compile_s, 2),
+        **({} if args.no_cpu_baseline else {"cpu_baseline": cpu_baseline_prefill(llama.LLAMA3_8B, batch, seq)}),
     }))
+
+
+def cpu_baseline_prefill(cfg, batch, seq):
+    """Times the CPU plan interpreter (float32 BLAS contractions, all host threads) on ONE decoder layer of the prefill
+    pass at the full batch x sequence, plus the LM head on the last positions, and scales the layer time to the depth."""
+    import dataclasses
+
+    from oracle import plan_interp
+
+    def timed(layers):
+        small = dataclasses.replace(cfg, layers=layers)
+        builder, names = llama.build_prefill(small, batch, seq)
+        weights = llama.make_weights(small, seed=0, threads=os.cpu_count() or 8, embed_period=4096)
+        tokens = np.random.default_rng(2).integers(0, cfg.vocab, size=(batch, seq), dtype=np.int32)
+        args = [tokens] + [weights[n] for n in names[1:]]
+        t0 = time.perf_counter()
+        plan_interp.run_plan(builder, args, fast_dot=True, weight_cache={})
+        return time.perf_counter() - t0
+
+    t_head = timed(0)
+    t_one = timed(1)
+    per_layer = max(t_one - t_head, 0.0)
+    full = t_head + per_layer * cfg.layers
+    return {"value": batch * seq / full, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 of {cfg.layers} layers at batch {batch} x seq {seq} + embedding and last-position LM head, layer time "
+                      f"scaled linearly; NumPy plan interpreter with f32 BLAS contractions ({t_one:.2f} s with one layer, "
+                      f"{t_head:.2f} s without)"}
 
 
 def cpu_baseline(cfg, batch, filled, budget_layers=2, steps=2):
@@ -533,8 +584,8 @@ def run_reference(args):
     if rank != 0:
         return
     cfg, batch, filled = (llama.LLAMA3_8B, 1, 2048) if world == 1 else (llama.LLAMA3_70B, 32, 4096)
-    base = cpu_baseline(cfg, batch, filled, budget_layers=args.cpu_layers,
-                        steps=max(1, min(args.steps, 16 if world == 1 else 2)))
+    timed_tokens = max(1, min(args.steps, 16 if world == 1 else 2))
+    base = cpu_baseline(cfg, batch, filled, budget_layers=args.cpu_layers, steps=timed_tokens)
     workload = ("llama3-8b-shape bf16 decode batch 1, KV prefilled 2048" if world == 1
                 else f"llama3-70b-shape bf16 decode batch 32, KV 4096, TP={world}")
     line = {
@@ -543,6 +594,8 @@ def run_reference(args):
         "ms_per_step": 1e3 * batch / base["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": {"workload": workload, "batch": batch, "kv_prefill": filled},
         "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        # what the sample really was: decode steps timed on the truncated copy (the driver's --steps is echoed above)
+        "steps_timed": timed_tokens, "layers_timed": args.cpu_layers,
     }
     print(json.dumps(line))
 
@@ -562,6 +615,8 @@ def main():
                     help="decode = the headline line (8B-shape batch 1 on one GPU, 70B-shape tensor parallel on more); "
                          "prefill = 8B-shape batch 4 x 2048 on one GPU (give it --steps 5); 70b = the 70B shape also on one GPU, "
                          "truncated to the layers that fit; int8 = 8B-shape int8 weights, batch 16, KV 4096, any GPU count")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="one GPU only: run rank 0's share of an N-way tensor-parallel step (development view of the shard shapes)")
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed region of --steps steps is run (median reported)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

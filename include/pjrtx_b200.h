@@ -175,6 +175,13 @@ int pjrtx_b200_copy_devices(PjrtxB200DeviceInfo *out_devices, int max_devices);
 int pjrtx_b200_device_memory_stats(int device_ordinal, PjrtxB200MemoryStats *out);
 /* Blocks until everything queued on the device's stream is done (mlx synchronize, api.cc:1512-1520). */
 int pjrtx_b200_device_synchronize(int device_ordinal);
+/* No counterpart in the reference (its failure tests overwrite buffer readiness on the host,
+ * src/runtime/execution_call.zig:355-360). Exercises the path by which a device-side wait that cannot complete is
+ * reported: enqueues one CTA that waits, with the bounded wait of the streaming kernels, for a barrier nothing ever
+ * completes; after `timeout_ms` (1..1000) it gives up, raises the device's error word (code 31) and returns. The next
+ * pjrtx_b200_device_synchronize then returns 0 with "gave up a bounded wait (code 31)" and clears the word; the
+ * context stays usable. 1 when enqueued. */
+int pjrtx_b200_device_bounded_wait_probe(int device_ordinal, uint32_t timeout_ms);
 
 /* Device-side timing on the stream every buffer and executable of the device uses. The reference measures the same
  * interval on the host around a forced device sync (PJRTX_PROFILE_DEVICE_SYNC, src/backend/mlx_metal/api.cc:65-75,

@@ -170,6 +170,7 @@ SYMBOLS = {
     "pjrtx_b200_comm_peer_import": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint8), ctypes.c_int, ctypes.c_int]),
     "pjrtx_b200_dot_static_scratch": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _P, _P, _P, ctypes.c_int64, ctypes.c_int64,
                                                       ctypes.c_int64, _P]),
+    "pjrtx_b200_device_bounded_wait_probe": (ctypes.c_int, [ctypes.c_int, ctypes.c_uint32]),
     "pjrtx_b200_dot_static_scratch_status": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p]),
     "pjrtx_b200_compile_check": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint64]),
     "pjrtx_b200_executable_cache_create": (_P, [ctypes.c_uint64]),
@@ -438,6 +439,11 @@ class Backend:
         if not self.lib.pjrtx_b200_device_memory_stats(device, ctypes.byref(m)):
             raise BackendError("InvalidDeviceCount", self._err())
         return {n: getattr(m, n) for n, _ in MemoryStats._fields_}
+
+    def bounded_wait_probe(self, device: int = 0, timeout_ms: int = 50) -> None:
+        """Enqueues a kernel whose bounded wait cannot complete; the next `synchronize` reports it (code 31)."""
+        if not self.lib.pjrtx_b200_device_bounded_wait_probe(device, timeout_ms):
+            raise BackendError("CommandSubmissionFailed", self._err())
 
     def record_event(self, device: int = 0):
         """Enqueues a timing event on the device's stream; pair two of them with `elapsed_ms`."""

@@ -138,6 +138,14 @@ int pjrtx_b200_device_synchronize(int device_ordinal) {
             if (!check_cuda(cudaStreamSynchronize(d->stream), "cudaStreamSynchronize")) return 0; return check_device_flag(d) ? 1 : 0;)
 }
 
+int pjrtx_b200_device_bounded_wait_probe(int device_ordinal, uint32_t timeout_ms) {
+  GUARD_INT(Device* d = get_device(device_ordinal); if (!d) return 0; cudaSetDevice(d->ordinal);
+            if (!bounded_wait_probe_launch(timeout_ms, d->error_flag_dev, d->stream)) {
+              set_last_error("bounded-wait probe refused (timeout must be 1..1000 ms)");
+              return 0;
+            } return 1;)
+}
+
 PjrtxB200DeviceEvent* pjrtx_b200_device_event_record(int device_ordinal) {
   GUARD_PTR(Device* d = get_device(device_ordinal); if (!d) return nullptr; cudaSetDevice(d->ordinal);
             auto* ev = new PjrtxB200DeviceEvent{device_ordinal, nullptr};

@@ -116,7 +116,8 @@ bool analyze_dot(const Plan& plan, const Instruction& ins, DotShape* out, std::s
   const Value& lhs = plan.values[ins.inputs[0]];
   const Value& rhs = plan.values[ins.inputs[1]];
   const Value& res = plan.values[ins.outputs[0]];
-  if (lhs.dtype != rhs.dtype || lhs.dtype != res.dtype || !dtype_is_float(lhs.dtype)) {
+  const bool rhs_s8 = ins.scalar("rhs_s8", 0) != 0;  // set by the planner: the rhs holds bytes, the third operand column scales
+  if ((!rhs_s8 && lhs.dtype != rhs.dtype) || (rhs_s8 && rhs.dtype != kS8) || lhs.dtype != res.dtype || !dtype_is_float(lhs.dtype)) {
     *why = "dot_general operands and result must share one of f32, f16, bf16";
     return false;
   }
@@ -209,6 +210,7 @@ bool analyze_dot(const Plan& plan, const Instruction& ins, DotShape* out, std::s
     *why = "dot_general result shape does not match its operands";
     return false;
   }
+  s.rhs_s8 = rhs_s8 ? 1 : 0;
   *out = s;
   return true;
 }
@@ -639,6 +641,79 @@ void fuse_decode_attention(Plan* plan) {
   plan->instructions = std::move(kept);
 }
 
+// Weight-only int8: dot_general(x, W) with W = [convert ->] multiply(convert(w : s8 -> f16), broadcast(scale : f16[n]))
+// over a [k, n] weight (the only quantised form the reference accepts: its mixed-type dot is rejected,
+// src/backend/mlx_metal/lowering_linalg.zig:14-53, and convert is api.cc:907-935). When the dequantised weight has no
+// other reader and the tensor-core stream can take the shape, the dot_general reads the bytes itself: its rhs becomes
+// w, the scale its third operand, and the dequantising instructions die. The kernel rebuilds, per element, exactly the
+// value the written program would have stored (f16 product rounded to nearest, then the conversion), so results are
+// those of the op-by-op program while the weights stay one byte wide in HBM.
+void fuse_dequant_dots(Plan* plan) {
+  const size_t ni = plan->instructions.size(), nv = plan->values.size();
+  std::vector<long> producer(nv, -1);
+  std::vector<int> readers(nv, 0);
+  for (size_t i = 0; i < ni; i++) {
+    for (uint32_t v : plan->instructions[i].outputs) producer[v] = (long)i;
+    for (uint32_t v : plan->instructions[i].inputs) readers[v]++;
+  }
+  for (uint32_t o : plan->output_ids) readers[o]++;
+  auto made_by = [&](uint32_t v, Kind kind) -> const Instruction* {
+    return producer[v] >= 0 && plan->instructions[producer[v]].kind == kind ? &plan->instructions[producer[v]] : nullptr;
+  };
+  for (size_t i = 0; i < ni; i++) {
+    Instruction& dot = plan->instructions[i];
+    if (dot.kind != Kind::dot_general || dot.inputs.size() != 2) continue;
+    const Value& x = plan->values[dot.inputs[0]];
+    uint32_t w = dot.inputs[1];
+    const Value& wv = plan->values[w];
+    if ((x.dtype != kBF16 && x.dtype != kF16) || wv.dtype != x.dtype || wv.dims.size() != 2 || readers[w] != 1) continue;
+    if (!dot.list("lhs_batch_dimensions").empty() || dot.list("rhs_contracting_dimensions") != std::vector<int64_t>{0} ||
+        dot.list("lhs_contracting_dimensions") != std::vector<int64_t>{(int64_t)x.dims.size() - 1})
+      continue;
+    if (x.dtype == kBF16) {  // f16 product converted to the element type
+      const Instruction* cv = made_by(w, Kind::convert);
+      if (!cv || plan->values[cv->inputs[0]].dtype != kF16 || readers[cv->inputs[0]] != 1) continue;
+      w = cv->inputs[0];
+    }
+    const Instruction* mul = made_by(w, Kind::multiply);
+    if (!mul || plan->values[w].dtype != kF16) continue;
+    const Instruction* widen = nullptr;
+    const Instruction* spread = nullptr;
+    for (int sw = 0; sw < 2; sw++) {
+      const Instruction* a = made_by(mul->inputs[sw], Kind::convert);
+      const Instruction* b = made_by(mul->inputs[1 - sw], Kind::broadcast_in_dim);
+      if (a && b && readers[mul->inputs[0]] == 1 && readers[mul->inputs[1]] == 1) {
+        widen = a;
+        spread = b;
+      }
+    }
+    if (!widen || !spread) continue;
+    const uint32_t bytes = widen->inputs[0], scale = spread->inputs[0];
+    const Value& bv = plan->values[bytes];
+    const Value& sv = plan->values[scale];
+    if (bv.dtype != kS8 || bv.dims != wv.dims || sv.dtype != kF16 || sv.dims != std::vector<int64_t>{wv.dims[1]} ||
+        spread->list("broadcast_dimensions") != std::vector<int64_t>{1})
+      continue;
+    // Bytes and scales must be values no instruction writes (parameters or constants): the kernel may read them early.
+    if ((producer[bytes] >= 0 && plan->instructions[producer[bytes]].kind != Kind::constant) ||
+        (producer[scale] >= 0 && plan->instructions[producer[scale]].kind != Kind::constant))
+      continue;
+    DotShape shape;
+    shape.dtype = x.dtype;
+    shape.m = x.count() / std::max<int64_t>(x.dims.back(), 1);
+    shape.k = wv.dims[0];
+    shape.n = wv.dims[1];
+    shape.lhs_m = shape.k;
+    shape.lhs_k = 1;
+    shape.rhs_k = shape.n;
+    shape.rhs_n = 1;
+    shape.out_m = shape.n;
+    if (!dot_s8_supported(shape)) continue;
+    dot.inputs = {dot.inputs[0], bytes, scale};
+    dot.attrs["rhs_s8"] = {1};
+  }
+}
+
 struct KernelPlan {
   Plan plan;  // rewritten
   Program program;
@@ -682,6 +757,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
   }
   if (!build_program(plan, &kp->program, error)) return false;
   if (env_flag_local("PJRTX_B200_FUSE_ATTENTION", true)) fuse_decode_attention(&kp->plan);
+  if (env_flag_local("PJRTX_B200_FUSE_DEQUANT", true)) fuse_dequant_dots(&kp->plan);
 
   const size_t nv = plan.values.size(), ni = plan.instructions.size();
   kp->params = plan.parameter_ids();
@@ -887,6 +963,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
         analyze_dot(plan, ins, &st.dot, &why);
         st.dot_scratch = dot_plan(st.dot, sm_count);
         st.inputs = {kp->root[ins.inputs[0]], kp->root[ins.inputs[1]]};
+        if (st.dot.rhs_s8) st.dot_scales = {kp->root[ins.inputs[2]]};
         st.outputs = {ins.outputs[0]};
         break;
       case Kind::dynamic_update_slice: {
@@ -992,7 +1069,8 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
       bool can = prev && prev->type == Step::kDot && st.type == Step::kDot && prev->dot_scratch.path == 1 &&
                  st.dot_scratch.path == 1 && prev->dot_scratch.umma == st.dot_scratch.umma && prev->inputs[0] == st.inputs[0] && prev->dot.b0 * prev->dot.b1 == 1 &&
                  st.dot.b0 * st.dot.b1 == 1 && prev->dot.m == st.dot.m && prev->dot.k == st.dot.k &&
-                 prev->dot.dtype == st.dot.dtype && prev->dot.lhs_m == st.dot.lhs_m && prev->dot.lhs_k == st.dot.lhs_k &&
+                 prev->dot.dtype == st.dot.dtype && prev->dot.rhs_s8 == st.dot.rhs_s8 && prev->dot.lhs_m == st.dot.lhs_m &&
+                 prev->dot.lhs_k == st.dot.lhs_k &&
                  std::max<size_t>(prev->dot_group.size(), 1) < (size_t)kDotGroupMax;
       if (can)
         for (uint32_t o : prev->outputs) can &= (o != st.inputs[1]);
@@ -1004,6 +1082,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
       prev->dot_group.push_back(st.dot);
       prev->nodes.push_back(st.nodes[0]);
       prev->inputs.push_back(st.inputs[1]);
+      for (uint32_t sc : st.dot_scales) prev->dot_scales.push_back(sc);
       prev->outputs.push_back(st.outputs[0]);
       prev->dot_scratch = dot_group_plan(prev->dot_group.data(), (int)prev->dot_group.size(), sm_count);
     }
@@ -1471,7 +1550,7 @@ std::string describe_steps(const KernelPlan& kp, bool with_source) {
           for (uint32_t r : sg.residual) residuals += r != UINT32_MAX;
         s += strfmt("%zu", residuals);
       }
-      s += strfmt(",\"weight_elems\":%lld", weight_elems);
+      s += strfmt(",\"weight_elems\":%lld,\"rhs_s8\":%d", weight_elems, st.dot.rhs_s8);
     } else if (st.type == Step::kSliceUpdate) {
       s += strfmt(",\"in_place\":%s", st.in_place ? "true" : "false");
     } else if (st.type == Step::kAttnDecode) {
@@ -1657,16 +1736,19 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
                                st.early_rhs, exe->pdl, dev->stream);
         } else if (st.dot_group.size() > 1) {
           const void* rhs[kDotGroupMax];
+          const void* scales[kDotGroupMax] = {nullptr, nullptr, nullptr, nullptr};
           void* out[kDotGroupMax];
           for (size_t g = 0; g < st.dot_group.size(); g++) {
             rhs[g] = ptr.of(st.inputs[1 + g]);
             out[g] = ptr.of(st.outputs[g]);
+            if (g < st.dot_scales.size()) scales[g] = ptr.of(st.dot_scales[g]);
           }
           n = dot_group_launch(st.dot_group.data(), (int)st.dot_group.size(), st.dot_scratch, ptr.of(st.inputs[0]), rhs, out,
-                               partials, counters, dev->error_flag_dev, st.early_rhs, exe->pdl, dev->stream);
+                               partials, counters, dev->error_flag_dev, st.early_rhs, exe->pdl, dev->stream, scales);
         } else {
           n = dot_launch(st.dot, st.dot_scratch, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.outputs[0]), partials,
-                         counters, dev->error_flag_dev, st.early_rhs, exe->pdl, dev->stream);
+                         counters, dev->error_flag_dev, st.early_rhs, exe->pdl, dev->stream,
+                         st.dot_scales.empty() ? nullptr : ptr.of(st.dot_scales[0]));
         }
         if (n == 0) {
           *error = "dot_general kernel refused the shape";

@@ -67,6 +67,7 @@ struct Step {
   JitKernel* jit = nullptr;
   DotShape dot;
   std::vector<DotShape> dot_group;  // more than one entry: contractions sharing inputs[0], launched together
+  std::vector<uint32_t> dot_scales; // int8 weights: the f16 column scales, one per contraction (parameters / constants)
   DotScratch dot_scratch;
   // Non-empty: the step runs as one launch of the chained streaming kernel (dot / dot_group describe its first segment).
   std::vector<DotSeg> segs;

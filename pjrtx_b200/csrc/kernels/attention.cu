@@ -90,6 +90,10 @@ struct DecodeArgs {
   // they start, so that HBM works through the attention step's latencies instead of idling.
   const unsigned char* prefetch;
   unsigned long long prefetch_bytes;
+  // 1: the whole grid is resident at once, so the CTAs of a (sequence, KV head) wait for each other and each merges
+  // its own slice of the outputs instead of leaving the whole merge to the CTA that arrives last.
+  int coop_merge;
+  unsigned long long timeout_ns;
 };
 
 // Every CTA asks for its share of [prefetch, prefetch + prefetch_bytes) in 16 KiB bulk requests (no destination, no
@@ -113,6 +117,61 @@ __device__ __forceinline__ void prefetch_next_weights(const DecodeArgs& a) {
 template <typename T, int REP, int HD, int THREADS>
 __device__ __forceinline__ void merge_splits(const DecodeArgs& a, long long tile, int b, int g, float* scratch, int* is_last,
                                              T* __restrict__ out) {
+  if (a.coop_merge) {
+    // Cooperative merge. counters[2 * tile] counts arrivals, counters[2 * tile + 1] departures (the last one to leave
+    // clears both). Every CTA of the launch is resident (the host checked), so the wait ends as soon as the slowest split
+    // has published; it is bounded by time all the same.
+    unsigned* arrive = a.counters + 2 * tile;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      atomicAdd(arrive, 1u);
+      unsigned long long t0;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      bool ok = false;
+      for (unsigned spin = 0;; spin++) {
+        unsigned seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrive) : "memory");
+        if (seen >= (unsigned)a.splits) {
+          ok = true;
+          break;
+        }
+        if ((spin & 63) == 63) {
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+          if (t1 - t0 > a.timeout_ns) break;
+        }
+      }
+      if (!ok && a.error_flag) atomicExch(a.error_flag, 5);
+      *is_last = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!*is_last) return;
+    const int split = blockIdx.x;
+    const int per = (REP * HD + a.splits - 1) / a.splits;
+    const int lo = split * per, hi = min(lo + per, REP * HD);
+    const float* base = a.workspace + tile * a.splits * (long long)REP * (HD + 2);
+    const long long split_stride = (long long)REP * (HD + 2);
+    for (int idx = lo + threadIdx.x; idx < hi; idx += THREADS) {
+      const int r = idx / HD, d = idx % HD;
+      float mm = -INFINITY;
+      for (int sp = 0; sp < a.splits; sp++) mm = fmaxf(mm, __ldcg(base + sp * split_stride + r * (HD + 2) + HD));
+      float acc = 0.f, lsum = 0.f;
+      for (int sp = 0; sp < a.splits; sp++) {  // split order, the same arithmetic as the single-CTA merge
+        const float ms = __ldcg(base + sp * split_stride + r * (HD + 2) + HD);
+        const float w = ms == -INFINITY ? 0.f : __expf(ms - mm);
+        lsum = fmaf(__ldcg(base + sp * split_stride + r * (HD + 2) + HD + 1), w, lsum);
+        acc = fmaf(__ldcg(base + sp * split_stride + r * (HD + 2) + d), w, acc);
+      }
+      out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(lsum > 0.f ? acc / lsum : 0.f);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(arrive + 1, 1u) == (unsigned)a.splits - 1) {
+      arrive[0] = 0;
+      arrive[1] = 0;
+    }
+    return;
+  }
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) *is_last = atomicAdd(&a.counters[tile], 1u) == (unsigned)a.splits - 1;
@@ -1153,7 +1212,7 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
       p.mma = 2;
       p.splits = (int)std::max<long long>(1, std::min<long long>(std::min<long long>(want, s.kv_len), 64));
       p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
-      p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+      p.counter_bytes = (uint64_t)tiles * 2 * sizeof(unsigned);
       return p;
     }
   }
@@ -1167,7 +1226,7 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
     long long max_splits = std::max<long long>(1, s.kv_len / (2 * kMmaStageKeys));
     p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
     p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
-    p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+    p.counter_bytes = (uint64_t)tiles * 2 * sizeof(unsigned);
     return p;
   }
   // Keys one CTA handles per chunk (see the kernel): no split should be shorter than that.
@@ -1178,7 +1237,7 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   long long max_splits = std::max<long long>(1, s.kv_len / chunk);
   p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
   p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
-  p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
+  p.counter_bytes = (uint64_t)tiles * 2 * sizeof(unsigned);
   return p;
 }
 
@@ -1217,6 +1276,19 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
   a.counters = static_cast<unsigned*>(counters);
   dim3 grid((unsigned)plan.splits, (unsigned)s.kv_heads, (unsigned)s.batch);
   const int rep = (int)(s.heads / s.kv_heads);
+  {
+    // Cooperative merge of the splits only where every CTA of the grid has an SM to itself (the CUDA-core and the
+    // staged kernels, at most one CTA per SM counted), so that CTAs may wait for each other.
+    static const bool coop_allowed = [] {
+      const char* e = getenv("PJRTX_B200_ATTENTION_COOP_MERGE");
+      return !(e && *e && atoi(e) == 0);
+    }();
+    int device = 0, sms = 0;
+    if (coop_allowed && plan.mma != 1 && plan.splits > 1 && cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess)
+      a.coop_merge = (long long)plan.splits * s.kv_heads * s.batch <= sms ? 1 : 0;
+    a.timeout_ns = 2000000000ull;
+  }
   if (plan.mma == 2) {
     if (s.dtype == kF16) return dispatch_decode_staged<__half>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
     return dispatch_decode_staged<__nv_bfloat16>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);

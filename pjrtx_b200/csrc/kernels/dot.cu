@@ -347,6 +347,111 @@ tile_kernel(DotShape s, const T* __restrict__ lhs, const T* __restrict__ rhs, T*
   }
 }
 
+// ---------------------------------------------------------------- f32 tile, register-blocked
+// out[m, n] = sum_k lhs[m, k] * rhs[k, n] in true f32 (the parity bar for f32 contractions is rel 1e-5, which TF32
+// products miss at k = 1024), for dense operands: lhs k-contiguous, rhs n-contiguous, 16-byte aligned rows.
+// 128 x 64 output tile per CTA of 256 threads, 8 x 4 outputs per thread, k in slabs of 16: the next slab travels
+// global -> registers while the current one is multiplied out of shared memory (two buffers, one barrier per slab).
+// Per k step a thread issues three 16-byte shared loads (two broadcast, one conflict-free) for 32 FFMAs, so the FMA pipe
+// is the limit. A 1024^3 product is 128 tiles: one wave of one CTA per SM.
+constexpr int kSgBM = 128, kSgBN = 64, kSgBK = 16;
+
+__global__ void __launch_bounds__(256, 2)
+sgemm_kernel(DotShape s, const float* __restrict__ lhs, const float* __restrict__ rhs, float* __restrict__ out) {
+  PJRTX_PDL_PROLOGUE();
+  __shared__ __align__(16) float As[2][kSgBK][kSgBM + 4];
+  __shared__ __align__(16) float Bs[2][kSgBK][kSgBN + 4];
+  const int tid = threadIdx.x;
+  const int64_t batch = blockIdx.z, b0 = batch / s.b1, b1 = batch % s.b1;
+  const float* a = lhs + b0 * s.lhs_b0 + b1 * s.lhs_b1;
+  const float* b = rhs + b0 * s.rhs_b0 + b1 * s.rhs_b1;
+  float* o = out + b0 * s.out_b0 + b1 * s.out_b1;
+  const int64_t m0 = (int64_t)blockIdx.y * kSgBM, n0 = (int64_t)blockIdx.x * kSgBN;
+  // Global -> register mapping: A slab = 128 rows x 4 chunks of 4 k (two chunks per thread), B slab = 16 rows x 16
+  // chunks of 4 n (one per thread).
+  const int a_row[2] = {tid >> 2, (tid + 256) >> 2}, a_kc = tid & 3;
+  const int b_row = tid >> 4, b_nc = tid & 15;
+  float4 ra[2], rb;
+  auto gload = [&](int64_t k0) {
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int64_t gm = m0 + a_row[i], gk = k0 + a_kc * 4;
+      if (gm < s.m && gk + 3 < s.k) {
+        ra[i] = *reinterpret_cast<const float4*>(a + gm * s.lhs_m + gk);
+      } else {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = (gm < s.m && gk + j < s.k) ? a[gm * s.lhs_m + gk + j] : 0.f;
+        ra[i] = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+    const int64_t gk = k0 + b_row, gn = n0 + b_nc * 4;
+    if (gk < s.k && gn + 3 < s.n) {
+      rb = *reinterpret_cast<const float4*>(b + gk * s.rhs_k + gn);
+    } else {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) v[j] = (gk < s.k && gn + j < s.n) ? b[gk * s.rhs_k + gn + j] : 0.f;
+      rb = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  };
+  auto sstore = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      As[buf][a_kc * 4 + 0][a_row[i]] = ra[i].x;
+      As[buf][a_kc * 4 + 1][a_row[i]] = ra[i].y;
+      As[buf][a_kc * 4 + 2][a_row[i]] = ra[i].z;
+      As[buf][a_kc * 4 + 3][a_row[i]] = ra[i].w;
+    }
+    *reinterpret_cast<float4*>(&Bs[buf][b_row][b_nc * 4]) = rb;
+  };
+  const int tx = tid & 15, ty = tid >> 4;  // outputs: rows ty * 8 .. + 7, columns tx * 4 .. + 3
+  float acc[8][4] = {};
+  const int64_t slabs = (s.k + kSgBK - 1) / kSgBK;
+  gload(0);
+  sstore(0);
+  __syncthreads();
+  for (int64_t t = 0; t < slabs; t++) {
+    const int buf = (int)(t & 1);
+    if (t + 1 < slabs) gload((t + 1) * kSgBK);
+#pragma unroll
+    for (int kk = 0; kk < kSgBK; kk++) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 8]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 8 + 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bw[j], acc[i][j]);
+    }
+    if (t + 1 < slabs) sstore(buf ^ 1);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int64_t gm = m0 + ty * 8 + i, gn = n0 + tx * 4;
+    if (gm >= s.m) continue;
+    float* dst = o + gm * s.out_m + gn;
+    if (gn + 3 < s.n && (s.out_m & 3) == 0) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (gn + j < s.n) dst[j] = acc[i][j];
+    }
+  }
+}
+
+// True when the register-blocked f32 kernel can take the contraction as it lies in memory.
+inline bool sgemm_ok(const DotShape& s, const void* lhs, const void* rhs, const void* out) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return s.dtype == kF32 && s.lhs_k == 1 && s.rhs_n == 1 && (s.lhs_m & 3) == 0 && (s.rhs_k & 3) == 0 && (s.lhs_b0 & 3) == 0 &&
+         (s.lhs_b1 & 3) == 0 && (s.rhs_b0 & 3) == 0 && (s.rhs_b1 & 3) == 0 && (s.out_b0 & 3) == 0 && (s.out_b1 & 3) == 0 &&
+         al16(lhs) && al16(rhs) && al16(out) && (s.m + kSgBM - 1) / kSgBM <= 65535;
+}
+
 template <typename T>
 int launch_group_typed(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
                        void* const* out, void* partials, void* counters, bool pdl, cudaStream_t stream) {
@@ -407,6 +512,10 @@ int launch_typed(const DotShape& s, const DotScratch& plan, const void* lhs, con
     return e == cudaSuccess ? 1 : 0;
   }
   if (plan.path == 3) {
+    if (sgemm_ok(s, lhs, rhs, out)) {
+      dim3 grid((unsigned)((s.n + kSgBN - 1) / kSgBN), (unsigned)((s.m + kSgBM - 1) / kSgBM), (unsigned)batch);
+      return launch_kernel(sgemm_kernel, grid, dim3(256), 0, stream, pdl, s, (const float*)lhs, (const float*)rhs, (float*)out) == cudaSuccess ? 1 : 0;
+    }
     dim3 grid((unsigned)((s.n + kTile - 1) / kTile), (unsigned)((s.m + kTile - 1) / kTile), (unsigned)batch);
     return launch_kernel(tile_kernel<T>, grid, dim3(256), 0, stream, pdl, s, a, b, o) == cudaSuccess ? 1 : 0;
   }
@@ -659,6 +768,7 @@ int umma_eligible(const DotShape& s) {
   if (s.b0 * s.b1 != 1 || s.m < min_m || s.k < 1 || s.n < 1) return 0;
   if (s.lhs_k != 1 || (s.m > 1 && s.lhs_m % 8 != 0)) return 0;
   if (s.m > (1 << 20) || s.n > (1ll << 30) || s.k > (1ll << 30)) return 0;
+  if (s.rhs_s8) return s.rhs_n == 1 && s.rhs_k % 16 == 0 && s.rhs_k >= s.n ? 1 : 0;  // byte rows: 16-byte pitch
   if (s.rhs_n == 1 && s.rhs_k % 8 == 0 && s.rhs_k >= s.n) return 1;
   if (s.rhs_k == 1 && s.rhs_n % 8 == 0 && s.rhs_n >= s.k) return 2;
   return 0;
@@ -676,39 +786,49 @@ DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_maj
   int64_t tiles128 = 0;
   for (int g = 0; g < count; g++) tiles128 += (shapes[g].n + 127) / 128 * m_tiles;
   static const int wide = env_int("PJRTX_B200_UMMA_WIDE", 0);
-  p.nh = (wide && p.m_tile <= 128 && tiles128 * ((s.k + 63) / 64) >= 16 * (int64_t)sm_count) ? 2 : 1;
+  p.nh = (wide && !s.rhs_s8 && p.m_tile <= 128 && tiles128 * ((s.k + 63) / 64) >= 16 * (int64_t)sm_count) ? 2 : 1;
   const int tw = umma::kTileN * p.nh;
   int64_t tiles = 0;
   for (int g = 0; g < count; g++) tiles += (shapes[g].n + tw - 1) / tw * m_tiles;
-  const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(tiles * ((s.k + 63) / 64), sm_count));
-  // 128-deep stages once every CTA still gets a long run of them; 64-deep otherwise (finer split, better balance).
+  // Short activation tiles leave room for two CTAs per SM (half the shared memory each): while one CTA folds a tile or
+  // a kernel drains, the other CTA - or the first CTAs of the next kernel, which programmatic dependent launch has
+  // already placed - keeps the SM's copies in flight. PJRTX_B200_UMMA_CTAS=1 gives the single CTA back.
+  static const int ctas_wanted = env_int("PJRTX_B200_UMMA_CTAS", 2);
+  const bool w8 = s.rhs_s8 != 0;
+  const int per_sm = (ctas_wanted >= 2 && p.m_tile <= 64 && !w8 && p.nh == 1) ? 2 : 1;
+  const int64_t slots = (int64_t)sm_count * per_sm;
+  const size_t smem_budget = per_sm == 2 ? 112 * 1024 - 2048 : 227 * 1024 - 2048;
+  const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(tiles * ((s.k + 63) / 64), slots));
+  // 128-deep stages once every CTA still gets a long run of them; 64-deep otherwise (finer split, better balance), and
+  // whenever the ring would hold fewer than four of the deep ones.
   p.sub = (p.nh == 1 && tiles * ((s.k + 127) / 128) >= 32 * grid) ? 2 : 1;
+  if (p.sub == 2 && smem_budget / umma::stage_bytes(p.m_tile, 2, p.nh, w8) < 4) p.sub = 1;
   const int64_t kblocks = (s.k + 64 * p.sub - 1) / (64 * p.sub);
   const int64_t units = tiles * kblocks;
-  p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(units, sm_count));
+  p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(units, slots));
   // A split tile costs its f32 partial twice (written, read back): m_tile x 128 x 8 bytes per contributor, against
   // 128 x k x 2 bytes of weights per tile. Split only while the partials of a tile stay below about half its weights,
   // or when whole tiles would leave most of the machine idle.
   const int64_t split_ok = s.k / (8 * (int64_t)p.m_tile);
   p.whole_tiles = (split_ok < 2 || (p.m_tile >= 128 && 2 * tiles >= sm_count)) ? 1 : 0;
-  if (p.whole_tiles) p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count));
+  if (p.whole_tiles) p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, slots));
   p.per_cta = units / p.grid;
   p.max_contrib = p.whole_tiles ? 1 : (int)((kblocks + p.per_cta - 1) / p.per_cta) + 1;
-  const size_t stage = umma::stage_bytes(p.m_tile, p.sub, p.nh);
-  p.stages = (int)std::max<size_t>(2, std::min<size_t>(12, (227 * 1024 - 1536) / stage));
-  p.smem = umma::smem_bytes(p.stages, p.m_tile, p.sub, p.nh);
+  const size_t stage = umma::stage_bytes(p.m_tile, p.sub, p.nh, w8);
+  p.stages = (int)std::max<size_t>(2, std::min<size_t>(12, smem_budget / stage));
+  p.smem = umma::smem_bytes(p.stages, p.m_tile, p.sub, p.nh, w8);
   p.ksplit = p.max_contrib;
   p.partial_bytes = (uint64_t)tiles * p.max_contrib * p.m_tile * tw * sizeof(float);
   p.counter_bytes = (uint64_t)tiles * sizeof(unsigned);
   return p;
 }
 
-template <int SUB, int NH>
+template <int SUB, int NH, bool W8 = false>
 int launch_umma_sub(const umma::Params& prm, const umma::Maps& maps, const DotScratch& plan, bool pdl, cudaStream_t stream) {
-  if (!raise_smem_limit((const void*)umma::umma_stream_kernel<SUB, NH>, 227 * 1024)) return 0;
+  if (!raise_smem_limit((const void*)umma::umma_stream_kernel<SUB, NH, W8>, 227 * 1024)) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)plan.grid);
-  cfg.blockDim = dim3(umma::kThreads);
+  cfg.blockDim = dim3(W8 ? umma::kThreadsW8 : umma::kThreads);
   cfg.dynamicSmemBytes = plan.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -716,12 +836,15 @@ int launch_umma_sub(const umma::Params& prm, const umma::Maps& maps, const DotSc
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, umma::umma_stream_kernel<SUB, NH>, prm, maps) == cudaSuccess ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, umma::umma_stream_kernel<SUB, NH, W8>, prm, maps) == cudaSuccess ? 1 : 0;
 }
 
 int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs, void* const* out,
-                void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
+                void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream,
+                const void* const* scales) {
   const DotShape& s = shapes[0];
+  const bool w8 = s.rhs_s8 != 0;
+  if (w8 && (!scales || plan.path == 4 || plan.nh != 1)) return 0;
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return 0;
   const bool k_major = plan.path == 4;
@@ -738,7 +861,7 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
   // One 3-d copy per stage when every rhs is made of whole 64-column blocks (a ragged last block would make the
   // view read past the end of the last row).
   static const int allow_3d = env_int("PJRTX_B200_UMMA_3D", 1);
-  bool use_3d = allow_3d && !k_major;
+  bool use_3d = allow_3d && !k_major && !w8;
   for (int g = 0; g < count; g++) use_3d &= shapes[g].n % 64 == 0;
   int tiles = 0;
   for (int g = 0; g < count; g++) {
@@ -748,6 +871,7 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
     p.out[g] = out[g];
     p.n[g] = shapes[g].n;
     p.ldo[g] = shapes[g].out_m;
+    p.scale[g] = w8 ? scales[g] : nullptr;
   }
   auto encode_rhs = [&](bool three_d) {
     for (int g = 0; g < count; g++) {
@@ -755,6 +879,17 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
       cuuint32_t box[3];
       const cuuint32_t estr3[3] = {1, 1, 1};
       int rank = 2;
+      if (w8) {
+        // raw bytes: one box of 128 columns x 64 * SUB rows per stage, no swizzle (the converters place the values)
+        gdim[0] = (cuuint64_t)shapes[g].n; gdim[1] = (cuuint64_t)s.k;
+        gstride[0] = (cuuint64_t)shapes[g].rhs_k;
+        box[0] = 128; box[1] = (cuuint32_t)(64 * plan.sub);
+        if (enc(&maps.rhs[g], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(rhs[g]), gdim, gstride, box, estr3,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+          return false;
+        continue;
+      }
       if (three_d) {
         rank = 3;
         gdim[0] = 64; gdim[1] = (cuuint64_t)s.k; gdim[2] = (cuuint64_t)shapes[g].n / 64;
@@ -801,6 +936,8 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
   p.rhs_k_major = k_major ? 1 : 0;
   p.early_rhs = early_rhs ? 1 : 0;
   p.whole_tiles = plan.whole_tiles;
+  if (w8)
+    return plan.sub == 2 ? launch_umma_sub<2, 1, true>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 1, true>(p, maps, plan, pdl, stream);
   if (plan.nh == 2)
     return plan.sub == 2 ? launch_umma_sub<2, 2>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 2>(p, maps, plan, pdl, stream);
   return plan.sub == 2 ? launch_umma_sub<2, 1>(p, maps, plan, pdl, stream) : launch_umma_sub<1, 1>(p, maps, plan, pdl, stream);
@@ -868,11 +1005,40 @@ int dot_chain_launch(const DotChainSegment* segs, const DotChainArgs* args, int 
   }
 }
 
+namespace {
+// One CTA waits, with the streaming kernel's own bounded wait, on an mbarrier that nothing ever completes.
+__global__ void bounded_wait_probe_kernel(unsigned long long timeout_ns, int* error_flag) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    tma::mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const tma::WaitBudget budget{tma::global_timer_ns() + timeout_ns, &abort_word};
+  if (!tma::mbar_wait(&bar, 0, budget) && threadIdx.x == 0) atomicExch(error_flag, 31);
+}
+}  // namespace
+
+int bounded_wait_probe_launch(unsigned timeout_ms, int* error_flag, cudaStream_t stream) {
+  if (!error_flag || timeout_ms < 1 || timeout_ms > 1000) return 0;
+  bounded_wait_probe_kernel<<<1, 64, 0, stream>>>((unsigned long long)timeout_ms * 1000000ull, error_flag);
+  return cudaGetLastError() == cudaSuccess ? 1 : 0;
+}
+
+bool dot_s8_supported(const DotShape& s) {
+  DotShape probe = s;
+  probe.rhs_s8 = 1;
+  return umma_eligible(probe) == 1;
+}
+
 int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
                      void* const* out, void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const void* const* scales) {
   if (count < 1 || count > kDotGroupMax) return 0;
-  if (plan.umma) return launch_umma(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
+  if (plan.umma) return launch_umma(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream, scales);
+  if (shapes[0].rhs_s8) return 0;  // int8 weights run on the tensor-core stream only
   if (plan.tma) {
     switch (shapes[0].dtype) {
       case kF32: return launch_tma<float>(shapes, count, plan, lhs, rhs, out, partials, counters, error_flag, early_rhs, pdl, stream);
@@ -920,13 +1086,15 @@ DotScratch dot_plan(const DotShape& s, int sm_count) {
 }
 
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out, void* partials,
-               void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream) {
+               void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream, const void* scale) {
   if (s.b0 * s.b1 * s.m * s.n == 0) return 1;
   if (plan.umma || (plan.path == 1 && plan.tma)) {
     const void* rhs_list[1] = {rhs};
     void* out_list[1] = {out};
-    return dot_group_launch(&s, 1, plan, lhs, rhs_list, out_list, partials, counters, error_flag, early_rhs, pdl, stream);
+    const void* scale_list[1] = {scale};
+    return dot_group_launch(&s, 1, plan, lhs, rhs_list, out_list, partials, counters, error_flag, early_rhs, pdl, stream, scale_list);
   }
+  if (s.rhs_s8) return 0;
   switch (s.dtype) {
     case kF32: return launch_typed<float>(s, plan, lhs, rhs, out, partials, counters, pdl, stream);
     case kF16: return launch_typed<__half>(s, plan, lhs, rhs, out, partials, counters, pdl, stream);

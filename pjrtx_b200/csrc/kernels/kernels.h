@@ -57,6 +57,9 @@ struct DotShape {
   int64_t lhs_b0 = 0, lhs_b1 = 0, lhs_m = 0, lhs_k = 1;
   int64_t rhs_b0 = 0, rhs_b1 = 0, rhs_k = 0, rhs_n = 1;
   int64_t out_b0 = 0, out_b1 = 0, out_m = 0;  // out n stride is 1
+  // 1: the rhs holds signed bytes with one f16 scale per column n; the contraction uses
+  // round_to_dtype(round_f16(f16(byte) * scale)) as rhs[k, n] (the program's convert * multiply [* convert]).
+  int rhs_s8 = 0;
 };
 
 // Scratch a split-K streaming contraction needs: f32 partials + tile counters.
@@ -84,9 +87,10 @@ DotScratch dot_group_plan(const DotShape* shapes, int count, int sm_count, bool 
 // `error_flag` (device-visible int) receives a non-zero code if a bounded device-side wait gives up.
 // `early_rhs`: the rhs operands are never written by earlier work of the same stream, so their copies may start
 // before the preceding kernel has finished (programmatic dependent launch).
+// `scales` (one f16 pointer per contraction) is read only when the shapes have `rhs_s8`.
 int dot_group_launch(const DotShape* shapes, int count, const DotScratch& plan, const void* lhs, const void* const* rhs,
                      void* const* out, void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const void* const* scales = nullptr);
 
 // Chooses the kernel for a shape and sizes its scratch.
 DotScratch dot_plan(const DotShape& s, int sm_count);
@@ -137,7 +141,10 @@ DotChainPlan dot_chain_plan(const DotChainSegment* segs, int n, int sm_count);
 int dot_chain_launch(const DotChainSegment* segs, const DotChainArgs* args, int n, const DotChainPlan& plan, void* partials,
                      void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream);
 int dot_launch(const DotShape& s, const DotScratch& plan, const void* lhs, const void* rhs, void* out,
-               void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream);
+               void* partials, void* counters, int* error_flag, bool early_rhs, bool pdl, cudaStream_t stream,
+               const void* scale = nullptr);
+// True when an int8-weight contraction of this shape has a kernel (the tensor-core stream with in-kernel dequantisation).
+bool dot_s8_supported(const DotShape& s);
 
 // out[m, n] = lhs[m, k] . rhs[k, n] (dense row-major device pointers) with split-K scratch taken from a fixed
 // array in the library image instead of an allocation. 1 on success, 0 with last_error set.
@@ -146,6 +153,11 @@ int stream_dot_static_scratch(int device, int dtype, const void* lhs, const void
 // Waits for `stream` and reports whether the most recent static-scratch contraction on the device ran to completion
 // (1) or gave up a bounded device-side wait (0 with last_error set). Allocates nothing.
 int stream_dot_static_scratch_status(int device, cudaStream_t stream);
+
+// Self-test of the bounded device-side waits: one CTA waits (with the wait the streaming kernels use) for an mbarrier
+// that nothing completes, gives up after `timeout_ms` (1..1000) and raises `error_flag` with code 31. The kernel
+// returns normally; nothing faults or hangs.
+int bounded_wait_probe_launch(unsigned timeout_ms, int* error_flag, cudaStream_t stream);
 
 // dynamic_update_slice: writes `update` into `dst` (already holding the operand)
 // at start indices read from device scalars, clamped as StableHLO requires.

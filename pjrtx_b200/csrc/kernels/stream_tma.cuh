@@ -384,15 +384,15 @@ __device__ __forceinline__ bool run_units(const Params& p, const Segment& sg, co
             for (int idx = threadIdx.x; idx < M * COLS; idx += kConsumers) {
               const int m = idx / COLS, c = idx % COLS;
               float t = 0.f;
-              int q = 0;
-              for (; q + 8 <= contributors; q += 8) {  // loads first, then the adds in CTA order
-                float v[8];
+              // All of a tile's partials (12 to 19 contributors at the decode shapes) are requested in one round of
+              // loads, then added in CTA order: the fold sits in the kernel's tail, where a round trip is what it costs.
+              for (int q = 0; q < contributors; q += 24) {
+                float v[24];
 #pragma unroll
-                for (int e = 0; e < 8; e++) v[e] = __ldcg(base + (long long)(q + e) * M * COLS + idx);
+                for (int e = 0; e < 24; e++) v[e] = q + e < contributors ? __ldcg(base + (long long)(q + e) * M * COLS + idx) : 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; e++) t += v[e];
+                for (int e = 0; e < 24; e++) t += v[e];
               }
-              for (; q < contributors; q++) t += __ldcg(base + (long long)q * M * COLS + idx);
               emit(m, c, t);
             }
             if (threadIdx.x == 0) sg.counters[cur_tile] = 0;

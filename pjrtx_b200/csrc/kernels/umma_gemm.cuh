@@ -25,8 +25,18 @@
 // Programmatic dependent launch: weights are never written by earlier work of the stream (`early_rhs`), so their
 // copies for the first ring of stages are issued before griddepcontrol.wait; activation copies and all stores wait.
 //
-// Every mbarrier wait is bounded; on a timeout the kernel sets *error_flag, every role falls through to the common
-// exit, the allocating warp frees its tensor memory, and the kernel returns.
+// Int8 weights (W8): the rhs is [k, n] signed bytes with one f16 scale per column, the program's
+// convert(s8 -> f16) * scale [-> bf16] feeding the contraction. The weights stay one byte wide in HBM: a stage receives
+// the raw bytes, eight converter warps write the integers (exact in either 16-bit type) into the swizzled operand tile
+// the tensor core reads, the MMA lane waits for `ready` (converted) instead of `full`, and the epilogue multiplies each
+// accumulator by its column's scale in f32. That is the contraction the program wrote with the scale moved out of the
+// sum: sum_k x[k] * (w[k,n] * s[n]) = s[n] * sum_k x[k] * w[k,n]. The op-by-op program rounds every w * s to the element
+// type first; this form skips that rounding (one relative 2^-9 per weight at bf16), so the two agree to rounding, not
+// bit for bit, and a product w * s that overflows f16 in the written program stays finite here.
+//
+// Every mbarrier wait is bounded by time (two seconds per launch; the thread that sees the deadline pass sets a CTA-wide
+// abort word and every other wait gives up at its next check); the kernel then sets *error_flag, every role falls
+// through to the common exit, the allocating warp frees its tensor memory, and the kernel returns.
 #pragma once
 
 #include <cuda.h>
@@ -42,7 +52,8 @@ constexpr int kGroupMax = 4;
 constexpr int kTileN = 128;          // weight columns per tile (MMA M)
 constexpr int kSubK = 64;            // k elements per swizzle row (128 bytes of 16-bit data)
 constexpr int kThreads = 192;        // warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer
-constexpr unsigned kSpinLimit = 1u << 22;
+constexpr int kThreadsW8 = 448;      // ... plus warps 6-13: int8 -> 16-bit converters
+constexpr unsigned long long kTimeoutNs = 2000000000ull;  // budget of one launch for all of its waits
 
 struct Params {
   int m, k;
@@ -65,6 +76,7 @@ struct Params {
   int rhs_3d;            // rhs [k, n] with n % 64 == 0: one copy per stage through a 3-d view {64 n, k, n / 64}
   int early_rhs;         // rhs copies may start before the preceding kernel of the stream has finished
   int whole_tiles;       // 1: CTA b owns tiles [b*T/G, (b+1)*T/G) completely instead of an equal share of units
+  const void* scale[kGroupMax];  // W8: f16 scale per weight column
 };
 
 struct Maps {
@@ -95,10 +107,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  for (unsigned spin = 0; spin < kSpinLimit; spin++)
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Deadline of the launch (every thread reads the timer when it starts) and the CTA's abort word in shared memory.
+struct WaitBudget {
+  unsigned long long deadline;
+  volatile int* abort;
+};
+// Bounded by time: gives up when the launch's deadline has passed or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, const WaitBudget& w) {
+  for (unsigned spin = 0;; spin++) {
     if (mbar_try_wait(bar, parity)) return true;
-  return false;
+    if ((spin & 15) == 15) {
+      if (*w.abort) return false;
+      if (global_timer_ns() > w.deadline) {
+        *w.abort = 1;
+        return false;
+      }
+    }
+  }
 }
 // x = innermost coordinate (always a multiple of 64 elements here, i.e. 128 bytes), y = outer coordinate.
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -170,13 +200,14 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__host__ __device__ inline size_t stage_bytes(int m_tile, int sub, int nh) {
-  return (size_t)sub * ((size_t)nh * 16384 + (size_t)m_tile * 128);
+// A stage: the weight operand tile (16-bit, swizzled), the activation tile, and with int8 weights the raw bytes.
+__host__ __device__ inline size_t stage_bytes(int m_tile, int sub, int nh, bool w8 = false) {
+  return (size_t)sub * ((size_t)nh * 16384 + (size_t)m_tile * 128 + (w8 ? (size_t)nh * 8192 : 0));
 }
-inline size_t smem_bytes(int stages, int m_tile, int sub, int nh) {
+inline size_t smem_bytes(int stages, int m_tile, int sub, int nh, bool w8 = false) {
   // stages (every block 1024-byte aligned: m_tile is a multiple of 16, so m_tile * 128 is a multiple of 2048) +
   // barriers and flags + slack for aligning the dynamic segment to 1024 bytes
-  return (size_t)stages * stage_bytes(m_tile, sub, nh) + 1024 + 512;
+  return (size_t)stages * stage_bytes(m_tile, sub, nh, w8) + 1024 + 512;
 }
 
 struct Cursor {
@@ -210,21 +241,24 @@ __device__ __forceinline__ void advance(const Params& p, Cursor* c) {
 
 // SUB: 64-deep k sub-blocks per stage (1 or 2). NH: 128-column halves per tile (1 or 2); two halves make every weight
 // row of a stage 512 contiguous bytes in memory and take two accumulators per tile (so m_tile <= 128).
-template <int SUB, int NH>
-__global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p, const __grid_constant__ Maps maps) {
+template <int SUB, int NH, bool W8 = false>
+__global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_kernel(const Params p, const __grid_constant__ Maps maps) {
   extern __shared__ unsigned char smem_dyn[];
   // 128-byte swizzled tiles need 1024-byte aligned bases.
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
-  const uint32_t per_stage = (uint32_t)stage_bytes(p.m_tile, SUB, NH);
+  const uint32_t per_stage = (uint32_t)stage_bytes(p.m_tile, SUB, NH, W8);
   const uint32_t a_bytes = NH * SUB * 16384u;
+  const uint32_t raw_offset = a_bytes + (uint32_t)SUB * p.m_tile * 128u;  // W8: raw bytes behind the activation tile
   constexpr int TW = kTileN * NH;  // tile width in weight columns
   uint64_t* full = reinterpret_cast<uint64_t*>(base_ptr + (size_t)p.stages * per_stage);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;   // [2]
   uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  int* flags = reinterpret_cast<int*>(tmem_slot + 1);  // [0] is_last of a fold
+  uint64_t* ready = acc_empty + 2;         // [stages], W8: the converters have rebuilt the stage's weight tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ready + p.stages);
+  int* flags = reinterpret_cast<int*>(tmem_slot + 1);  // [0] is_last of a fold, [1] abort
+  const WaitBudget budget{global_timer_ns() + kTimeoutNs, flags + 1};
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -243,12 +277,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
     for (int s = 0; s < p.stages; s++) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      mbar_init(&ready[s], (kThreadsW8 - kThreads) / 32);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);
     }
     flags[0] = 0;
+    flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -263,10 +299,17 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
   if (warp == 4) {
     // ---- TMA producer ------------------------------------------------------------------------------------------
     if (lane == 0 && count > 0) {
-      const unsigned tx = per_stage;
+      // bytes the copies of one stage deliver: weight tile (16-bit, or raw bytes with int8 weights) + activation tile
+      const unsigned tx = W8 ? (unsigned)(NH * SUB * 8192u + SUB * p.m_tile * 128u) : per_stage;
       auto load_rhs = [&](const Cursor& c, int stage) {
         const uint32_t st = base + (uint32_t)stage * per_stage;
         const int k0 = c.kb * (kSubK * SUB), n0 = c.n_tile * TW;
+        if (W8) {
+          // Raw bytes [64 * SUB k rows][128 columns] per half, unswizzled.
+#pragma unroll
+          for (int h = 0; h < NH; h++) tma_load_2d(st + raw_offset + h * (SUB * 8192u), &maps.rhs[c.group], n0 + h * kTileN, k0, &full[stage]);
+          return;
+        }
         if (p.rhs_3d) {
           // Blocks of 64 columns are the outer coordinate: the box lands as [column block][k row][128 bytes], which
           // is the layout the two-box form produces, in one copy of 16 * SUB * NH KiB.
@@ -315,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
       int stage = first % p.stages;
       unsigned phase = first == p.stages ? 1 : 0;
       for (int i = first; i < count; i++) {
-        if (i >= p.stages && !mbar_wait(&empty[stage], phase ^ 1)) {
+        if (i >= p.stages && !mbar_wait(&empty[stage], phase ^ 1, budget)) {
           atomicExch(p.error_flag, 11);
           break;
         }
@@ -345,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
           // New tile segment: take the next accumulator once the epilogue has drained its previous use.
           cur_tile = cur.tile;
           const int buf = seg & 1;
-          if (seg >= 2 && !mbar_wait(&acc_empty[buf], ((seg >> 1) & 1) ^ 1)) {
+          if (seg >= 2 && !mbar_wait(&acc_empty[buf], ((seg >> 1) & 1) ^ 1, budget)) {
             atomicExch(p.error_flag, 14);
             break;
           }
@@ -353,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
           acc = tmem_base + (uint32_t)(buf * NH * p.m_tile);
           fresh = true;
         }
-        if (!mbar_wait(&full[stage], phase)) {
+        if (!mbar_wait(W8 ? &ready[stage] : &full[stage], phase, budget)) {
           atomicExch(p.error_flag, 12);
           break;
         }
@@ -390,7 +433,76 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
         }
       }
     }
-  } else {
+  } else if (W8 && warp >= 6) {
+    // ---- converters (warps 6-13): raw s8 tile -> swizzled 16-bit operand tile ----------------------------------------
+    // Thread t owns the 16 columns nc * 16 .. + 15 (nc = t % 8) of rows t / 8, t / 8 + 32, ... : one 16-byte read of
+    // raw bytes per row, two 16-byte writes of eight 16-bit values each at their swizzled places. The values written
+    // are the integers themselves (exact in f16 and bf16); the column scales multiply the accumulators.
+    if (count > 0) {
+      const int t = threadIdx.x - kThreads;
+      const int nc = t & 7, row0 = t >> 3;
+      constexpr int ROWS = 2 * SUB;  // rows per thread and half: 64 * SUB rows over 32 row slots
+      int stage = 0;
+      unsigned phase = 0;
+      for (int i = 0; i < count; i++) {
+        if (!mbar_wait(&full[stage], phase, budget)) {
+          if (lane == 0) atomicExch(p.error_flag, 15);
+          break;
+        }
+        unsigned char* st = base_ptr + (size_t)stage * per_stage;
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+          const unsigned char* raw = st + raw_offset + h * (SUB * 8192u) + row0 * 128 + nc * 16;
+          unsigned char* dst = st + h * (SUB * 16384u) + (nc >> 2) * (SUB * 8192u);
+          uint4 q[ROWS];  // every row of this thread is requested before the first is converted
+#pragma unroll
+          for (int r = 0; r < ROWS; r++) q[r] = *reinterpret_cast<const uint4*>(raw + r * 32 * 128);
+#pragma unroll
+          for (int r = 0; r < ROWS; r++) {
+            const int k = row0 + 32 * r;
+            const uint32_t words[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+            uint32_t packed[8];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+              if (p.is_bf16) {
+                // b = low7 - 128 * sign. {0x43, low7} is the bf16 128 + low7 and {0x43, sign << 7} is 128 or 256:
+                // their difference is b, exactly.
+                const uint32_t low7 = words[w] & 0x7f7f7f7fu, sign = words[w] & 0x80808080u;
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                  const uint32_t sel = e ? 0x4342 : 0x4140;
+                  const uint32_t x = __byte_perm(low7, 0x43434343u, sel), y = __byte_perm(sign, 0x43434343u, sel);
+                  const __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&x), *reinterpret_cast<const __nv_bfloat162*>(&y));
+                  packed[w * 2 + e] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+              } else {
+                // {0x64, b + 128} is the f16 1024 + 128 + b.
+                const uint32_t flipped = words[w] ^ 0x80808080u;
+                const __half2 bias = __float2half2_rn(1152.0f);
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                  const uint32_t x = __byte_perm(flipped, 0x64646464u, e ? 0x4342 : 0x4140);
+                  const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&x), bias);
+                  packed[w * 2 + e] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+              }
+            }
+            const int cc = (nc & 3) * 2;  // first of this thread's two 16-byte column chunks inside the 64-column box
+            *reinterpret_cast<uint4*>(dst + k * 128 + (((cc) ^ (k & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(dst + k * 128 + (((cc + 1) ^ (k & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          }
+        }
+        // The tile was written through the generic proxy; the tensor core reads it through the async proxy.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready[stage]);
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp < 4) {
     // ---- epilogue warps 0..3: TMEM lane quarter = warp index ------------------------------------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (count > 0) {
@@ -405,7 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
         locate_tile(p, &c);
         const int buf = seg & 1;
         // One decision for all four warps: tcgen05.ld is warp-collective and named barriers follow.
-        const bool ok = epilogue_all(mbar_wait(&acc_full[buf], (seg >> 1) & 1));
+        const bool ok = epilogue_all(mbar_wait(&acc_full[buf], (seg >> 1) & 1, budget));
         if (!ok) {
           if (threadIdx.x == 0) atomicExch(p.error_flag, 13);
           break;
@@ -425,6 +537,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
 #pragma unroll
         for (int h = 0; h < NH; h++) {
           const long long n = n_first + h * kTileN;
+          // Int8 weights: the tensor core contracted the integers; this thread's column scale finishes the product.
+          const float scale = W8 ? (n < n_total ? __half2float(static_cast<const __half*>(p.scale[c.group])[n]) : 0.f) : 1.f;
           const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((buf * NH + h) * p.m_tile);
           for (int c0 = 0; c0 < m_rows; c0 += 16) {
             uint32_t r[16];
@@ -434,6 +548,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                 : "r"(taddr + (uint32_t)c0));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (W8) {
+#pragma unroll
+              for (int j = 0; j < 16; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) * scale);
+            }
             if (contributors > 1) {
 #pragma unroll
               for (int j = 0; j < 16; j++)
@@ -470,8 +588,24 @@ __global__ void __launch_bounds__(kThreads, 1) umma_stream_kernel(const Params p
                 float t[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) t[j] = 0.f;
-#pragma unroll 2
-                for (int q = 0; q < contributors; q++) {
+                // Four contributors' rows are requested at once (64 loads in flight per thread: the fold of a tile
+                // with fifteen contributors is a quarter of a megabyte through one CTA, so its time is round trips),
+                // then added in CTA order.
+                int q = 0;
+                for (; q + 4 <= contributors; q += 4) {
+                  float v[4][16];
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    const float* src = first_slot + (long long)(q + e) * slot_stride + r0 * TW + h * kTileN + n_local;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[e][j] = (r0 + j < m_rows) ? __ldcg(src + j * TW) : 0.f;
+                  }
+#pragma unroll
+                  for (int e = 0; e < 4; e++)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) t[j] += v[e][j];
+                }
+                for (; q < contributors; q++) {
                   const float* src = first_slot + (long long)q * slot_stride + r0 * TW + h * kTileN + n_local;
                   float v[16];
 #pragma unroll

@@ -120,21 +120,34 @@ def test_tiny_prefill(gpu_backend):
     assert outs[0].to_numpy().shape == (batch,)
 
 
-def test_int8_weight_only_decode(gpu_backend):
-    """Dequantisation written as convert + multiply feeding dot_general."""
+@pytest.mark.parametrize("batch,dtype", [(2, P.BF16_CODE), (16, P.BF16_CODE), (5, P.BF16_CODE), (16, P.F16)])
+def test_int8_weight_only_decode(gpu_backend, monkeypatch, batch, dtype):
+    """Dequantisation written as convert + multiply feeding dot_general. From three rows up the contractions read the
+    bytes themselves (tensor-core stream with in-kernel dequantisation, weights one byte wide in HBM); the result must be
+    what the written program gives, within tolerance of the oracle and equal to the materialising path's to rounding."""
     import dataclasses
 
     be = gpu_backend
-    cfg = dataclasses.replace(llama.TINY, int8_weights=True)
-    batch, max_len, filled = 2, 64, 40
+    cfg = dataclasses.replace(llama.TINY, int8_weights=True, dtype=dtype)
+    max_len, filled = 64, 40
     builder, names = llama.build_decode_step(cfg, batch, max_len, return_logits=True)
     weights = llama.make_weights(cfg, seed=0)
     caches = llama.make_kv_cache(cfg, batch, max_len, filled)
-    args = [np.array([5, 9], np.int32), np.array(filled, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
+    tokens = (np.arange(batch, dtype=np.int32) * 37 + 5) % cfg.vocab
+    args = [tokens, np.array(filled, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
     want = run_oracle(builder, args)
     exe = be.compile_executable(builder, [0])
+    dots = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
+    assert all(s["rhs_s8"] == (1 if batch >= 3 else 0) for s in dots), dots
     outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
-    assert_close(outs[1].to_numpy(), want[1], 2e-2, what="int8 logits")
+    logits = outs[1].to_numpy()
+    assert_close(logits, want[1], 2e-2, what="int8 logits")
+    if batch >= 3:
+        monkeypatch.setenv("PJRTX_B200_FUSE_DEQUANT", "0")
+        plain = be.compile_executable(builder, [0])
+        assert all(s["rhs_s8"] == 0 for s in plain.describe()["kernel_plan"]["steps"] if s["type"] == "dot")
+        ref = be.execute_executable(plain, [be.buffer_from_host(a) for a in args])[1].to_numpy()
+        assert_close(logits, ref, 2e-2, what="in-kernel dequantisation vs materialised weights")
 
 
 def test_unfused_attention_path_agrees(gpu_backend, monkeypatch):

@@ -82,6 +82,30 @@ def test_8b_width_decode_two_layers(gpu_backend, weights_8b_two_layers, monkeypa
     print(f"8B-width batch {batch}: logits max-abs error over 2 steps {worst:.4e}")
 
 
+def test_8b_width_int8_decode_two_layers(gpu_backend):
+    """Weight-only int8 at the 8B widths, batch 16: every projection (and the 128256-column LM head) reads signed bytes
+    and f16 column scales and dequantises inside the tensor-core stream; two layers, 512 cached positions."""
+    be = gpu_backend
+    cfg = dataclasses.replace(llama.LLAMA3_8B, layers=2, int8_weights=True)
+    batch, filled, max_len = 16, 512, 512 + 8
+    builder, names = llama.build_decode_step(cfg, batch, max_len, return_logits=True)
+    weights = llama.make_weights(cfg, seed=0, threads=THREADS, embed_period=4096)
+    caches = llama.make_kv_cache(cfg, batch, max_len, filled)
+    exe = be.compile_executable(builder, [0])
+    dots = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
+    assert dots and all(s["rhs_s8"] == 1 and s["umma"] == 1 for s in dots), dots
+    tokens = (np.arange(batch, dtype=np.int32) * 4099 + 17) % cfg.vocab
+    args = [tokens, np.array(filled, np.int32)] + [weights[n] for n in names[2:2 + len(weights)]] + caches
+    want = run_oracle(builder, args)
+    outs = be.execute_executable(exe, [be.buffer_from_host(a) for a in args])
+    got = outs[1].to_numpy()
+    assert_close(got, want[1], 2e-2, what="int8 logits at 8B width")
+    err = float(np.max(np.abs(got.astype(np.float32) - np.asarray(want[1]).astype(np.float32))))
+    keep = _decisive(want[1], err)
+    assert np.array_equal(outs[0].to_numpy()[keep], np.asarray(want[0])[keep])
+    print(f"8B-width int8 batch {batch}: logits max-abs error {err:.4e}")
+
+
 def _local_weights(cfg, names, table, seed=0):
     """Seeded N(0, 0.02) tensors at the LOCAL shapes of one tensor-parallel rank (a shard of an i.i.d. tensor is an
     i.i.d. tensor, so the full 140 GB model never has to exist on the host)."""

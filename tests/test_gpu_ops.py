@@ -126,12 +126,16 @@ def test_config1_fused_chain_and_reductions(gpu_backend):
     # row sums: relative to the magnitude that was summed (cancellation makes |sum| << sum|terms|)
     assert np.max(np.abs(got[0].astype(np.float64) - want[0]) / z_abs_sum) <= 1e-5
     assert_close(got[1], want[1], 1e-5, what="row max")
-    # argmax is bit-exact wherever the f32 maximum itself is unambiguous; elsewhere the chosen element must hold the max
-    z32 = want[1]
-    same = got[2] == want[2]
-    zf = (x * y + np.sin(x) - np.log1p(np.abs(y)))
-    picked = zf[np.arange(zf.shape[0]), got[2]]
-    assert same.mean() >= 0.999 and np.all(np.abs(picked - z32) <= 1e-5 * np.abs(z32) + 1e-6)
+    # argmax: the oracle rounds a float64 z, the kernel's sinf / log1pf differ from that by an ulp, so a row whose two
+    # best z lie within that ulp can pick the other index. Every differing row must be such a row: the z the oracle holds
+    # at the kernel's index is within two float32 ulps of the oracle's maximum. All other rows are bit-exact.
+    z32 = np.asarray(want[1], np.float32)
+    zf = (x * y + np.sin(x) - np.log1p(np.abs(y))).astype(np.float32)
+    differing = np.nonzero(got[2] != want[2])[0]
+    picked = zf[differing, got[2][differing]]
+    ulp = np.spacing(np.abs(z32[differing]))
+    assert np.all(np.abs(picked.astype(np.float64) - z32[differing]) <= 2 * ulp), (len(differing), differing[:8])
+    assert len(differing) <= 0.001 * len(z32)  # and there are few of them
 
 
 @pytest.mark.parametrize("dtype", [P.F32, P.F16])
@@ -439,3 +443,20 @@ def test_prefill_attention_same_as_written_chain(gpu_backend, monkeypatch):
     assert "attention_prefill" not in [s["type"] for s in exe.describe()["kernel_plan"]["steps"]]
     plain = run_backend(gpu_backend, b, args, exe=exe)
     assert_close(fused[0], plain[0], 2e-2, what="prefill attention kernel vs chain")
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_survives(gpu_backend):
+    """Failure detection without a GPU fault (the reference injects failures on the host, src/runtime/execution_call.zig:
+    355-360): a CTA waits for a barrier nothing completes, gives up after 50 ms and raises the device's error word; the
+    host reads it at the next synchronize, the word is cleared, and the device keeps computing correctly."""
+    be = gpu_backend
+    be.synchronize(0)
+    t0 = be.record_event(0)
+    be.bounded_wait_probe(0, timeout_ms=50)
+    t1 = be.record_event(0)
+    with pytest.raises(be_mod.BackendError, match=r"gave up a bounded wait \(code 31\)"):
+        be.synchronize(0)
+    assert 40.0 <= be.elapsed_ms(t0, t1) <= 500.0  # the wait ended by its time limit, not by a poll count
+    be.synchronize(0)  # the word was cleared by the failed call
+    b, args = cases.u8_chain()
+    assert run_backend(be, b, args)[0].tolist() == [6, 15, 28, 45]
