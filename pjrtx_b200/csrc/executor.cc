@@ -1103,7 +1103,9 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
   // 3.58 (every CTA repeats the row reduction after it has waited for its predecessor, where the one-CTA norm kernel ran
   // concurrently with the next contraction's ramp); chained 4.16 (a segment boundary - fold, grid barrier, factors,
   // first lhs values - is 7 to 8 us of dependent round trips against the 4 us of weights the rings hold).
-  if (env_flag_local("PJRTX_B200_DOT_FUSE", false)) {
+  const char* fuse_env = getenv("PJRTX_B200_DOT_FUSE");
+  const bool fuse_silu_only = fuse_env && std::string(fuse_env) == "silu";  // only the silu(gate) * up transform
+  if (fuse_silu_only || env_flag_local("PJRTX_B200_DOT_FUSE", false)) {
     auto chainable = [&](const Step& st) {
       return st.type == Step::kDot && st.dot_scratch.path == 1 && st.dot_scratch.tma == 1 && st.dot_scratch.umma == 0 &&
              st.dot.b0 * st.dot.b1 == 1;
@@ -1317,7 +1319,7 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
       Step& d = kp->steps[i];
       if (!d.segs.empty() && !fused.empty() && fused.back().type == Step::kFused) {
         Step* prev_dot = fused.size() >= 2 && !fused[fused.size() - 2].segs.empty() ? &fused[fused.size() - 2] : nullptr;
-        if (match_silu(fused.back(), d) || match_norm(fused.back(), d, prev_dot)) {
+        if (match_silu(fused.back(), d) || (!fuse_silu_only && match_norm(fused.back(), d, prev_dot))) {
           for (size_t n : fused.back().nodes) d.nodes.push_back(n);
           fused.pop_back();
         }
@@ -1686,6 +1688,13 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
     if (timed && step_index > 0) record_step_event(exe->step_events[step_index], dev->stream, capturing);
     step_index++;
     exe->pdl = pdl_setting && !(ordered_first && *launches == launches_at_entry);
+#ifdef PJRTX_DEBUG_SKIP
+    {
+      // Timing diagnostic of a special build only: leave out every step of the named types (results are then wrong).
+      static const char* skip = getenv("PJRTX_DEBUG_SKIP");
+      if (skip && strstr(skip, ("," + step_type_name(st.type) + ",").c_str())) continue;
+    }
+#endif
     switch (st.type) {
       case Step::kFused: {
         std::vector<void*> addr;

@@ -17,8 +17,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cuda.h>
+
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "../common.h"
 #include "kernels.h"
@@ -96,6 +99,17 @@ struct DecodeArgs {
   unsigned long long timeout_ns;
 };
 
+constexpr int kMergeChunk = 24;  // splits whose (max, sum, value) a merging thread requests at once
+
+// PJRTX_B200_ATTENTION_COOP_MERGE=0 makes the CTA that arrives last merge a tile's splits alone.
+inline bool coop_merge_allowed() {
+  static const bool allowed = [] {
+    const char* e = getenv("PJRTX_B200_ATTENTION_COOP_MERGE");
+    return !(e && *e && atoi(e) == 0);
+  }();
+  return allowed;
+}
+
 // Every CTA asks for its share of [prefetch, prefetch + prefetch_bytes) in 16 KiB bulk requests (no destination, no
 // completion to wait for).
 __device__ __forceinline__ void prefetch_next_weights(const DecodeArgs& a) {
@@ -152,16 +166,56 @@ __device__ __forceinline__ void merge_splits(const DecodeArgs& a, long long tile
     const int lo = split * per, hi = min(lo + per, REP * HD);
     const float* base = a.workspace + tile * a.splits * (long long)REP * (HD + 2);
     const long long split_stride = (long long)REP * (HD + 2);
+    // All loads of a round are issued before the first is used (a dependent load per split would cost a round trip to
+    // L2 each): up to kMergeChunk splits need one round, more need two passes of chunks.
+    constexpr int CH = kMergeChunk;
     for (int idx = lo + threadIdx.x; idx < hi; idx += THREADS) {
       const int r = idx / HD, d = idx % HD;
-      float mm = -INFINITY;
-      for (int sp = 0; sp < a.splits; sp++) mm = fmaxf(mm, __ldcg(base + sp * split_stride + r * (HD + 2) + HD));
-      float acc = 0.f, lsum = 0.f;
-      for (int sp = 0; sp < a.splits; sp++) {  // split order, the same arithmetic as the single-CTA merge
-        const float ms = __ldcg(base + sp * split_stride + r * (HD + 2) + HD);
-        const float w = ms == -INFINITY ? 0.f : __expf(ms - mm);
-        lsum = fmaf(__ldcg(base + sp * split_stride + r * (HD + 2) + HD + 1), w, lsum);
-        acc = fmaf(__ldcg(base + sp * split_stride + r * (HD + 2) + d), w, acc);
+      const float* row = base + r * (HD + 2);
+      float mm = -INFINITY, acc = 0.f, lsum = 0.f;
+      if (a.splits <= CH) {
+        float ms[CH], lv[CH], ov[CH];
+#pragma unroll
+        for (int u = 0; u < CH; u++) {
+          const bool in = u < a.splits;
+          const float* src = row + (in ? u : 0) * split_stride;
+          ms[u] = in ? __ldcg(src + HD) : -INFINITY;
+          lv[u] = in ? __ldcg(src + HD + 1) : 0.f;
+          ov[u] = in ? __ldcg(src + d) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < CH; u++) mm = fmaxf(mm, ms[u]);
+#pragma unroll
+        for (int u = 0; u < CH; u++) {  // split order, the same arithmetic as the single-CTA merge
+          const float w = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - mm);
+          lsum = fmaf(lv[u], w, lsum);
+          acc = fmaf(ov[u], w, acc);
+        }
+      } else {
+        for (int sp0 = 0; sp0 < a.splits; sp0 += CH) {
+          float ms[CH];
+#pragma unroll
+          for (int u = 0; u < CH; u++) ms[u] = sp0 + u < a.splits ? __ldcg(row + (sp0 + u) * split_stride + HD) : -INFINITY;
+#pragma unroll
+          for (int u = 0; u < CH; u++) mm = fmaxf(mm, ms[u]);
+        }
+        for (int sp0 = 0; sp0 < a.splits; sp0 += CH) {
+          float ms[CH], lv[CH], ov[CH];
+#pragma unroll
+          for (int u = 0; u < CH; u++) {
+            const bool in = sp0 + u < a.splits;
+            const float* src = row + (in ? sp0 + u : 0) * split_stride;
+            ms[u] = in ? __ldcg(src + HD) : -INFINITY;
+            lv[u] = in ? __ldcg(src + HD + 1) : 0.f;
+            ov[u] = in ? __ldcg(src + d) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < CH; u++) {
+            const float w = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - mm);
+            lsum = fmaf(lv[u], w, lsum);
+            acc = fmaf(ov[u], w, acc);
+          }
+        }
       }
       out[b * a.q_batch_stride + (g * REP + r) * a.q_head_stride + d] = Elem<T>::store(lsum > 0.f ? acc / lsum : 0.f);
     }
@@ -635,7 +689,6 @@ attn_decode_staged_kernel(DecodeArgs a, const T* __restrict__ q, const T* __rest
 // like in the CUDA-core kernel.
 constexpr int kMmaWarps = 4;
 constexpr int kMmaStageKeys = 16 * kMmaWarps;
-constexpr int kMmaStages = 3;
 
 template <typename T> struct MmaOps;
 template <> struct MmaOps<__nv_bfloat16> {
@@ -674,19 +727,32 @@ __device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* src, 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
 }
 
-template <typename T, int REP, int HD>
-__global__ void __launch_bounds__(kMmaWarps * 32)
-attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                       const void* __restrict__ token, T* __restrict__ out) {
+// STAGES = 3: two CTAs per SM, two stages in flight each. (A two-stage ring with three CTAs per SM and a third more
+// splits was measured on thirty-two (sequence, KV head) pairs of 4K keys: no faster.)
+template <typename T, int REP, int HD, int STAGES>
+__global__ void __launch_bounds__(kMmaWarps * 32, STAGES == 2 ? 3 : 2)
+attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
+                       const __grid_constant__ CUtensorMap vmap, const void* __restrict__ token, T* __restrict__ out) {
   static_assert(sizeof(T) == 2 && (HD == 64 || HD == 128) && REP <= 16, "16-bit elements, head_dim 64 or 128");
   constexpr int THREADS = kMmaWarps * 32;
-  constexpr int CPR = HD / 8;                        // 16-byte chunks per row
-  constexpr int HALVES = HD / 64;                    // 128-byte column blocks per row
+  constexpr int HALVES = HD / 64;                     // 128-byte column blocks per row
   constexpr int TILE_BYTES = kMmaStageKeys * HD * 2;  // one of K or V for one stage
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  extern __shared__ __align__(1024) unsigned char smem_attn[];
+  // The swizzle of a tiled copy follows the absolute shared-memory address: tiles start on 1024-byte boundaries.
+  extern __shared__ unsigned char smem_attn_raw[];
+  unsigned char* smem_attn = smem_attn_raw + ((1024u - (attn_smem_u32(smem_attn_raw) & 1023u)) & 1023u);
   __shared__ int is_last;
-  PJRTX_PDL_PROLOGUE();
+  __shared__ int gave_up;
+  __shared__ __align__(8) uint64_t full[STAGES];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < STAGES; st++)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(attn_smem_u32(&full[st])), "r"(1));
+    gave_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -698,29 +764,38 @@ attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restric
   const long long j_end = min(j_begin + per_split, count);
   const int stages_total = j_end > j_begin ? (int)((j_end - j_begin + kMmaStageKeys - 1) / kMmaStageKeys) : 0;
 
-  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride;
-  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride;
   const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_attn);
 
   // Row `row` (0..63) of a stage tile, 16-byte chunk `c` of the row: column block c / 8 holds [64 rows][128 bytes],
-  // chunk position XORed with the row's low three bits.
+  // chunk position XORed with the row's low three bits - the layout a 128-byte swizzled tensor copy writes.
   auto tile_offset = [](int row, int c) { return (unsigned)((c >> 3) * (kMmaStageKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)); };
+  // A stage is 64 K rows and 64 V rows: one tiled copy per 128-byte column block of each, issued by one thread and
+  // completing on the stage's barrier. The maps are [head_dim][keys][KV heads][sequences]; rows past the end of the
+  // cache arrive as zeros.
   auto issue_stage = [&](int st) {
-    const unsigned dst = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
-    const long long j0 = j_begin + (long long)st * kMmaStageKeys;
-    for (int idx = threadIdx.x; idx < kMmaStageKeys * CPR; idx += THREADS) {
-      const int row = idx / CPR, c = idx % CPR;
-      const long long j = j0 + row;
-      const bool in = j < j_end;
-      const long long jj = in ? j : j_begin;
-      cp_async16(dst + tile_offset(row, c), kb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
-      cp_async16(dst + TILE_BYTES + tile_offset(row, c), vb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
+    if (threadIdx.x != 0) return;
+    const int slot = st % STAGES;
+    const unsigned bar = attn_smem_u32(&full[slot]);
+    const unsigned dst = smem_base + (unsigned)slot * STAGE_BYTES;
+    const int j0 = (int)(j_begin + (long long)st * kMmaStageKeys);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(STAGE_BYTES) : "memory");
+#pragma unroll
+    for (int c = 0; c < HALVES; c++) {
+      asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                       dst + c * (kMmaStageKeys * 128)),
+                   "l"(&kmap), "r"(c * 64), "r"(j0), "r"(g), "r"(b), "r"(bar)
+                   : "memory");
+      asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                       dst + TILE_BYTES + c * (kMmaStageKeys * 128)),
+                   "l"(&vmap), "r"(c * 64), "r"(j0), "r"(g), "r"(b), "r"(bar)
+                   : "memory");
     }
   };
-  for (int st = 0; st < kMmaStages - 1; st++) {
+  for (int st = 0; st < STAGES - 1; st++)
     if (st < stages_total) issue_stage(st);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  }
+  unsigned long long deadline;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(deadline));
+  deadline += a.timeout_ns;
 
   // Q fragments: row r = lane / 4 (and r + 8), columns ks * 16 + (lane % 4) * 2 (+ 8).
   unsigned qa[HD / 16][4];
@@ -743,13 +818,47 @@ attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restric
 #pragma unroll
     for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
 
+  bool arrived = true;
   for (int st = 0; st < stages_total; st++) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(kMmaStages - 2) : "memory");
-    __syncthreads();  // stage st is complete for everyone, and everyone is done with stage st - 1
-    if (st + kMmaStages - 1 < stages_total) issue_stage(st + kMmaStages - 1);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    {  // every row of stage st has landed (bounded by time: a copy that never completes must not hang the GPU)
+      const unsigned bar = attn_smem_u32(&full[st % STAGES]), parity = (unsigned)(st / STAGES) & 1u;
+      for (unsigned spin = 0;; spin++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) break;
+        if ((spin & 255) == 255) {
+          unsigned long long now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (now > deadline || *reinterpret_cast<volatile int*>(&gave_up)) {
+            gave_up = 1;
+            arrived = false;
+            break;
+          }
+        }
+      }
+    }
+    // V rows past the end of the split belong to other splits or to nobody: their probabilities are zero, but
+    // 0 * whatever is stored there need not be, so they are cleared (K rows need nothing: their scores are replaced).
+    if (arrived && j_begin + (long long)(st + 1) * kMmaStageKeys > j_end) {
+      const int first = (int)(j_end - (j_begin + (long long)st * kMmaStageKeys));
+      unsigned char* vt = smem_attn + (size_t)(st % STAGES) * STAGE_BYTES + TILE_BYTES;
+      for (int idx = first * (HD / 8) + threadIdx.x; idx < kMmaStageKeys * (HD / 8); idx += THREADS) {
+        const int row = idx / (HD / 8), c = idx % (HD / 8);
+        *reinterpret_cast<uint4*>(vt + tile_offset(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    // Everyone is done with stage st - 1 (its slot is refilled below); a thread that gave up tells the others here.
+    arrived = __syncthreads_and(arrived ? 1 : 0) != 0;
+    if (!arrived) break;
+    if (st + STAGES - 1 < stages_total) issue_stage(st + STAGES - 1);
 
-    const unsigned ktile = smem_base + (unsigned)(st % kMmaStages) * STAGE_BYTES;
+    const unsigned ktile = smem_base + (unsigned)(st % STAGES) * STAGE_BYTES;
     const unsigned vtile = ktile + TILE_BYTES;
     const int row0 = warp * 16;  // this warp's keys inside the stage
     // S = Q . K^T for 16 keys: two accumulator tiles of 8 keys.
@@ -824,7 +933,26 @@ attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restric
       MmaOps<T>::mma(o[2 * np + 1], pa, bv[2], bv[3]);
     }
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (!arrived) {
+    // Copies of later stages may still be in flight towards this CTA's shared memory: give them the same bounded time
+    // before leaving (the barriers they complete on must outlive them), then report and go.
+    for (int st = 0; st < stages_total; st++) {
+      const unsigned bar = attn_smem_u32(&full[st % STAGES]), parity = (unsigned)(st / STAGES) & 1u;
+      for (unsigned spin = 0; spin < (1u << 16); spin++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) break;
+      }
+    }
+    if (threadIdx.x == 0 && a.error_flag) atomicExch(a.error_flag, 6);
+    return;
+  }
   __syncthreads();  // the stage memory is free: reuse it for the merge of the four warps
 
   // Row sums over the quad, then per-warp (max, sum, out) to shared memory.
@@ -885,19 +1013,64 @@ attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const T* __restric
   merge_splits<T, REP, HD, THREADS>(a, tile, b, g, reinterpret_cast<float*>(smem_attn), &is_last, out);
 }
 
-template <typename T, int REP, int HD>
-int launch_decode_mma(const DecodeArgs& a, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out,
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A cache as the 4-d tensor [head_dim][keys][KV heads][sequences] (strides in elements come with the launch); the box
+// is 64 elements x kMmaStageKeys keys of one head of one sequence.
+bool encode_kv_map(CUtensorMap* map, const void* base, bool f16, const DecodeArgs& a, int head_dim) {
+  static const EncodeTiledFn enc = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  if (!enc) return false;
+  // A dimension of extent 1 may come with any stride (0 included); the encoder wants multiples of 16 bytes that
+  // are not smaller than the dimension below, so give those dimensions the stride of the whole cache.
+  const cuuint64_t gdim[4] = {(cuuint64_t)head_dim, (cuuint64_t)a.kv_len, (cuuint64_t)a.kv_heads, (cuuint64_t)a.batch};
+  cuuint64_t gstride[3] = {(cuuint64_t)a.kv_row_stride * 2, (cuuint64_t)a.kv_head_stride * 2, (cuuint64_t)a.kv_batch_stride * 2};
+  for (int d = 0; d < 3; d++)
+    if (gdim[d + 1] == 1 && gstride[d] == 0) gstride[d] = (cuuint64_t)head_dim * 2;
+  const cuuint32_t box[4] = {64, (cuuint32_t)kMmaStageKeys, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstride,
+             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int REP, int HD, int STAGES>
+int launch_decode_mma_stages(const DecodeArgs& args, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out,
                       bool pdl, cudaStream_t stream) {
-  constexpr size_t stage_smem = (size_t)kMmaStages * 2 * kMmaStageKeys * HD * 2;
+  constexpr size_t stage_smem = (size_t)STAGES * 2 * kMmaStageKeys * HD * 2;
   constexpr size_t merge_smem = (size_t)(2 * kMmaWarps * 16 + kMmaWarps * REP * HD) * sizeof(float);
   constexpr size_t scratch_smem = (size_t)64 * REP * 2 * sizeof(float);
-  constexpr size_t smem = stage_smem > merge_smem ? (stage_smem > scratch_smem ? stage_smem : scratch_smem)
-                                                  : (merge_smem > scratch_smem ? merge_smem : scratch_smem);
-  if (!raise_smem_limit((const void*)attn_decode_mma_kernel<T, REP, HD>, (int)smem)) return 0;
-  return launch_kernel(attn_decode_mma_kernel<T, REP, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q,
-                       (const T*)k, (const T*)v, token, (T*)out) == cudaSuccess
+  constexpr size_t smem = 1024 + (stage_smem > merge_smem ? (stage_smem > scratch_smem ? stage_smem : scratch_smem)
+                                                          : (merge_smem > scratch_smem ? merge_smem : scratch_smem));
+  if (!raise_smem_limit((const void*)attn_decode_mma_kernel<T, REP, HD, STAGES>, (int)smem)) return 0;
+  // The splits merge cooperatively (every CTA waits for its tile's other splits) only when the whole grid is resident.
+  DecodeArgs a = args;
+  int device = 0, sms = 0, per_sm = 0;
+  if (coop_merge_allowed() && a.splits > 1 && cudaGetDevice(&device) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_mma_kernel<T, REP, HD, STAGES>, kMmaWarps * 32, smem) == cudaSuccess)
+    a.coop_merge = (long long)grid.x * grid.y * grid.z <= (long long)per_sm * sms ? 1 : 0;
+  // K and V as [head_dim][keys][KV heads][sequences] for tiled copies of 64 keys x 128 bytes, 128-byte swizzled.
+  CUtensorMap kmap, vmap;
+  if (!encode_kv_map(&kmap, k, sizeof(T) == 2 && std::is_same<T, __half>::value, a, HD) ||
+      !encode_kv_map(&vmap, v, sizeof(T) == 2 && std::is_same<T, __half>::value, a, HD))
+    return 0;
+  return launch_kernel(attn_decode_mma_kernel<T, REP, HD, STAGES>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q, kmap,
+                       vmap, token, (T*)out) == cudaSuccess
              ? 1
              : 0;
+}
+
+template <typename T, int REP, int HD>
+int launch_decode_mma(const DecodeArgs& args, dim3 grid, const void* q, const void* k, const void* v, const void* token, void* out,
+                      bool pdl, cudaStream_t stream) {
+  return launch_decode_mma_stages<T, REP, HD, 3>(args, grid, q, k, v, token, out, pdl, stream);
 }
 
 template <typename T>
@@ -1196,7 +1369,8 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   // Tensor-core kernel: 16-bit caches where the CUDA cores would be the limit (eight heads per KV head) or where the
   // cache is large enough for throughput to matter more than the latency of one short CTA.
   // PJRTX_B200_ATTENTION_MMA=0 / 1 forces the choice wherever the kernel applies.
-  const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8);
+  const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8) && s.kv_row_stride % 8 == 0 &&
+                      s.kv_head_stride % 8 == 0 && s.kv_batch_stride % 8 == 0;  // rows arrive as 16-byte aligned bulk copies
   const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
   const bool large = tiles * s.kv_len >= (long long)sm_count * 256;  // measured: ahead from batch 4 at 2K keys, 8 KV heads
   // Few (sequence, KV head) pairs of a 16-bit cache can run on the shared-memory staged kernel (one split per
@@ -1279,16 +1453,13 @@ int attn_decode_launch(const AttnDecodeShape& s, const AttnDecodePlan& plan, con
   {
     // Cooperative merge of the splits only where every CTA of the grid has an SM to itself (the CUDA-core and the
     // staged kernels, at most one CTA per SM counted), so that CTAs may wait for each other.
-    static const bool coop_allowed = [] {
-      const char* e = getenv("PJRTX_B200_ATTENTION_COOP_MERGE");
-      return !(e && *e && atoi(e) == 0);
-    }();
     int device = 0, sms = 0;
-    if (coop_allowed && plan.mma != 1 && plan.splits > 1 && cudaGetDevice(&device) == cudaSuccess &&
+    if (coop_merge_allowed() && plan.mma != 1 && plan.splits > 1 && cudaGetDevice(&device) == cudaSuccess &&
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess)
       a.coop_merge = (long long)plan.splits * s.kv_heads * s.batch <= sms ? 1 : 0;
     a.timeout_ns = 2000000000ull;
   }
+  if (plan.mma == 1 && ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0) return 0;  // bulk copies of rows
   if (plan.mma == 2) {
     if (s.dtype == kF16) return dispatch_decode_staged<__half>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);
     return dispatch_decode_staged<__nv_bfloat16>(rep, (int)s.head_dim, a, grid, q, k, v, token, out, pdl, stream);

@@ -790,19 +790,29 @@ DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_maj
   const int tw = umma::kTileN * p.nh;
   int64_t tiles = 0;
   for (int g = 0; g < count; g++) tiles += (shapes[g].n + tw - 1) / tw * m_tiles;
-  // Short activation tiles leave room for two CTAs per SM (half the shared memory each): while one CTA folds a tile or
-  // a kernel drains, the other CTA - or the first CTAs of the next kernel, which programmatic dependent launch has
-  // already placed - keeps the SM's copies in flight. PJRTX_B200_UMMA_CTAS=1 gives the single CTA back.
-  static const int ctas_wanted = env_int("PJRTX_B200_UMMA_CTAS", 2);
+  // Short activation tiles leave room for two CTAs per SM (half the shared memory each; PJRTX_B200_UMMA_CTAS=2), so
+  // that one CTA streams while the other folds a tile. Measured on B200 at m = 32 it is slower than one CTA per SM with
+  // the whole ring (8B-width layers 1.665 against 1.640 ms per 8 layers; one eighth of the 70B-shape widths 3.00
+  // against 2.79 ms per 20 layers): twice the partial sums to fold outweigh the overlap. Off by default.
+  static const int ctas_wanted = env_int("PJRTX_B200_UMMA_CTAS", 1);
   const bool w8 = s.rhs_s8 != 0;
   const int per_sm = (ctas_wanted >= 2 && p.m_tile <= 64 && !w8 && p.nh == 1) ? 2 : 1;
   const int64_t slots = (int64_t)sm_count * per_sm;
-  const size_t smem_budget = per_sm == 2 ? 112 * 1024 - 2048 : 227 * 1024 - 2048;
+  // PJRTX_B200_UMMA_SMEM_KB bounds the ring (experiments: a CTA that leaves half of the shared memory free lets the
+  // first CTAs of the next kernel move in and start their weight copies while this one folds its last tile).
+  static const int smem_kb = env_int("PJRTX_B200_UMMA_SMEM_KB", 0);
+  const bool small_ring = smem_kb >= 48 && smem_kb <= 225 && !w8 && p.m_tile <= 64;
+  const size_t smem_budget = small_ring ? (size_t)smem_kb * 1024 - 2048 : per_sm == 2 ? 112 * 1024 - 2048 : 227 * 1024 - 2048;
   const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(tiles * ((s.k + 63) / 64), slots));
   // 128-deep stages once every CTA still gets a long run of them; 64-deep otherwise (finer split, better balance), and
   // whenever the ring would hold fewer than four of the deep ones.
   p.sub = (p.nh == 1 && tiles * ((s.k + 127) / 128) >= 32 * grid) ? 2 : 1;
   if (p.sub == 2 && smem_budget / umma::stage_bytes(p.m_tile, 2, p.nh, w8) < 4) p.sub = 1;
+  // Int8 weights: 128-deep stages (PJRTX_B200_W8_SUB=1 gives 64-deep ones: a deeper ring of raw bytes, but twice the
+  // hand-overs between copies, converters and the MMA lane; measured 1.54 against 1.25 ms for the contractions of eight
+  // 8B-width layers and the LM head at 32 rows).
+  static const int w8_sub = env_int("PJRTX_B200_W8_SUB", 2);
+  if (w8) p.sub = w8_sub == 1 ? 1 : 2;
   const int64_t kblocks = (s.k + 64 * p.sub - 1) / (64 * p.sub);
   const int64_t units = tiles * kblocks;
   p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(units, slots));
@@ -815,7 +825,8 @@ DotScratch umma_plan(const DotShape* shapes, int count, int sm_count, bool k_maj
   p.per_cta = units / p.grid;
   p.max_contrib = p.whole_tiles ? 1 : (int)((kblocks + p.per_cta - 1) / p.per_cta) + 1;
   const size_t stage = umma::stage_bytes(p.m_tile, p.sub, p.nh, w8);
-  p.stages = (int)std::max<size_t>(2, std::min<size_t>(12, smem_budget / stage));
+  const size_t ring_budget = smem_budget - (w8 ? umma::kOperandSlots * umma::operand_bytes(p.sub, p.nh) : 0);
+  p.stages = (int)std::max<size_t>(w8 ? umma::kOperandSlots : 2, std::min<size_t>(w8 ? 16 : 12, ring_budget / stage));
   p.smem = umma::smem_bytes(p.stages, p.m_tile, p.sub, p.nh, w8);
   p.ksplit = p.max_contrib;
   p.partial_bytes = (uint64_t)tiles * p.max_contrib * p.m_tile * tw * sizeof(float);

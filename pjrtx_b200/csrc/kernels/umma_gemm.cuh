@@ -200,14 +200,18 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// A stage: the weight operand tile (16-bit, swizzled), the activation tile, and with int8 weights the raw bytes.
+// A stage of the ring: the weight operand tile (16-bit, swizzled) and the activation tile. With int8 weights a stage
+// holds the activation tile and the raw bytes (half the size, so the ring is deeper and more bytes are in flight), and
+// the 16-bit operand tiles the converters write live in kOperandSlots slots of their own in front of the ring.
+constexpr int kOperandSlots = 3;
+__host__ __device__ inline size_t operand_bytes(int sub, int nh) { return (size_t)sub * nh * 16384; }
 __host__ __device__ inline size_t stage_bytes(int m_tile, int sub, int nh, bool w8 = false) {
-  return (size_t)sub * ((size_t)nh * 16384 + (size_t)m_tile * 128 + (w8 ? (size_t)nh * 8192 : 0));
+  return (size_t)sub * ((size_t)m_tile * 128 + (size_t)nh * (w8 ? 8192 : 16384));
 }
 inline size_t smem_bytes(int stages, int m_tile, int sub, int nh, bool w8 = false) {
   // stages (every block 1024-byte aligned: m_tile is a multiple of 16, so m_tile * 128 is a multiple of 2048) +
   // barriers and flags + slack for aligning the dynamic segment to 1024 bytes
-  return (size_t)stages * stage_bytes(m_tile, sub, nh, w8) + 1024 + 512;
+  return (size_t)stages * stage_bytes(m_tile, sub, nh, w8) + (w8 ? kOperandSlots * operand_bytes(sub, nh) : 0) + 1024 + 512;
 }
 
 struct Cursor {
@@ -248,15 +252,21 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
   const uint32_t per_stage = (uint32_t)stage_bytes(p.m_tile, SUB, NH, W8);
-  const uint32_t a_bytes = NH * SUB * 16384u;
-  const uint32_t raw_offset = a_bytes + (uint32_t)SUB * p.m_tile * 128u;  // W8: raw bytes behind the activation tile
+  constexpr uint32_t a_bytes = NH * SUB * 16384u;  // one 16-bit weight operand tile
+  // Without int8 weights a stage is [operand tile][activation tile]. With them the operand slots come first, then the
+  // ring of [activation tile][raw bytes] stages.
+  const uint32_t ring = base + (W8 ? kOperandSlots * a_bytes : 0u);
+  unsigned char* ring_ptr = base_ptr + (W8 ? kOperandSlots * a_bytes : 0u);
+  const uint32_t lhs_offset = W8 ? 0u : a_bytes;
+  const uint32_t raw_offset = (uint32_t)SUB * p.m_tile * 128u;  // W8: raw bytes behind the activation tile
   constexpr int TW = kTileN * NH;  // tile width in weight columns
-  uint64_t* full = reinterpret_cast<uint64_t*>(base_ptr + (size_t)p.stages * per_stage);
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring_ptr + (size_t)p.stages * per_stage);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;   // [2]
   uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint64_t* ready = acc_empty + 2;         // [stages], W8: the converters have rebuilt the stage's weight tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ready + p.stages);
+  uint64_t* ready = acc_empty + 2;         // [kOperandSlots], W8: the converters have written the slot's operand tile
+  uint64_t* slot_empty = ready + 4;        // [kOperandSlots], W8: the MMAs that read the slot have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(slot_empty + 4);
   int* flags = reinterpret_cast<int*>(tmem_slot + 1);  // [0] is_last of a fold, [1] abort
   const WaitBudget budget{global_timer_ns() + kTimeoutNs, flags + 1};
 
@@ -277,7 +287,10 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
     for (int s = 0; s < p.stages; s++) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < kOperandSlots; s++) {
       mbar_init(&ready[s], (kThreadsW8 - kThreads) / 32);
+      mbar_init(&slot_empty[s], 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full[b], 1);
@@ -300,9 +313,9 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
     // ---- TMA producer ------------------------------------------------------------------------------------------
     if (lane == 0 && count > 0) {
       // bytes the copies of one stage deliver: weight tile (16-bit, or raw bytes with int8 weights) + activation tile
-      const unsigned tx = W8 ? (unsigned)(NH * SUB * 8192u + SUB * p.m_tile * 128u) : per_stage;
+      const unsigned tx = per_stage;
       auto load_rhs = [&](const Cursor& c, int stage) {
-        const uint32_t st = base + (uint32_t)stage * per_stage;
+        const uint32_t st = ring + (uint32_t)stage * per_stage;
         const int k0 = c.kb * (kSubK * SUB), n0 = c.n_tile * TW;
         if (W8) {
           // Raw bytes [64 * SUB k rows][128 columns] per half, unswizzled.
@@ -330,7 +343,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
         }
       };
       auto load_lhs = [&](const Cursor& c, int stage) {
-        const uint32_t st = base + (uint32_t)stage * per_stage + a_bytes;
+        const uint32_t st = ring + (uint32_t)stage * per_stage + lhs_offset;
         const int k0 = c.kb * (kSubK * SUB);
 #pragma unroll
         for (int s = 0; s < SUB; s++)
@@ -378,6 +391,8 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
       const uint32_t idesc = instr_desc(p.is_bf16, p.m_tile, !p.rhs_k_major);
       int stage = 0;
       unsigned phase = 0;
+      int slot = 0;            // W8: operand slot of this unit
+      unsigned slot_phase = 0;
       int seg = 0;
       Cursor cur = cursor_at(p, u_begin);
       int cur_tile = -1;
@@ -396,18 +411,20 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
           acc = tmem_base + (uint32_t)(buf * NH * p.m_tile);
           fresh = true;
         }
-        if (!mbar_wait(W8 ? &ready[stage] : &full[stage], phase, budget)) {
+        // The activation tile of the stage has landed; with int8 weights the converters have also filled the slot.
+        if (!mbar_wait(&full[stage], phase, budget) || (W8 && !mbar_wait(&ready[slot], slot_phase, budget))) {
           atomicExch(p.error_flag, 12);
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t st = base + (uint32_t)stage * per_stage;
+        const uint32_t st = ring + (uint32_t)stage * per_stage;
+        const uint32_t weights = W8 ? base + (uint32_t)slot * a_bytes : st;
 #pragma unroll
         for (int kk = 0; kk < 4 * SUB; kk++) {
-          const uint64_t b_desc = smem_desc(st + a_bytes + (uint32_t)(kk >> 2) * p.m_tile * 128u + (kk & 3) * 32u, 16, 1024);
+          const uint64_t b_desc = smem_desc(st + lhs_offset + (uint32_t)(kk >> 2) * p.m_tile * 128u + (kk & 3) * 32u, 16, 1024);
 #pragma unroll
           for (int h = 0; h < NH; h++) {
-            const uint32_t sh = st + h * (SUB * 16384u);
+            const uint32_t sh = weights + h * (SUB * 16384u);
             uint64_t a_desc;
             if (p.rhs_k_major) {
               // A K-major like B: 64-k sub-blocks 16 KiB apart, 32 bytes per 16-k step inside the swizzled row.
@@ -422,6 +439,13 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
         }
         fresh = false;
         mma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+        if (W8) {
+          mma_commit(&slot_empty[slot]);  // and so is the operand slot
+          if (++slot == kOperandSlots) {
+            slot = 0;
+            slot_phase ^= 1;
+          }
+        }
         if (++stage == p.stages) {
           stage = 0;
           phase ^= 1;
@@ -442,18 +466,20 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
       const int t = threadIdx.x - kThreads;
       const int nc = t & 7, row0 = t >> 3;
       constexpr int ROWS = 2 * SUB;  // rows per thread and half: 64 * SUB rows over 32 row slots
-      int stage = 0;
-      unsigned phase = 0;
+      int stage = 0, slot = 0;
+      unsigned phase = 0, slot_phase = 0;
       for (int i = 0; i < count; i++) {
-        if (!mbar_wait(&full[stage], phase, budget)) {
+        // The raw bytes have landed, and the MMAs that read this slot's previous tile have completed.
+        if (!mbar_wait(&full[stage], phase, budget) || (i >= kOperandSlots && !mbar_wait(&slot_empty[slot], slot_phase ^ 1, budget))) {
           if (lane == 0) atomicExch(p.error_flag, 15);
           break;
         }
-        unsigned char* st = base_ptr + (size_t)stage * per_stage;
+        const unsigned char* st = ring_ptr + (size_t)stage * per_stage;
+        unsigned char* operand = base_ptr + (size_t)slot * a_bytes;
 #pragma unroll
         for (int h = 0; h < NH; h++) {
           const unsigned char* raw = st + raw_offset + h * (SUB * 8192u) + row0 * 128 + nc * 16;
-          unsigned char* dst = st + h * (SUB * 16384u) + (nc >> 2) * (SUB * 8192u);
+          unsigned char* dst = operand + h * (SUB * 16384u) + (nc >> 2) * (SUB * 8192u);
           uint4 q[ROWS];  // every row of this thread is requested before the first is converted
 #pragma unroll
           for (int r = 0; r < ROWS; r++) q[r] = *reinterpret_cast<const uint4*>(raw + r * 32 * 128);
@@ -495,7 +521,11 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
         // The tile was written through the generic proxy; the tensor core reads it through the async proxy.
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ready[stage]);
+        if (lane == 0) mbar_arrive(&ready[slot]);
+        if (++slot == kOperandSlots) {
+          slot = 0;
+          slot_phase ^= 1;
+        }
         if (++stage == p.stages) {
           stage = 0;
           phase ^= 1;

@@ -94,7 +94,9 @@ def make_weights(cfg: LlamaConfig, seed: int = 0, threads: int = 8, embed_period
 
     Each row block of each tensor draws from its own `default_rng([seed, index, block])`, so the values do not depend
     on how many threads generate them. With `int8_weights` linear weights are s8 ~U{-127..127} and `<name>.scale`
-    holds per-output-channel f16 scales ~U(0.001, 0.01).
+    holds per-output-channel f16 scales ~U(0.5, 1.5) * 0.02 * sqrt(3) / 127, which gives the dequantised weights the
+    spread of the 16-bit initialisation (standard deviation about 0.02): with much larger weights the attention scores
+    saturate the softmax and the logits amplify differences of one rounding in a weight.
     """
     dt = P.np_dtype(cfg.dtype)
     shapes = weight_shapes(cfg)
@@ -104,7 +106,7 @@ def make_weights(cfg: LlamaConfig, seed: int = 0, threads: int = 8, embed_period
         quant = cfg.int8_weights and _is_linear(name)
         out[name] = np.empty(shape, dtype=np.int8 if quant else dt)
         if quant:
-            out[name + ".scale"] = np.random.default_rng([seed, index, 1 << 20]).uniform(0.001, 0.01, size=(shape[-1],)).astype(np.float16)
+            out[name + ".scale"] = (np.random.default_rng([seed, index, 1 << 20]).uniform(0.5, 1.5, size=(shape[-1],)) * (0.02 * np.sqrt(3.0) / 127.0)).astype(np.float16)
         gen_shape = shape
         if name == "embed" and embed_period and embed_period < shape[0]:
             gen_shape = (embed_period,) + tuple(shape[1:])

@@ -123,8 +123,9 @@ def test_tiny_prefill(gpu_backend):
 @pytest.mark.parametrize("batch,dtype", [(2, P.BF16_CODE), (16, P.BF16_CODE), (5, P.BF16_CODE), (16, P.F16)])
 def test_int8_weight_only_decode(gpu_backend, monkeypatch, batch, dtype):
     """Dequantisation written as convert + multiply feeding dot_general. From three rows up the contractions read the
-    bytes themselves (tensor-core stream with in-kernel dequantisation, weights one byte wide in HBM); the result must be
-    what the written program gives, within tolerance of the oracle and equal to the materialising path's to rounding."""
+    bytes themselves (weights one byte wide in HBM; the tensor core contracts the integers and the column scales
+    multiply the accumulators, which skips the rounding of every scaled weight to the element type); the result must
+    be within tolerance of the oracle, which rounds as the program is written, and of the materialising path."""
     import dataclasses
 
     be = gpu_backend

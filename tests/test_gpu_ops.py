@@ -460,3 +460,31 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_survives(gpu_b
     be.synchronize(0)  # the word was cleared by the failed call
     b, args = cases.u8_chain()
     assert run_backend(be, b, args)[0].tolist() == [6, 15, 28, 45]
+
+
+@pytest.mark.parametrize("m,k,n,dtype", [(16, 256, 256, P.BF16_CODE), (16, 256, 128, P.F16), (32, 1024, 384, P.BF16_CODE),
+                                         (5, 512, 200, P.BF16_CODE), (32, 4096, 6144, P.BF16_CODE), (64, 512, 1000, P.F16)])
+def test_int8_dequantising_contraction(gpu_backend, m, k, n, dtype):
+    """dot_general(x, convert(convert(w s8 -> f16) * scale)) from three rows up reads the bytes themselves where the
+    byte rows have a 16-byte pitch: the tensor core contracts the integers and the column scales multiply the f32
+    accumulators. Against the exact contraction in f64 the only error left is the rounding of the output (one part in
+    2^8 at bf16, 2^11 at f16, of the largest value); the other widths materialise the scaled weights and round each."""
+    rng = np.random.default_rng(m * 1000 + n)
+    npdt = P.np_dtype(dtype)
+    x = rng.standard_normal((m, k), dtype=np.float32).astype(npdt)
+    w = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    sc = (rng.uniform(0.5, 1.5, size=(n,)) / 127 / np.sqrt(k)).astype(np.float16)
+    b = PlanBuilder()
+    px, pw, ps = b.parameter(dtype, x.shape), b.parameter(P.S8, w.shape), b.parameter(P.F16, sc.shape)
+    wf = b.convert(pw, P.F16) * b.broadcast_in_dim(ps, w.shape, [1])
+    if dtype != P.F16:
+        wf = b.convert(wf, dtype)
+    b.set_outputs([b.dot_general(px, wf, [1], [0])])
+    exe = gpu_backend.compile_executable(b, [0])
+    dots = [s for s in exe.describe()["kernel_plan"]["steps"] if s["type"] == "dot"]
+    assert len(dots) == 1 and dots[0]["rhs_s8"] == (1 if n % 16 == 0 else 0), dots  # byte rows need a 16-byte pitch
+    got = gpu_backend.execute_executable(exe, [gpu_backend.buffer_from_host(a) for a in (x, w, sc)])[0].to_numpy().astype(np.float64)
+    want = x.astype(np.float64) @ (w.astype(np.float64) * sc.astype(np.float64)[None, :])
+    ulp = 2.0 ** (-8 if dtype == P.BF16_CODE else -11)
+    bound = (1.01 if n % 16 == 0 else 3.0) * ulp * np.max(np.abs(want))
+    assert np.max(np.abs(got - want)) <= bound, (np.max(np.abs(got - want)), np.max(np.abs(want)))
