@@ -1103,6 +1103,8 @@ bool plan_kernels(const Plan& original, int sm_count, KernelPlan* kp, std::strin
   // 3.58 (every CTA repeats the row reduction after it has waited for its predecessor, where the one-CTA norm kernel ran
   // concurrently with the next contraction's ramp); chained 4.16 (a segment boundary - fold, grid barrier, factors,
   // first lhs values - is 7 to 8 us of dependent round trips against the 4 us of weights the rings hold).
+  // PJRTX_B200_DOT_FUSE=silu folds in only the silu(gate) * up transform (no row reduction involved): 3.47 against
+  // 3.40 ms per step - the generated kernel costs 2.6 us inside the step, the transform costs the contraction more.
   const char* fuse_env = getenv("PJRTX_B200_DOT_FUSE");
   const bool fuse_silu_only = fuse_env && std::string(fuse_env) == "silu";  // only the silu(gate) * up transform
   if (fuse_silu_only || env_flag_local("PJRTX_B200_DOT_FUSE", false)) {
@@ -1707,11 +1709,9 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
         cfg.gridDim = dim3((unsigned)st.fused.grid);
         cfg.blockDim = dim3((unsigned)st.fused.block);
         cfg.stream = dev->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchAttribute attr[2];
         cfg.attrs = attr;
-        cfg.numAttrs = exe->pdl ? 1 : 0;
+        cfg.numAttrs = fill_launch_attributes(attr, exe->pdl);
         cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)st.jit->kernel, args.data());
         if (e != cudaSuccess) {
           *error = std::string("fused kernel launch failed: ") + cudaGetErrorString(e);

@@ -631,11 +631,9 @@ int launch_tma_m(const tma::Params& prm, const tma::Maps& maps, int grid, size_t
   cfg.blockDim = dim3(tma::kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = fill_launch_attributes(attr, pdl);
   return cudaLaunchKernelEx(&cfg, tma::stream_tma_kernel<T, M, EXTRAS>, prm, maps) == cudaSuccess ? 1 : 0;
 }
 
@@ -842,11 +840,9 @@ int launch_umma_sub(const umma::Params& prm, const umma::Maps& maps, const DotSc
   cfg.blockDim = dim3(W8 ? umma::kThreadsW8 : umma::kThreads);
   cfg.dynamicSmemBytes = plan.smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = fill_launch_attributes(attr, pdl);
   return cudaLaunchKernelEx(&cfg, umma::umma_stream_kernel<SUB, NH, W8>, prm, maps) == cudaSuccess ? 1 : 0;
 }
 
@@ -895,8 +891,11 @@ int launch_umma(const DotShape* shapes, int count, const DotScratch& plan, const
         gdim[0] = (cuuint64_t)shapes[g].n; gdim[1] = (cuuint64_t)s.k;
         gstride[0] = (cuuint64_t)shapes[g].rhs_k;
         box[0] = 128; box[1] = (cuuint32_t)(64 * plan.sub);
+        // A row of the box is 128 bytes: with 256-byte promotion L2 would fetch the neighbouring tile's 128 bytes with
+        // every row and usually lose them again before that tile's turn (measured on the 4096 x 128256 LM head:
+        // 742 MB read for 525 MB of weights).
         if (enc(&maps.rhs[g], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(rhs[g]), gdim, gstride, box, estr3,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
           return false;
         continue;

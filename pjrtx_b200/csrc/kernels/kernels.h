@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 #include <set>
 #include <utility>
@@ -25,6 +26,28 @@ inline bool raise_smem_limit(const void* kernel, int bytes) {
   return true;
 }
 
+// Attributes of every launch of the library: programmatic stream serialization when `pdl`, and - when
+// PJRTX_B200_CARVEOUT is set (0..100) - that shared-memory carveout, the same for every kernel, so that consecutive
+// kernels never ask the SMs for different splits between L1 and shared memory. Returns the number filled in (<= 2).
+inline unsigned fill_launch_attributes(cudaLaunchAttribute* attr, bool pdl) {
+  static const int carveout = [] {
+    const char* v = getenv("PJRTX_B200_CARVEOUT");
+    return v && *v ? atoi(v) : -1;
+  }();
+  unsigned n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+  }
+  if (carveout >= 0 && carveout <= 100) {
+    attr[n].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+    attr[n].val.sharedMemCarveout = (unsigned)carveout;
+    n++;
+  }
+  return n;
+}
+
 // Launch with (optionally) programmatic stream serialization: the kernel may begin while its predecessor in the stream
 // is still running; kernels call griddepcontrol.wait before their first dependent access.
 template <typename... KArgs, typename... Args>
@@ -35,11 +58,9 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = fill_launch_attributes(attr, pdl);
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

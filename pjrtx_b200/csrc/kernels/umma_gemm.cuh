@@ -33,6 +33,11 @@
 // sum: sum_k x[k] * (w[k,n] * s[n]) = s[n] * sum_k x[k] * w[k,n]. The op-by-op program rounds every w * s to the element
 // type first; this form skips that rounding (one relative 2^-9 per weight at bf16), so the two agree to rounding, not
 // bit for bit, and a product w * s that overflows f16 in the written program stays finite here.
+// What bounds it: shared memory. A 128-deep stage moves about 110 KB through shared memory (16 KB of raw bytes written
+// by the copy and read by the converters, 32 KB of 16-bit values written by them and read by the tensor core, the
+// activation tile) against 80 KB on the 16-bit path, for half the HBM bytes: measured 1630 cycles per stage on the
+// 4096 x 128256 LM head at 32 rows, where the 16-bit path takes 1510 (HBM-bound). Two groups of converter warps on
+// alternate stages (to overlap one group's proxy fence with the other's work) measured the same to four digits.
 //
 // Every mbarrier wait is bounded by time (two seconds per launch; the thread that sees the deadline pass sets a CTA-wide
 // abort word and every other wait gives up at its next check); the kernel then sets *error_flag, every role falls
@@ -77,6 +82,9 @@ struct Params {
   int early_rhs;         // rhs copies may start before the preceding kernel of the stream has finished
   int whole_tiles;       // 1: CTA b owns tiles [b*T/G, (b+1)*T/G) completely instead of an equal share of units
   const void* scale[kGroupMax];  // W8: f16 scale per weight column
+#ifdef PJRTX_UMMA_TIMESTAMPS
+  unsigned long long* stamps;  // [grid][16] nanosecond timestamps of the phases (measurement builds only)
+#endif
 };
 
 struct Maps {
@@ -245,6 +253,12 @@ __device__ __forceinline__ void advance(const Params& p, Cursor* c) {
 
 // SUB: 64-deep k sub-blocks per stage (1 or 2). NH: 128-column halves per tile (1 or 2); two halves make every weight
 // row of a stage 512 contiguous bytes in memory and take two accumulators per tile (so m_tile <= 128).
+#ifdef PJRTX_UMMA_TIMESTAMPS
+#define PJRTX_STAMP(slot) (p.stamps[(size_t)blockIdx.x * 16 + (slot)] = global_timer_ns())
+#else
+#define PJRTX_STAMP(slot) ((void)0)
+#endif
+
 template <int SUB, int NH, bool W8 = false>
 __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_kernel(const Params p, const __grid_constant__ Maps maps) {
   extern __shared__ unsigned char smem_dyn[];
@@ -271,6 +285,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
   const WaitBudget budget{global_timer_ns() + kTimeoutNs, flags + 1};
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) PJRTX_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Equal shares of units; with `whole_tiles` equal shares of tiles (no tile is split, nothing to fold).
   const long long tiles_total = p.units / p.kblocks;
@@ -308,6 +323,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) PJRTX_STAMP(1);
 
   if (warp == 4) {
     // ---- TMA producer ------------------------------------------------------------------------------------------
@@ -368,6 +384,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
         asm volatile("griddepcontrol.wait;" ::: "memory");
         first = 0;
       }
+      PJRTX_STAMP(2);
       int stage = first % p.stages;
       unsigned phase = first == p.stages ? 1 : 0;
       for (int i = first; i < count; i++) {
@@ -417,6 +434,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (i == 0) PJRTX_STAMP(3);
         const uint32_t st = ring + (uint32_t)stage * per_stage;
         const uint32_t weights = W8 ? base + (uint32_t)slot * a_bytes : st;
 #pragma unroll
@@ -454,6 +472,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
         if (i + 1 == count || cur.tile != cur_tile) {
           mma_commit(&acc_full[seg & 1]);
           seg++;
+          if (i + 1 == count) PJRTX_STAMP(4);
         }
       }
     }
@@ -553,6 +572,7 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (threadIdx.x == 0 && tile == last_tile) PJRTX_STAMP(5);
         // CTA that owns unit u: the largest b with b*units/grid <= u, i.e. ceil((u+1)*grid/units) - 1.
         const long long tile_units_begin = (long long)tile * p.kblocks;
         const long long first_cta = ((tile_units_begin + 1) * gridDim.x + p.units - 1) / p.units - 1;
@@ -605,9 +625,12 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
         if (contributors > 1) {
           asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 0 && tile == last_tile) PJRTX_STAMP(6);
           if (threadIdx.x == 0) flags[0] = arrive_acq_rel(&p.counters[tile]) == (unsigned)contributors - 1;
           asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 0 && tile == last_tile) PJRTX_STAMP(7);
           if (flags[0]) {
+            if (threadIdx.x == 0) PJRTX_STAMP(10);
             const float* first_slot = p.partials + ((long long)tile * p.max_contrib * p.m_tile) * TW;
             const long long slot_stride = (long long)p.m_tile * TW;
             // Sixteen rows at a time, all their loads issued before the adds; contributors are added in CTA order.
@@ -620,7 +643,10 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
                 for (int j = 0; j < 16; j++) t[j] = 0.f;
                 // Four contributors' rows are requested at once (64 loads in flight per thread: the fold of a tile
                 // with fifteen contributors is a quarter of a megabyte through one CTA, so its time is round trips),
-                // then added in CTA order.
+                // then added in CTA order. (A fold shared by the contributors - every CTA waits until the tile's
+                // partials are all published, then adds a slice of the rows with one round of loads - was measured
+                // slower: 2.80 against 2.23 ms for the 81 contractions of twenty 70B-shape layers cut eight ways,
+                // 1.57 against 1.31 ms for eight 8B-width layers at 32 rows.)
                 int q = 0;
                 for (; q + 4 <= contributors; q += 4) {
                   float v[4][16];
@@ -656,14 +682,17 @@ __global__ void __launch_bounds__(W8 ? kThreadsW8 : kThreads, 1) umma_stream_ker
               }
             }
             if (threadIdx.x == 0) p.counters[tile] = 0;
+            if (threadIdx.x == 0) PJRTX_STAMP(12);
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (threadIdx.x == 0) PJRTX_STAMP(8);
   }
   __syncthreads();
+  if (threadIdx.x == 0) PJRTX_STAMP(9);
   if (warp == 5) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
