@@ -752,7 +752,9 @@ attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const __grid_const
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // With `early_kv` the only row an earlier kernel of the step writes is the one at the token index (and the token is a
+  // parameter): stages that do not hold that row are requested before the wait for the predecessor.
+  if (!a.early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -791,8 +793,22 @@ attn_decode_mma_kernel(DecodeArgs a, const T* __restrict__ q, const __grid_const
                    : "memory");
     }
   };
-  for (int st = 0; st < STAGES - 1; st++)
-    if (st < stages_total) issue_stage(st);
+  {
+    bool issued[STAGES - 1];
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; st++) {
+      const long long j0 = j_begin + (long long)st * kMmaStageKeys;
+      const bool holds_token_row = j0 <= limit && limit < j0 + kMmaStageKeys;
+      issued[st] = st < stages_total && !(a.early_kv && holds_token_row);
+      if (issued[st]) issue_stage(st);
+    }
+    if (a.early_kv) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+      for (int st = 0; st < STAGES - 1; st++)
+        if (st < stages_total && !issued[st]) issue_stage(st);
+    }
+  }
   unsigned long long deadline;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(deadline));
   deadline += a.timeout_ns;
@@ -1366,9 +1382,9 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   AttnDecodePlan p;
   const long long tiles = s.batch * s.kv_heads;
   const long long rep = s.heads / s.kv_heads;
-  // Tensor-core kernel: 16-bit caches where the CUDA cores would be the limit (eight heads per KV head) or where the
-  // cache is large enough for throughput to matter more than the latency of one short CTA.
-  // PJRTX_B200_ATTENTION_MMA=0 / 1 forces the choice wherever the kernel applies.
+  // Tensor-core kernel: 16-bit caches with four or eight query heads per KV head and 16-byte aligned rows; everything else
+  // (f32, other head ratios) runs on the CUDA-core kernel. PJRTX_B200_ATTENTION_MMA=0 / 1 forces the choice wherever
+  // the tensor-core kernel applies.
   const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8) && s.kv_row_stride % 8 == 0 &&
                       s.kv_head_stride % 8 == 0 && s.kv_batch_stride % 8 == 0;  // rows arrive as 16-byte aligned bulk copies
   const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
@@ -1390,7 +1406,10 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
       return p;
     }
   }
-  p.mma = mma_ok && (force && *force ? atoi(force) != 0 : (rep == 8 || large)) ? 1 : 0;
+  // The tensor-core kernel wherever it applies: since its rows come by tiled copies and its splits merge cooperatively it
+  // is ahead at every size measured (8B shape, batch 1: 3.28 against 3.35 ms per step with 2.1 K keys, 3.36 against
+  // 3.48 ms with 2.7 K; batch 2: 3.75 against 3.93 ms).
+  p.mma = mma_ok && (force && *force ? atoi(force) != 0 : true) ? 1 : 0;
   if (p.mma) {
     // Two CTAs per SM are resident: one wave of them, no more (measured at 4K keys, batch 32: 32 / 64 / 128 / 256
     // (sequence, KV head) pairs run fastest with 9 / 4 / 2 / 1 splits — 25.5 / 36 / 57 / 84 us against 44 / 50 / 68 /
@@ -1406,8 +1425,12 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   // Keys one CTA handles per chunk (see the kernel): no split should be shorter than that.
   const long long lanes_per_key = s.head_dim * (long long)dtype_size(s.dtype) / 16;
   const long long chunk = 8 * (32 / lanes_per_key) * (rep <= 4 ? 8 : 4);
-  // About four CTAs per SM in total, so that the tail of the last wave is short next to the whole.
-  long long want = (4ll * sm_count + tiles - 1) / tiles;
+  // Many pairs: about four CTAs per SM in total, so that the tail of the last wave is short next to the whole. Fewer
+  // pairs than SMs (the latency regime: batch-1 decode): one wave of one CTA per SM - the 16-bit kernel with four heads
+  // per KV head holds one CTA of 256 threads per SM, a second wave would start after the first, and only a grid that
+  // is resident as a whole merges its splits cooperatively (with a 3744-key buffer the old rule asked for 29 splits
+  // of the 8B shape's 8 KV heads: 232 CTAs, two waves, 0.82 instead of 0.53 ms for a step's 32 launches).
+  long long want = tiles < sm_count ? std::max<long long>(1, sm_count / tiles) : (4ll * sm_count + tiles - 1) / tiles;
   long long max_splits = std::max<long long>(1, s.kv_len / chunk);
   p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
   p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
