@@ -337,6 +337,7 @@ def run_ours(args):
     # ---- per-kernel device times for the roofline of the dominant kernel ------------
     exe.set_profiling(True)
     per_type = {}
+    per_shape = {}
     reps = 3
     desc = exe.describe()["kernel_plan"]["steps"]
     acc = np.zeros(len(desc))
@@ -364,6 +365,10 @@ def run_ours(args):
             stream_bytes += weight_elems * wsize + st["m"] * (weight_elems // max(st["k"], 1) + st["k"]) * esize
             stream_ms += float(t)
             tensor_core |= bool(st.get("umma"))
+            shape = f"{st['k']}x{weight_elems // max(st['k'], 1)}"  # K x N (N summed over a grouped launch)
+            per_shape.setdefault(shape, [0, 0.0])
+            per_shape[shape][0] += 1
+            per_shape[shape][1] += float(t)
     peak, peak_kind = measured_peaks()
     step_ms = ms / args.steps
     kv_mid = filled + args.warmup + (repeats * args.steps) // 2
@@ -396,6 +401,8 @@ def run_ours(args):
                                     "frac": alg / (step_ms * 1e-3) / 1e9 / peak, "frac_of_8tbs": alg / (step_ms * 1e-3) / 8e12}},
         "clocks": clocks,
         "kernel_time_ms_per_step": {k: {"launches": v[0], "ms": round(v[1], 4)} for k, v in sorted(per_type.items())},
+        # streaming contractions by shape: launches per step and device time per launch (same event-per-step replay)
+        "contraction_us_by_shape": {k: {"launches": v[0], "us": round(1e3 * v[1] / v[0], 2)} for k, v in sorted(per_shape.items())},
         "compile_s": round(compile_s, 2), "setup_s": round(setup_s, 2),
     }
     if rank == 0 and world == 1 and batch == 1 and args.workload == "decode" and not args.no_cpu_baseline:

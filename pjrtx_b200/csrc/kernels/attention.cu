@@ -1416,6 +1416,8 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
     // 103 us with twice as many CTAs), and no split shorter than two stages of keys.
     long long want = std::max<long long>(1, 2ll * sm_count / tiles);
     if (const char* w = getenv("PJRTX_B200_ATTENTION_SPLITS")) want = std::max(1, atoi(w));  // experiments
+    // No split shorter than two stages (splits of one stage measured slower at 2.1 K keys and 8 KV heads: 3.30 ms per
+    // 8B-shape step with 37, 3.31 with 30, 3.23 with 24 against 3.21 with 18).
     long long max_splits = std::max<long long>(1, s.kv_len / (2 * kMmaStageKeys));
     p.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, max_splits), 64));
     p.workspace_bytes = (uint64_t)tiles * p.splits * rep * (s.head_dim + 2) * sizeof(float);
