@@ -1390,8 +1390,8 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
   const bool large = tiles * s.kv_len >= (long long)sm_count * 256;  // measured: ahead from batch 4 at 2K keys, 8 KV heads
   // Few (sequence, KV head) pairs of a 16-bit cache can run on the shared-memory staged kernel (one split per
-  // kStagedKeys keys at least, about one CTA per SM) with PJRTX_B200_ATTENTION_STAGED=1. The register-staged kernel
-  // stays the default: on the 8B-shape decode step it gives 3.50 ms per step against 3.53 ms.
+  // kStagedKeys keys at least, about one CTA per SM) with PJRTX_B200_ATTENTION_STAGED=1. It is not a
+  // default: on the 8B-shape decode step it gave 3.53 ms per step against 3.50 ms for the register-staged kernel.
   const char* staged_env = getenv("PJRTX_B200_ATTENTION_STAGED");
   const bool staged_on = staged_env && *staged_env && atoi(staged_env) != 0;
   if (staged_on && !(force && *force) && !large && (s.dtype == kF16 || s.dtype == kBF16)) {
