@@ -1385,8 +1385,9 @@ AttnDecodePlan attn_decode_plan(const AttnDecodeShape& s, int sm_count) {
   // Tensor-core kernel: 16-bit caches with four or eight query heads per KV head and 16-byte aligned rows; everything else
   // (f32, other head ratios) runs on the CUDA-core kernel. PJRTX_B200_ATTENTION_MMA=0 / 1 forces the choice wherever
   // the tensor-core kernel applies.
-  const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8) && s.kv_row_stride % 8 == 0 &&
-                      s.kv_head_stride % 8 == 0 && s.kv_batch_stride % 8 == 0;  // rows arrive as 16-byte aligned bulk copies
+  const bool mma_ok = (s.dtype == kF16 || s.dtype == kBF16) && (rep == 4 || rep == 8) && (s.head_dim == 64 || s.head_dim == 128) &&
+                      s.kv_len >= kMmaStageKeys &&  // the copies' box is a whole stage of keys
+                      s.kv_row_stride % 8 == 0 && s.kv_head_stride % 8 == 0 && s.kv_batch_stride % 8 == 0;  // 16-byte pitches
   const char* force = getenv("PJRTX_B200_ATTENTION_MMA");
   const bool large = tiles * s.kv_len >= (long long)sm_count * 256;  // measured: ahead from batch 4 at 2K keys, 8 KV heads
   // Few (sequence, KV head) pairs of a 16-bit cache can run on the shared-memory staged kernel (one split per

@@ -330,6 +330,8 @@ def test_buffer_round_trip_and_errors(gpu_backend):
     ("mma", P.BF16_CODE, 16, 2, 128, 150),
     ("cuda", P.F16, 16, 2, 64, 200),
     ("cuda", P.F32, 8, 4, 64, 100),
+    ("default", P.BF16_CODE, 16, 4, 128, 40),    # a buffer shorter than a stage of the tensor-core kernel: CUDA cores
+    ("default", P.BF16_CODE, 32, 8, 128, 64),    # exactly one stage: tensor-core kernel
     ("staged", P.BF16_CODE, 32, 8, 128, 300),
     ("staged3", P.BF16_CODE, 32, 8, 128, 384),
     ("staged", P.F16, 16, 2, 64, 200),
@@ -349,6 +351,8 @@ def test_decode_attention_every_visible_length(gpu_backend, monkeypatch, kernel,
         monkeypatch.setenv("PJRTX_B200_ATTENTION_STAGED", "1")
         if kernel == "staged3":
             monkeypatch.setenv("PJRTX_B200_ATTENTION_SPLITS", "3")
+    elif kernel == "default":
+        monkeypatch.delenv("PJRTX_B200_ATTENTION_MMA", raising=False)
     else:
         monkeypatch.setenv("PJRTX_B200_ATTENTION_MMA", "1" if kernel == "mma" else "0")
     rng = np.random.default_rng(23)
@@ -364,7 +368,7 @@ def test_decode_attention_every_visible_length(gpu_backend, monkeypatch, kernel,
     exe = be.compile_executable(b, [0])
     steps = exe.describe()["kernel_plan"]["steps"]
     assert [s["type"] for s in steps] == ["attention_decode"]
-    assert steps[0]["mma"] == {"cuda": 0, "mma": 1, "staged": 2, "staged3": 2}[kernel]
+    assert steps[0]["mma"] == {"cuda": 0, "mma": 1, "staged": 2, "staged3": 2, "default": 1 if kv_len >= 64 else 0}[kernel]
     if kernel == "staged3":
         assert steps[0]["splits"] == 3
     bufs = [be.buffer_from_host(a) for a in (q, k, v)]
