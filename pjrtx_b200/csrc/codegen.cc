@@ -127,6 +127,9 @@ template <typename T> __device__ __forceinline__ T f2i(float x) {
 }
 __device__ __forceinline__ float f_sign(float x) { return x != x ? x : (x > 0.f ? 1.f : (x < 0.f ? -1.f : x)); }
 __device__ __forceinline__ float f_logistic(float x) { return 1.0f / (1.0f + expf(-x)); }
+// For results stored in a 16-bit type: the approximate exponential and division are off by about 2^-21, the rounding
+// to f16 / bf16 that follows by 2^-12 / 2^-9.
+__device__ __forceinline__ float f_logistic16(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float f_rsqrt(float x) { return 1.0f / sqrtf(x); }
 )CUDA";
 
@@ -655,7 +658,7 @@ class Gen {
       case Kind::floor: return ffun("floorf");
       case Kind::log: return ffun("logf");
       case Kind::log1p: return ffun("log1pf");
-      case Kind::logistic: return ffun("f_logistic");
+      case Kind::logistic: return ffun(dt == kF16 || dt == kBF16 ? "f_logistic16" : "f_logistic");
       case Kind::sine: return ffun("sinf");
       case Kind::cosine: return ffun("cosf");
       case Kind::round_nearest_afz: return ffun("roundf");
