@@ -1058,6 +1058,8 @@ class Gen {
       // Later loops start at a rotated block so that small loops do not all land on block 0.
       std::string bx = g == 0 ? "blockIdx.x" : strfmt("((blockIdx.x + %zuu) %% gridDim.x)", g);
       if (vec_ > 1) {
+        // (Unrolling this loop two or four times, so that more loads are in flight per thread, measured no change on the
+        // 705 MB SiLU x up kernel of an 8B-shape prefill: 170 us either way.)
         loops += strfmt("  for (idx_t i0 = ((idx_t)%s * %d + threadIdx.x) * %d; i0 < %lld; i0 += (idx_t)gridDim.x * %d) {\n",
                         bx.c_str(), k->block, vec_, (long long)N_, k->block * vec_);
         for (const VecAccess& a : vec_loads_) {
