@@ -386,6 +386,8 @@ __device__ __forceinline__ bool run_units(const Params& p, const Segment& sg, co
               float t = 0.f;
               // All of a tile's partials (12 to 19 contributors at the decode shapes) are requested in one round of
               // loads, then added in CTA order: the fold sits in the kernel's tail, where a round trip is what it costs.
+              // (Without the arrival counter - partials published as {value, launch stamp} pairs that the tile's first
+              // contributor polls and folds, no fence and no atomic - the 8B-shape step measured 3.30 against 3.29 ms.)
               for (int q = 0; q < contributors; q += 24) {
                 float v[24];
 #pragma unroll
