@@ -147,6 +147,7 @@ typedef struct PjrtxB200ExecutableStats {
   uint64_t graph_capture_count;
   uint64_t graph_launch_count;
   uint64_t kernel_launch_total;
+  uint64_t profile_event_gap_ns; /* profiled executions: what two event records with nothing between them read */
 } PjrtxB200ExecutableStats;
 
 /* Replaces MemoryStats (src/runtime/device_memory.zig:258-304). */

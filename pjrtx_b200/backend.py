@@ -56,7 +56,7 @@ _STATS_FIELDS = [
     "captured_program_captured_input_count", "donation_alias_output_count", "donation_alias_output_bytes",
     "fusion_group_execute_count", "execute_wall_us_total", "execute_wall_us_peak", "kernel_step_count",
     "generated_kernel_count", "arena_bytes", "scratch_bytes", "graph_capture_count", "graph_launch_count",
-    "kernel_launch_total",
+    "kernel_launch_total", "profile_event_gap_ns",
 ]
 
 

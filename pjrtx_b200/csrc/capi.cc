@@ -491,6 +491,7 @@ int pjrtx_b200_executable_stats(PjrtxB200Executable* executable, PjrtxB200Execut
       r.generated_kernel_count = s.generated_kernel_count; r.arena_bytes = s.arena_bytes; r.scratch_bytes = s.scratch_bytes;
       r.graph_capture_count = s.graph_capture_count; r.graph_launch_count = s.graph_launch_count;
       r.kernel_launch_total = s.kernel_launch_total;
+      r.profile_event_gap_ns = s.profile_event_gap_ns;
       uint64_t n = out->struct_size ? std::min<uint64_t>(out->struct_size, sizeof r) : sizeof r; memcpy(out, &r, n); return 1;)
 }
 

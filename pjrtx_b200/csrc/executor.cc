@@ -1652,9 +1652,13 @@ void record_step_event(cudaEvent_t event, cudaStream_t stream, bool capturing) {
 // Waits for the last step event and fills step_ms from consecutive event pairs.
 void collect_step_times(Executable* exe) {
   const size_t n = exe->kp.steps.size();
-  cudaEventSynchronize(exe->step_events[n]);
+  cudaEventSynchronize(exe->step_events[n + 1]);
   exe->step_ms.assign(n, 0.f);
   for (size_t k = 0; k < n; k++) cudaEventElapsedTime(&exe->step_ms[k], exe->step_events[k], exe->step_events[k + 1]);
+  // The last two records have nothing between them: their distance is what the records themselves cost.
+  float gap_ms = 0.f;
+  if (cudaEventElapsedTime(&gap_ms, exe->step_events[n], exe->step_events[n + 1]) == cudaSuccess && gap_ms > 0.f)
+    exe->stats.profile_event_gap_ns = (uint64_t)(gap_ms * 1e6f);
 }
 
 // `timed`: an event is recorded before every step and after the last one. Outside a stream capture the call then
@@ -1678,7 +1682,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
   } restore{exe, pdl_setting};
   const uint64_t launches_at_entry = *launches;
   if (timed) {
-    while (exe->step_events.size() < kp.steps.size() + 1) {
+    while (exe->step_events.size() < kp.steps.size() + 2) {
       cudaEvent_t e;
       cudaEventCreate(&e);
       exe->step_events.push_back(e);
@@ -1850,6 +1854,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
   }
   if (timed) {
     record_step_event(exe->step_events[kp.steps.size()], dev->stream, capturing);
+    record_step_event(exe->step_events[kp.steps.size() + 1], dev->stream, capturing);  // an empty interval: calibration
     if (!capturing) collect_step_times(exe);
   }
   return true;

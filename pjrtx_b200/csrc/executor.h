@@ -47,6 +47,9 @@ struct ExecutableStats {
   uint64_t arena_bytes = 0, scratch_bytes = 0;
   uint64_t graph_capture_count = 0, graph_launch_count = 0;
   uint64_t kernel_launch_total = 0;      // kernels enqueued since compile
+  // Profiling: what two event records with nothing between them read in the latest profiled execution - the part of
+  // every step time that is the measurement's, not the kernel's (0 before the first profiled execution).
+  uint64_t profile_event_gap_ns = 0;
 };
 
 // One segment of a chained streaming contraction (kernels.h, DotChainSegment): a group of contractions sharing an
