@@ -52,19 +52,32 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 __device__ __forceinline__ void st_wire(void* p, unsigned d0, unsigned d1, unsigned step) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(step), "r"(d1), "r"(step) : "memory");
 }
-// Polls until both halves carry `step`; false when the launch's deadline passed (seen by this thread, or by another
-// thread of the CTA that has set *gave_up).
-__device__ __forceinline__ bool ld_wire(const void* p, unsigned step, unsigned* d0, unsigned* d1, unsigned long long deadline,
-                                        volatile int* gave_up) {
-  for (unsigned spin = 0;; spin++) {
-    unsigned a, fa, b, fb;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(p) : "memory");
-    if (fa == step && fb == step) {
-      *d0 = a;
-      *d1 = b;
-      return true;
-    }
-    if ((spin & 63) == 63) {
+// Polls until both halves of a vector carry `step`; false when the launch's deadline passed (seen by this thread, or
+// by another thread of the CTA that has set *gave_up). One vector of each source in `mask` at once: all loads of a
+// round are issued before the first is looked at, so that waiting for eight peers costs the slowest arrival plus one
+// round trip to L2, not eight.
+// Source q's vector is at first + q * stride (bytes).
+__device__ __forceinline__ bool ld_wire_all(const unsigned char* first, unsigned long long stride, unsigned mask, unsigned step,
+                                            unsigned (&d0)[kPeerMax], unsigned (&d1)[kPeerMax], unsigned long long deadline,
+                                            volatile int* gave_up) {
+  unsigned pending = mask;
+  for (unsigned spin = 0; pending; spin++) {
+    unsigned a[kPeerMax], fa[kPeerMax], b[kPeerMax], fb[kPeerMax];
+#pragma unroll
+    for (int q = 0; q < kPeerMax; q++)
+      if (pending >> q & 1u)
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a[q]), "=r"(fa[q]), "=r"(b[q]), "=r"(fb[q])
+                     : "l"(first + q * stride)
+                     : "memory");
+#pragma unroll
+    for (int q = 0; q < kPeerMax; q++)
+      if ((pending >> q & 1u) && fa[q] == step && fb[q] == step) {
+        d0[q] = a[q];
+        d1[q] = b[q];
+        pending &= ~(1u << q);
+      }
+    if (pending && (spin & 63) == 63) {
       if (*gave_up) return false;
       if (global_timer_ns() > deadline) {
         *gave_up = 1;
@@ -72,6 +85,7 @@ __device__ __forceinline__ bool ld_wire(const void* p, unsigned step, unsigned* 
       }
     }
   }
+  return true;
 }
 
 template <typename T> struct Pair;  // 8 data bytes = two 32-bit words
@@ -155,13 +169,16 @@ __global__ void __launch_bounds__(256) peer_all_reduce_kernel(PeerArgs a, const 
     float acc[Pair<T>::N];
 #pragma unroll
     for (int e = 0; e < Pair<T>::N; e++) acc[e] = 0.f;
+    {
+      unsigned d0[kPeerMax], d1[kPeerMax];
 #pragma unroll
-    for (int q = 0; q < kPeerMax; q++)
-      if (q < a.world) {
-        unsigned d0 = 0, d1 = 0;
-        ok &= ld_wire(slot(a.rank, 0, q) + j, step, &d0, &d1, deadline, &gave_up);
-        Pair<T>::add(acc, d0, d1);
-      }
+      for (int q = 0; q < kPeerMax; q++) d0[q] = d1[q] = 0;
+      ok &= ld_wire_all(reinterpret_cast<const unsigned char*>(slot(a.rank, 0, 0) + j), a.slot_bytes, (1u << a.world) - 1u, step, d0, d1,
+                        deadline, &gave_up);
+#pragma unroll
+      for (int q = 0; q < kPeerMax; q++)  // rank order, whoever arrived first
+        if (q < a.world) Pair<T>::add(acc, d0[q], d1[q]);
+    }
     unsigned r0, r1;
     Pair<T>::store(acc, &r0, &r1);
 #pragma unroll
@@ -171,13 +188,14 @@ __global__ void __launch_bounds__(256) peer_all_reduce_kernel(PeerArgs a, const 
   }
   // C: collect the other parts.
   for (unsigned long long j = first; j < part_pairs; j += stride) {
+    unsigned d0[kPeerMax], d1[kPeerMax];
+#pragma unroll
+    for (int p = 0; p < kPeerMax; p++) d0[p] = d1[p] = 0;
+    ok &= ld_wire_all(reinterpret_cast<const unsigned char*>(slot(a.rank, 1, 0) + j), a.slot_bytes,
+                      ((1u << a.world) - 1u) & ~(1u << a.rank), step, d0, d1, deadline, &gave_up);
 #pragma unroll
     for (int p = 0; p < kPeerMax; p++)
-      if (p < a.world && p != a.rank) {
-        unsigned d0 = 0, d1 = 0;
-        ok &= ld_wire(slot(a.rank, 1, p) + j, step, &d0, &d1, deadline, &gave_up);
-        out[(unsigned long long)p * part_pairs + j] = make_uint2(d0, d1);
-      }
+      if (p < a.world && p != a.rank) out[(unsigned long long)p * part_pairs + j] = make_uint2(d0[p], d1[p]);
   }
   if (!ok) atomicExch(a.error_flag, 21);
 }
