@@ -328,3 +328,48 @@ def test_plan_fingerprint_is_stable_and_sensitive(backend):
         assert backend.plan_fingerprint(build()) != a
     finally:
         backend.lib.pjrtx_b200_unregister_custom_call(b"tests.fingerprint.identity")
+
+
+def test_decode_attention_kernel_choice_and_grid(backend, monkeypatch):
+    """Planner rules of the decode attention step (device independent, 148 SMs assumed): 16-bit caches with 4 or 8
+    query heads per KV head, head size 64 / 128 and at least one 64-key stage go to the tensor-core kernel with one
+    wave of two CTAs per SM and no split shorter than 128 keys; a shorter buffer, f32 caches or another head ratio go to
+    the CUDA-core kernel, which keeps to one wave of one CTA per SM when there are fewer (sequence, KV head) pairs
+    than SMs."""
+    from pjrtx_b200 import PlanBuilder
+
+    monkeypatch.delenv("PJRTX_B200_ATTENTION_MMA", raising=False)
+    monkeypatch.delenv("PJRTX_B200_ATTENTION_STAGED", raising=False)
+    monkeypatch.delenv("PJRTX_B200_ATTENTION_SPLITS", raising=False)
+
+    def plan_of(dtype, batch, heads, kv_heads, hd, kv_len):
+        b = PlanBuilder()
+        pq = b.parameter(dtype, [batch, 1, heads, hd])
+        pk = b.parameter(dtype, [batch, kv_len, kv_heads, hd])
+        pv = b.parameter(dtype, [batch, kv_len, kv_heads, hd])
+        pt = b.parameter(P.S32, [])
+        b.set_outputs([b.custom_call("pjrtx.b200.scaled_dot_product_attention", [pq, pk, pv, pt], dtype, [batch, 1, heads, hd])])
+        steps = backend.describe_kernels(b)["steps"]
+        assert [s["type"] for s in steps] == ["attention_decode"]
+        return steps[0]
+
+    # 8B shape at batch 1: 8 pairs, 2304-key buffer -> tensor-core kernel, 18 splits of 128 keys (144 CTAs <= 296)
+    st = plan_of(P.BF16_CODE, 1, 32, 8, 128, 2304)
+    assert st["mma"] == 1 and st["splits"] == 18
+    # the same with a longer buffer: as many splits as one wave of two CTAs per SM holds (296 // 8 = 37), at most kv_len // 128
+    st = plan_of(P.BF16_CODE, 1, 32, 8, 128, 3744)
+    assert st["mma"] == 1 and st["splits"] == 29
+    # 256 pairs (batch 32): one split each
+    st = plan_of(P.BF16_CODE, 32, 32, 8, 128, 2304)
+    assert st["mma"] == 1 and st["splits"] == 1
+    # one eighth of the 70B shape: 32 pairs -> 9 splits
+    st = plan_of(P.BF16_CODE, 32, 8, 1, 128, 4352)
+    assert st["mma"] == 1 and st["splits"] == 9
+    # a buffer shorter than a stage, f32 caches, two heads per KV head: CUDA-core kernel
+    assert plan_of(P.BF16_CODE, 2, 16, 4, 128, 40)["mma"] == 0
+    assert plan_of(P.F32, 2, 8, 2, 64, 512)["mma"] == 0
+    assert plan_of(P.F16, 2, 8, 4, 64, 512)["mma"] == 0
+    # CUDA-core kernel with fewer pairs than SMs: one wave (148 // 8 = 18 splits, not 29)
+    monkeypatch.setenv("PJRTX_B200_ATTENTION_MMA", "0")
+    st = plan_of(P.BF16_CODE, 1, 32, 8, 128, 3744)
+    assert st["mma"] == 0 and st["splits"] == 18
