@@ -45,15 +45,57 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
+    # NVML bit masks of the same reasons (nvmlClocksEventReasons*): read-only queries, a millisecond each, so that a
+    # timed region of a few hundred milliseconds still gets a dozen samples; nvidia-smi is the fallback.
+    NVML_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+
     def __init__(self, device: int):
         self.device = device
         self.sm, self.mx, self.reasons = [], [], set()
         self._stop = threading.Event()
         self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            # NVML orders devices by PCI bus id; map the CUDA ordinal through the bus id torch reports.
+            bus = getattr(torch.cuda.get_device_properties(device), "pci_bus_id", None)
+            handle = None
+            if bus is not None:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    if pynvml.nvmlDeviceGetPciInfo(h).bus == bus:
+                        handle = h
+                        break
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(device)
+            self._nvml = (pynvml, handle)
+        except Exception:
+            self._nvml = None
+
+    def _poll_nvml(self) -> bool:
+        pynvml, h = self._nvml
+        try:
+            sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            get = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            bits = int(get(h))
+        except Exception:
+            return False
+        self.sm.append(float(sm))
+        self.mx.append(float(mx))
+        for name, bit in self.NVML_BITS.items():
+            if bits & bit:
+                self.reasons.add(name)
+        return True
 
     def _poll_once(self):
         import subprocess
 
+        if self._nvml is not None and self._poll_nvml():
+            return
         try:
             out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.device)],
                                  capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
@@ -76,7 +118,7 @@ class ClockSampler:
         def loop():
             while not self._stop.is_set():
                 self._poll_once()
-                self._stop.wait(0.1)
+                self._stop.wait(0.02 if self._nvml is not None else 0.1)
 
         self._thread = threading.Thread(target=loop, daemon=True)
         self._thread.start()
