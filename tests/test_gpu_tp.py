@@ -31,7 +31,7 @@ def _shard(arr, split_dim, rank, world):
     return np.ascontiguousarray(np.take(arr, range(rank * n, (rank + 1) * n), axis=split_dim))
 
 
-def _worker(rank, world, port, batch, peer, queue):
+def _worker(rank, world, port, batch, peer, queue, int8=False):
     import torch.distributed as dist
 
     import pjrtx_b200
@@ -41,7 +41,7 @@ def _worker(rank, world, port, batch, peer, queue):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200)
+        _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200, int8)
     except Exception:  # report instead of leaving the parent to wait for its timeout
         import traceback
 
@@ -51,15 +51,17 @@ def _worker(rank, world, port, batch, peer, queue):
         dist.destroy_process_group()
 
 
-def _config(world):
-    """Two KV heads shard over two ranks; four ranks get a copy with twice the heads."""
-    return llama.TINY if world <= 2 else dataclasses.replace(llama.TINY, heads=2 * world, kv_heads=world)
+def _config(world, int8=False):
+    """Two KV heads shard over two ranks; four ranks get a copy with twice the heads. `int8`: weight-only int8 linear
+    layers with f16 column scales (the scales shard with the columns they belong to)."""
+    cfg = llama.TINY if world <= 2 else dataclasses.replace(llama.TINY, heads=2 * world, kv_heads=world)
+    return dataclasses.replace(cfg, int8_weights=True) if int8 else cfg
 
 
-def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
+def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200, int8=False):
     if True:
         be = pjrtx_b200.Backend()
-        cfg = _config(world)
+        cfg = _config(world, int8)
         max_len, filled = 64, 40
         full, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=world, return_logits=True)
         weights = llama.make_weights(cfg, seed=0)
@@ -87,10 +89,12 @@ def _run_rank(rank, world, batch, peer, queue, dist, pjrtx_b200):
                                  for r in results]))
 
 
-@pytest.mark.parametrize("world,batch,peer", [(2, 2, False), (2, 16, False), (2, 2, True), (2, 16, True),
-                                              (4, 16, False), (4, 2, True), (4, 16, True),
-                                              (8, 2, False), (8, 16, False), (8, 2, True), (8, 16, True)])
-def test_tensor_parallel_decode_matches_oracle(world, batch, peer):
+@pytest.mark.parametrize("world,batch,peer,int8", [(2, 2, False, False), (2, 16, False, False), (2, 2, True, False),
+                                                   (2, 16, True, False), (2, 16, True, True),
+                                                   (4, 16, False, False), (4, 2, True, False), (4, 16, True, False),
+                                                   (8, 2, False, False), (8, 16, False, False), (8, 2, True, False),
+                                                   (8, 16, True, False)])
+def test_tensor_parallel_decode_matches_oracle(world, batch, peer, int8):
     import torch
     import torch.multiprocessing as mp
 
@@ -101,7 +105,7 @@ def test_tensor_parallel_decode_matches_oracle(world, batch, peer):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, batch, peer, queue)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, batch, peer, queue, int8)) for r in range(world)]
     for p in procs:
         p.start()
     got = {}
@@ -117,7 +121,7 @@ def test_tensor_parallel_decode_matches_oracle(world, batch, peer):
                 p.terminate()
     assert all(p.exitcode == 0 for p in procs)
 
-    cfg = _config(world)
+    cfg = _config(world, int8)
     max_len, filled = 64, 40
     full, names = llama.build_decode_step(cfg, batch, max_len, num_partitions=1, return_logits=True)
     weights = llama.make_weights(cfg, seed=0)
