@@ -1815,7 +1815,7 @@ bool run_steps(Executable* exe, DeviceState& ds, const Pointers& ptr, uint64_t* 
       }
       case Step::kAttnPrefill:
         if (!attn_prefill_launch(st.attn_prefill, ptr.of(st.inputs[0]), ptr.of(st.inputs[1]), ptr.of(st.inputs[2]),
-                                 ptr.of(st.outputs[0]), exe->pdl, dev->stream)) {
+                                 ptr.of(st.outputs[0]), exe->pdl, dev->stream, dev->error_flag_dev)) {
           *error = "attention kernel refused the shape";
           return false;
         }

@@ -722,11 +722,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned* r, unsigned smem_add
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
 }
-// 16-byte asynchronous copy; `bytes` = 0 writes zeros without reading the source.
-__device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* src, int bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
-}
-
 // STAGES = 3: two CTAs per SM, two stages in flight each. (A two-stage ring with three CTAs per SM and a third more
 // splits was measured on thirty-two (sequence, KV head) pairs of 4K keys: no faster.)
 template <typename T, int REP, int HD, int STAGES>
@@ -1155,8 +1150,8 @@ int dispatch_decode(int rep, int hd, const DecodeArgs& a, dim3 grid, const void*
 // q and out are [batch, kv_heads, seq, rep, head_dim] (the operand and result layout of the recognised
 // dot_general -> masked softmax -> dot_general form), so the `seq * rep` query rows that share one KV head are one
 // contiguous row-major matrix; row `x` belongs to position x / rep. One CTA (4 warps) owns 64 consecutive rows and
-// walks the keys 0..(its last position) in stages of 64 through the same cp.async ring and swizzled layout as the
-// decode kernel above; every warp owns 16 rows and multiplies them with all 64 keys of a stage:
+// walks the keys 0..(its last position) in stages of 64 through the same ring of tiled tensor-map copies and swizzled
+// layout as the decode kernel above; every warp owns 16 rows and multiplies them with all 64 keys of a stage:
 //   S[16 x 64] = Q[16 x HD] . K^T (mma.m16n8k16, Q fragments in registers), mask key <= position, online softmax on
 //   the fragments, O[16 x HD] += P[16 x 64] . V with the rounded probabilities as A fragments.
 // Scores and probabilities never leave the SM (the explicit form writes and re-reads batch*heads*seq*seq elements
@@ -1167,6 +1162,7 @@ struct PrefillArgs {
   int rep = 1, kv_heads = 1;
   long long kv_batch_stride = 0, kv_row_stride = 0, kv_head_stride = 0;
   float scale = 1.f;
+  int* error_flag = nullptr;
 };
 constexpr int kPrefillRows = 16 * kMmaWarps;
 constexpr int kPrefillStages = 2;  // 64 KiB per CTA at head_dim 128: three CTAs (twelve warps) per SM
@@ -1179,15 +1175,26 @@ __device__ __forceinline__ float ex2_approx(float x) {
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(kMmaWarps * 32, 3)
-attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                        T* __restrict__ out) {
+attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
+                        const __grid_constant__ CUtensorMap vmap, T* __restrict__ out) {
   static_assert(sizeof(T) == 2 && (HD == 64 || HD == 128), "16-bit elements, head_dim 64 or 128");
-  constexpr int THREADS = kMmaWarps * 32;
-  constexpr int CPR = HD / 8;
+  constexpr int HALVES = HD / 64;
   constexpr int TILE_BYTES = kMmaStageKeys * HD * 2;
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  extern __shared__ __align__(1024) unsigned char smem_attn[];
-  PJRTX_PDL_PROLOGUE();
+  // The swizzle of a tiled copy follows the absolute shared-memory address: tiles start on 1024-byte boundaries.
+  extern __shared__ unsigned char smem_prefill_raw[];
+  unsigned char* smem_attn = smem_prefill_raw + ((1024u - (attn_smem_u32(smem_prefill_raw) & 1023u)) & 1023u);
+  __shared__ int gave_up;
+  __shared__ __align__(8) uint64_t full[kPrefillStages];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < kPrefillStages; st++)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(attn_smem_u32(&full[st])), "r"(1));
+    gave_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.y, b = blockIdx.z;
@@ -1196,27 +1203,36 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
   const int j_end = (int)(last_row / a.rep) + 1;  // keys 0 .. last position of the tile
   const int stages_total = (j_end + kMmaStageKeys - 1) / kMmaStageKeys;
 
-  const T* kb = k + b * a.kv_batch_stride + g * a.kv_head_stride;
-  const T* vb = v + b * a.kv_batch_stride + g * a.kv_head_stride;
   const long long bg = ((long long)b * a.kv_heads + g) * a.rows;
   const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_attn);
   auto tile_offset = [](int row, int c) { return (unsigned)((c >> 3) * (kMmaStageKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)); };
+  // A stage is 64 K rows and 64 V rows, brought by one tiled copy per 128-byte column block of each (the decode
+  // kernel's maps and layout); one thread issues them. Keys past the tile's last position are other positions' rows
+  // (masked: their probabilities are zero and their values finite), keys past the sequence arrive as zeros.
   auto issue_stage = [&](int st) {
-    const unsigned dst = smem_base + (unsigned)(st % kPrefillStages) * STAGE_BYTES;
+    if (threadIdx.x != 0) return;
+    const int slot = st % kPrefillStages;
+    const unsigned bar = attn_smem_u32(&full[slot]);
+    const unsigned dst = smem_base + (unsigned)slot * STAGE_BYTES;
     const int j0 = st * kMmaStageKeys;
-    for (int idx = threadIdx.x; idx < kMmaStageKeys * CPR; idx += THREADS) {
-      const int row = idx / CPR, c = idx % CPR;
-      const int j = j0 + row;
-      const bool in = j < j_end;
-      const long long jj = in ? j : 0;
-      cp_async16(dst + tile_offset(row, c), kb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
-      cp_async16(dst + TILE_BYTES + tile_offset(row, c), vb + jj * a.kv_row_stride + c * 8, in ? 16 : 0);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(STAGE_BYTES) : "memory");
+#pragma unroll
+    for (int c = 0; c < HALVES; c++) {
+      asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                       dst + c * (kMmaStageKeys * 128)),
+                   "l"(&kmap), "r"(c * 64), "r"(j0), "r"(g), "r"(b), "r"(bar)
+                   : "memory");
+      asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                       dst + TILE_BYTES + c * (kMmaStageKeys * 128)),
+                   "l"(&vmap), "r"(c * 64), "r"(j0), "r"(g), "r"(b), "r"(bar)
+                   : "memory");
     }
   };
-  for (int st = 0; st < kPrefillStages - 1; st++) {
+  for (int st = 0; st < kPrefillStages - 1; st++)
     if (st < stages_total) issue_stage(st);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  }
+  unsigned long long deadline;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(deadline));
+  deadline += 2000000000ull;
 
   // This thread's two rows (accumulator rows lane / 4 and lane / 4 + 8 of the warp's 16) and their positions;
   // rows past the matrix end get position -1: every key is masked and nothing is stored.
@@ -1254,11 +1270,35 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
 #pragma unroll
     for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
 
+  bool arrived = true;
   for (int st = 0; st < stages_total; st++) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(kPrefillStages - 2) : "memory");
-    __syncthreads();  // stage st is complete for everyone, and everyone is done with stage st - 1
+    {  // stage st has landed (bounded by time)
+      const unsigned bar = attn_smem_u32(&full[st % kPrefillStages]), parity = (unsigned)(st / kPrefillStages) & 1u;
+      for (unsigned spin = 0;; spin++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) break;
+        if ((spin & 255) == 255) {
+          unsigned long long now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (now > deadline || *reinterpret_cast<volatile int*>(&gave_up)) {
+            gave_up = 1;
+            arrived = false;
+            break;
+          }
+        }
+      }
+    }
+    // Everyone is done with stage st - 1 (its slot is refilled below); a thread that gave up tells the others here.
+    arrived = __syncthreads_and(arrived ? 1 : 0) != 0;
+    if (!arrived) break;
     if (st + kPrefillStages - 1 < stages_total) issue_stage(st + kPrefillStages - 1);
-    asm volatile("cp.async.commit_group;" ::: "memory");
     const int key0 = st * kMmaStageKeys;
     if (key0 > warp_last_pos) continue;  // wholly above this warp's diagonal
 
@@ -1337,7 +1377,26 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
       }
     }
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (!arrived) {
+    // Copies of the next stage may still be in flight towards this CTA's shared memory: give them a bounded time
+    // before leaving, then report (nothing is stored).
+    for (int st = 0; st < stages_total; st++) {
+      const unsigned bar = attn_smem_u32(&full[st % kPrefillStages]), parity = (unsigned)(st / kPrefillStages) & 1u;
+      for (unsigned spin = 0; spin < (1u << 16); spin++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) break;
+      }
+    }
+    if (threadIdx.x == 0 && a.error_flag) atomicExch(a.error_flag, 8);
+    return;
+  }
 
   const int c0 = (lane & 3) * 2;
 #pragma unroll
@@ -1355,10 +1414,22 @@ attn_prefill_mma_kernel(PrefillArgs a, const T* __restrict__ q, const T* __restr
 template <typename T, int HD>
 int launch_prefill_mma(const PrefillArgs& a, dim3 grid, const void* q, const void* k, const void* v, void* out, bool pdl,
                        cudaStream_t stream) {
-  constexpr size_t smem = (size_t)kPrefillStages * 2 * kMmaStageKeys * HD * 2;
+  constexpr size_t smem = 1024 + (size_t)kPrefillStages * 2 * kMmaStageKeys * HD * 2;
   if (!raise_smem_limit((const void*)attn_prefill_mma_kernel<T, HD>, (int)smem)) return 0;
-  return launch_kernel(attn_prefill_mma_kernel<T, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q, (const T*)k,
-                       (const T*)v, (T*)out) == cudaSuccess
+  if (((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) != 0) return 0;
+  // K and V as [head_dim][keys][KV heads][sequences], the decode kernel's maps.
+  DecodeArgs view{};
+  view.kv_len = a.seq;
+  view.kv_heads = a.kv_heads;
+  view.batch = grid.z;
+  view.kv_batch_stride = a.kv_batch_stride;
+  view.kv_row_stride = a.kv_row_stride;
+  view.kv_head_stride = a.kv_head_stride;
+  CUtensorMap kmap, vmap;
+  const bool f16 = std::is_same<T, __half>::value;
+  if (!encode_kv_map(&kmap, k, f16, view, HD) || !encode_kv_map(&vmap, v, f16, view, HD)) return 0;
+  return launch_kernel(attn_prefill_mma_kernel<T, HD>, grid, dim3(kMmaWarps * 32), smem, stream, pdl, a, (const T*)q, kmap, vmap,
+                       (T*)out) == cudaSuccess
              ? 1
              : 0;
 }
@@ -1514,9 +1585,10 @@ bool attn_prefill_supported(const AttnPrefillShape& s) {
 }
 
 int attn_prefill_launch(const AttnPrefillShape& s, const void* q, const void* k, const void* v, void* out, bool pdl,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, int* error_flag) {
   if (!attn_prefill_supported(s)) return 0;
   PrefillArgs a;
+  a.error_flag = error_flag;
   a.seq = s.seq;
   a.rep = (int)s.rep;
   a.rows = s.seq * s.rep;

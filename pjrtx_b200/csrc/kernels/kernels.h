@@ -244,7 +244,7 @@ struct AttnPrefillShape {
 };
 bool attn_prefill_supported(const AttnPrefillShape& s);
 int attn_prefill_launch(const AttnPrefillShape& s, const void* q, const void* k, const void* v, void* out, bool pdl,
-                        cudaStream_t stream);
+                        cudaStream_t stream, int* error_flag = nullptr);
 
 // All-reduce (sum) over peer-mapped regions, one launch per rank (kernels/peer_reduce.cu). `regions[r]` is rank r's
 // region as mapped into this process (regions[rank] is the local one), `peer_region_bytes(slot_bytes)` long.
