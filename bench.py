@@ -654,7 +654,7 @@ def run_reference(args):
         "ms_per_step": 1e3 * batch / base["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": {"workload": workload, "batch": batch, "kv_prefill": filled},
         "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        # what the sample really was: decode steps timed on the truncated copy (the driver's --steps is echoed above)
+        # what the sample really was: decode steps timed on the truncated copy (the caller's --steps is echoed above)
         "steps_timed": timed_tokens, "layers_timed": args.cpu_layers,
     }
     print(json.dumps(line))
