@@ -51,7 +51,7 @@ Device* get_device(int ordinal) {
   }
   dev->sm_count = prop.multiProcessorCount;
   dev->memory_bytes = prop.totalGlobalMem;
-  snprintf(dev->name, sizeof dev->name, "%s", prop.name);
+  snprintf(dev->name, sizeof dev->name, "%.*s", (int)sizeof dev->name - 1, prop.name);
   if (!check_cuda(cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking), "cudaStreamCreate")) return nullptr;
   cudaMemPool_t pool;
   if (check_cuda(cudaDeviceGetDefaultMemPool(&pool, ordinal), "cudaDeviceGetDefaultMemPool")) {

@@ -75,8 +75,6 @@ __device__ __forceinline__ long long load_scalar(const void* p, int dtype) {
   }
 }
 
-constexpr int kWarps = 8;
-
 struct DecodeArgs {
   long long batch, heads, kv_heads, kv_len;
   long long q_batch_stride, q_head_stride;          // elements
